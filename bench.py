@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (N=1 and every N): the Llama-2-7B-shaped decoder-layer linear set in
+W4A16 g128 asymmetric -- q/k/v/o 4096x4096, gate/up 4096->11008, down
+11008->4096 -- at decode batch M=16, random-init N(0, 0.02) weights and
+N(0, 1) fp16 activations (synthetic; no checkpoint is available offline).
+One step = one pass of the seven linears over one layer set.  The timed
+region cycles through a pool of layer sets whose packed weights exceed the
+126 MB L2, so every step streams its weights from HBM.
+
+Reported metric: algorithmic HBM bytes per second of the W4A16 decode linears
+(packed codes + scales + packed zero points + X + Y, per linear, per step).
+``value`` is measured with inputs resident in HBM and the step replayed from a
+CUDA graph; ``e2e`` goes through ``VllmPackedInt4Linear.forward`` with host
+buffers (pinned H2D of X and D2H of Y inside the timed region).  With N>1
+every rank runs an independent replica (this config does not shard) and the
+values add up ("weak").  ``--impl reference`` times the reference's CPU path
+for the same linears, ``F.linear(x, Wdq)`` on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M_DECODE = 16
+GROUP = 128
+POOL_SETS = 6            # 6 x ~105 MB of packed weights: far beyond the 126 MB L2
+
+
+def w4a16_bytes(n, k, m, g=GROUP):
+    """Algorithmic bytes of one W4A16 linear: packed + scales + packed zeros + X + Y."""
+    return n * k // 2 + 2 * n * k // g + n * k // (2 * g) + 2 * m * k + 2 * m * n
+
+
+def layer_shapes():
+    from mindpipe_b200 import synth
+    return list(synth.LLAMA2_7B_LINEARS.items())
+
+
+def step_bytes(m):
+    return sum(w4a16_bytes(n, k, m) for _, (n, k) in layer_shapes())
+
+
+def step_flops(m):
+    return sum(2 * m * n * k for _, (n, k) in layer_shapes())
+
+
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs (read-only)."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {
+                pynvml.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                pynvml.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                pynvml.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                pynvml.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+            while not self._stop.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.02)
+        except Exception as err:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(err).__name__}")
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thr.join(timeout=2)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+# ----------------------------------------------------------------------------
+def cpu_reference_pass(sets, xs, repeats):
+    """The reference's W4A16 forward on the host: nn.Linear on dequantised fp16 weights
+    (algorithm/quantization/ptq/awq/source/awq/quantize/quantizer.py:109-130)."""
+    import torch
+    import torch.nn.functional as F
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        for r in range(repeats):
+            layer = sets[r % len(sets)]
+            for name, wdq in layer.items():
+                F.linear(xs[name], wdq)
+    return time.perf_counter() - t0
+
+
+def build_cpu_sets(n_sets, m):
+    """Dequantised fp16 weights produced by the oracle's restatement of pseudo_quantize_tensor."""
+    import torch
+    from mindpipe_b200 import synth
+    from oracle import pseudo_quant as O
+    sets, xs = [], {}
+    for s in range(n_sets):
+        layer = {}
+        for i, (name, (n, k)) in enumerate(layer_shapes()):
+            w = synth.normal_weight(n, k, seed=s, index=i).numpy()
+            wdq, _, _, _ = O.w4_group_asym_quantize(w, GROUP)
+            layer[name] = torch.from_numpy(wdq)
+        sets.append(layer)
+    for i, (name, (n, k)) in enumerate(layer_shapes()):
+        xs[name] = synth.normal_activation(m, k, seed=0, index=100 + i)
+    return sets, xs
+
+
+def run_reference(args, rank, world):
+    import torch
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    sets, xs = build_cpu_sets(2, M_DECODE)
+    for _ in range(max(args.warmup, 1)):
+        cpu_reference_pass(sets, xs, 1)
+    dt = cpu_reference_pass(sets, xs, args.steps)
+    gbs = step_bytes(M_DECODE) * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "w4a16_decode_linear_algorithmic_hbm_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} steps of the 7-linear set at M={M_DECODE}: torch CPU F.linear on "
+                                   "fp16 weights dequantised by the oracle, 2 layer sets alternating"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config():
+    return {"workload": "llama2-7b decoder-layer linear set (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008), "
+                        f"W4A16 asymmetric int4 g{GROUP}, decode M={M_DECODE}",
+            "weight_pool": f"{POOL_SETS} layer sets cycled, {POOL_SETS * step_bytes(M_DECODE) / 1e6:.0f} MB > 126 MB L2 "
+                           "(inputs larger than L2; no explicit flush)",
+            "parallelism": "replicas only (this config does not shard)"}
+
+
+# ----------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- build the pool: quantise seeded weights on the GPU with the product's own kernel ----
+    pool = []
+    for s in range(POOL_SETS):
+        layer = []
+        for i, (name, (n, k)) in enumerate(layer_shapes()):
+            w = synth.normal_weight(n, k, seed=s, index=i).to(dev)
+            packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+            mod = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k,
+                                       out_features=n, zero_point=zero)
+            mod.process_weights_after_loading()
+            layer.append((name, mod))
+            del w
+        pool.append(layer)
+    x_host = {name: synth.normal_activation(M_DECODE, k, seed=0, index=100 + i).pin_memory()
+              for i, (name, (n, k)) in enumerate(layer_shapes())}
+    x_dev = {name: t.to(dev) for name, t in x_host.items()}
+    y_host = {name: torch.empty((M_DECODE, n), dtype=torch.float16).pin_memory() for name, (n, k) in layer_shapes()}
+    torch.cuda.synchronize()
+
+    ws_bytes = max(ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) for _, (n, k) in layer_shapes())
+    ws = ops.new_workspace(ws_bytes, dev)          # the seven linears run back to back on one stream
+    y_dev = {name: torch.empty((M_DECODE, n), dtype=torch.float16, device=dev) for name, (n, k) in layer_shapes()}
+
+    def step(layer):
+        for name, mod in layer:
+            ops.w4a16_linear_decode(x_dev[name], mod.weight_packed, mod._scale_zero, workspace=ws, out=y_dev[name])
+
+    # ---- one CUDA graph per layer set: the kernels, without host launch gaps ----
+    for layer in pool[:2]:
+        step(layer)
+    torch.cuda.synchronize()
+    graphs = []
+    for layer in pool:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step(layer)
+        graphs.append((g, None))
+    launches_per_step = len(layer_shapes())
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        graphs[i % POOL_SETS][0].replay()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        ev0.record()
+        for i in range(args.steps):
+            graphs[(args.warmup + i) % POOL_SETS][0].replay()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if args.steps * ms < 200:          # keep the sampler alive long enough to see clocks under load
+            t_end = time.time() + 0.4
+            while time.time() < t_end:
+                graphs[0][0].replay()
+            torch.cuda.synchronize()
+
+    # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
+    def e2e_step(layer):
+        for name, mod in layer:
+            xd = x_host[name].to(dev, non_blocking=True)
+            y = mod(xd)
+            y_host[name].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(pool[i % POOL_SETS])
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(pool[(args.warmup + i) % POOL_SETS])
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        bytes_step = step_bytes(M_DECODE)
+        value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
+        e2e_val = world * bytes_step * args.steps / (e2e_ms * 1e-3) / 1e9
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_src = json.loads(peaks_path.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = 6650.0, "fallback 6.65 TB/s"
+        achieved = bytes_step * args.steps / (ms * 1e-3) / 1e9          # per GPU: the kernel's own rate
+        traffic = None
+        tr = ROOT / "profiles" / "w4a16_decode_traffic.json"
+        if tr.exists():
+            traffic = json.loads(tr.read_text()).get("dram_bytes_per_launch")
+        line = {
+            "metric": "w4a16_decode_linear_algorithmic_hbm_gbs", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_source": peak_src, "kernel": "w4a16_decode_kernel",
+                         "launch_bytes_avg": bytes_step / launches_per_step,
+                         "launch_us_avg": ms * 1e3 / (args.steps * launches_per_step)},
+            "e2e": {"value": e2e_val, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(t.numel() * 2 for t in x_host.values()),
+                    "d2h_bytes_per_step": sum(t.numel() * 2 for t in y_host.values())},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+            "tflops": world * step_flops(M_DECODE) * args.steps / (ms * 1e-3) / 1e12,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = torch.get_num_threads()
+            sets, xs = build_cpu_sets(2, M_DECODE)
+            cpu_reference_pass(sets, xs, 2)
+            reps = 40
+            dt = cpu_reference_pass(sets, xs, reps)
+            line["cpu_baseline"] = {"value": bytes_step * reps / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": f"{reps} passes of the 7-linear set at M={M_DECODE} (torch CPU F.linear on "
+                                              "oracle-dequantised fp16 weights), 2 layer sets alternating"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

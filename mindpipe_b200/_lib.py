@@ -1,0 +1,68 @@
+"""ctypes binding of ``libmindpipe_b200.so`` (the C ABI in ``include/mindpipe_b200.h``).
+
+The library is loaded lazily, once, under a lock (the reference guards its
+custom-op load the same way, acceleration/runtime_patches/vllm.patch:291-306).
+There is no CPU fallback: if the shared library is missing or a symbol is
+absent, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_char_p, c_int, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmindpipe_b200.so"
+
+_lock = threading.Lock()
+_lib = None
+
+# name -> (restype, argtypes); mirrors include/mindpipe_b200.h one to one.
+_P, _I, _Z = c_void_p, c_int, c_size_t
+SIGNATURES = {
+    "mp_abi_version": (_I, []),
+    "mp_status_string": (c_char_p, [_I]),
+    "mp_last_cuda_error": (_I, []),
+    "mp_w4a16_quantize": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "mp_w4a16_dequant": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_w4a16_prepare": (_I, [_P, _P, _I, _I, _I, _P, _P]),
+    "mp_w4a16_decode_workspace_bytes": (_Z, [_I, _I, _I]),
+    "mp_w4a16_decode_workspace_bytes_ex": (_Z, [_I, _I, _I, _I]),
+    "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
+    "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
+    "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
+}
+
+
+class MindPipeKernelError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m mindpipe_b200.build` "
+                "(there is no fallback path for the quantized kernels)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError if the symbol is absent
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, op: str, **shapes) -> None:
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.mp_status_string(status).decode()
+    detail = ", ".join(f"{k}={v}" for k, v in shapes.items())
+    extra = f", cudaError={lib.mp_last_cuda_error()}" if status == -5 else ""
+    raise MindPipeKernelError(f"{op} failed with status {status} ({msg}{extra}); {detail}")

@@ -1,0 +1,103 @@
+// Per-row (token / output channel) symmetric int8 quantisation.
+//
+// Arithmetic of quantize_activation_per_token_absmax and
+// quantize_weight_per_channel_absmax
+// (algorithm/quantization/ptq/smoothquant/source/smoothquant/fake_quant.py:10-31)
+// with the integer codes kept, which is what npu_dynamic_quant returns at
+// acceleration/runtime_patches/vllm_ascend.patch:3950:
+//   s    = f16( max(absmax, f16(1e-5)) / 127 )
+//   code = rint( f16( x / s ) )         (division in fp32, rounded to fp16 first)
+//   fake = f16( code * s )
+// The row is read with 128-bit loads, reduced with warp shuffles, and re-read
+// (an L1/L2 hit) for the second pass, so HBM sees it once.
+#include "common.cuh"
+
+namespace mp {
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
+                 float* __restrict__ scale, __half* __restrict__ fake) {
+  __shared__ float s_red[THREADS / 32];
+  __shared__ float s_scale;
+  const int row = blockIdx.x;
+  const __half* xr = x + (size_t)row * K;
+  const int chunks = K >> 3;
+  float amax = 0.0f;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(__habs2(h2[j]));
+      amax = fmaxf(amax, fmaxf(f.x, f.y));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < THREADS / 32 ? s_red[threadIdx.x] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (threadIdx.x == 0) {
+      const float eps = h2f(f2h(1e-5f));                      // clamp_(min=1e-5) on an fp16 tensor
+      const __half s = f2h(__fdiv_rn(fmaxf(v, eps), 127.0f)); // div_(q_max), rounded to fp16
+      s_scale = h2f(s);
+      if (scale) scale[row] = s_scale;
+    }
+  }
+  __syncthreads();
+  const float sf = s_scale;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half* h = reinterpret_cast<const __half*>(&raw);
+    float code[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) code[j] = rintf(h2f(f2h(__fdiv_rn(h2f(h[j]), sf))));
+    if (q) {
+      uint2 o;
+      o.x = (static_cast<uint32_t>(static_cast<int>(code[0])) & 0xFFu) |
+            ((static_cast<uint32_t>(static_cast<int>(code[1])) & 0xFFu) << 8) |
+            ((static_cast<uint32_t>(static_cast<int>(code[2])) & 0xFFu) << 16) |
+            ((static_cast<uint32_t>(static_cast<int>(code[3])) & 0xFFu) << 24);
+      o.y = (static_cast<uint32_t>(static_cast<int>(code[4])) & 0xFFu) |
+            ((static_cast<uint32_t>(static_cast<int>(code[5])) & 0xFFu) << 8) |
+            ((static_cast<uint32_t>(static_cast<int>(code[6])) & 0xFFu) << 16) |
+            ((static_cast<uint32_t>(static_cast<int>(code[7])) & 0xFFu) << 24);
+      *reinterpret_cast<uint2*>(q + (size_t)row * K + c * 8) = o;
+    }
+    if (fake) {
+      __half out[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out[j] = f2h(__fmul_rn(code[j], sf));
+      *reinterpret_cast<uint4*>(fake + (size_t)row * K + c * 8) = *reinterpret_cast<uint4*>(out);
+    }
+  }
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i8, void* scale_f32,
+                                      void* fake_f16, mp_stream_t stream) {
+  if (!x_f16 || M <= 0 || K <= 0 || (!q_i8 && !fake_f16)) return MP_ERR_INVALID_ARG;
+  if (K % 8 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || (q_i8 && !aligned(q_i8, 8)) || (fake_f16 && !aligned(fake_f16, 16))) return MP_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half* x = static_cast<const __half*>(x_f16);
+  int8_t* q = static_cast<int8_t*>(q_i8);
+  float* sc = static_cast<float*>(scale_f32);
+  __half* fk = static_cast<__half*>(fake_f16);
+  if (K <= 1024) {
+    act_quant_kernel<128><<<M, 128, 0, st>>>(x, M, K, q, sc, fk);
+  } else if (K <= 4096) {
+    act_quant_kernel<256><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
+  } else {
+    act_quant_kernel<512><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+  }
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}

@@ -1,0 +1,320 @@
+// W4A16 decode-shaped linear (M <= 64): y = x @ dequant(W)^T, streaming the
+// packed weights once at HBM rate.
+//
+// Work split: a block owns ROWS_PER_BLOCK output rows and one slice of K; its
+// warps are arranged WN (rows) x 4 (K).  A warp step covers 32 rows x 128
+// columns: every lane fetches, per 8-row group, one 128-bit word vector (32
+// codes of one row) with a no-allocate streaming load plus one (scale, zero)
+// pair, dequantises in registers (dequant8) and feeds the result straight
+// into mma.sync m16n8k16 as the B fragment -- the weights never touch shared
+// memory.  The packed nibble order makes dequant8 emit column pairs
+// (k, k+4); instead of shuffling them, the activations are staged in shared
+// memory with the same permutation, in fragment order, so each A fragment is
+// one conflict-free 128-bit load that is reused across the four row groups.
+// Partial sums are reduced across the K-warps in shared memory, then across
+// the K slices through a workspace: every block stores its partial tile,
+// bumps a per-row-block counter, and the block that arrives last adds the
+// slices in a fixed order (deterministic), adds the bias, writes fp16 and
+// re-arms the counter for the next call.
+#include "common.cuh"
+
+namespace mp {
+
+constexpr int kWarpsK = 4;        // warps along K inside a block
+constexpr int kRowGroups = 4;     // 8-row groups per warp -> 32 rows per warp
+constexpr int kChunk = 128;       // columns one warp step covers
+
+struct DecodeParams {
+  const __half* x;
+  const uint32_t* packed;
+  const uint32_t* sz;     // [K/group, N] (scale, zero) f16 pairs
+  const __half* bias;
+  __half* y;
+  float* partials;        // [k_split, M, N]
+  int* counters;          // one per row block
+  int M, N, K, group;
+  int chunks;             // K / 128
+  int chunks_per_split;
+  int k_split;
+};
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MB: 16-row token blocks held per warp; HALF: only token rows 0..7 exist
+// (M <= 8, MB == 1); WN: warps along the row dimension; STAGE: chunks of
+// activations staged in shared memory at a time (multiple of 4).
+template <int MB, bool HALF, int WN, int STAGE>
+__global__ void __launch_bounds__(WN * kWarpsK * 32)
+w4a16_decode_kernel(const DecodeParams p) {
+  constexpr int THREADS = WN * kWarpsK * 32;
+  constexpr int ROWS = WN * 32;                    // output rows per block
+  constexpr int HR = HALF ? 1 : 2;                 // 8-row halves per token block
+  constexpr int TOK = MB * HR * 8;                 // token rows staged
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);                      // STAGE*4*MB*HR*32 units
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)STAGE * 4 * MB * HR * 32 * 16);
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wk = warp % kWarpsK, wn = warp / kWarpsK;
+  const int row0 = blockIdx.x * ROWS + wn * 32;    // first output row of this warp
+  const int split = blockIdx.y;
+  const int cs = split * p.chunks_per_split;
+  const int ce = min(p.chunks, cs + p.chunks_per_split);
+  const int words_per_row = p.K >> 3;
+
+  float acc[MB][kRowGroups][4];
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+    for (int r = 0; r < kRowGroups; ++r)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mb][r][i] = 0.0f;
+
+  uint4 qn[kRowGroups];
+  uint32_t szn[kRowGroups];
+  auto prefetch = [&](int chunk) {
+    const int kabs = chunk * kChunk + t * 32;
+    const int grp = kabs / p.group;
+#pragma unroll
+    for (int r = 0; r < kRowGroups; ++r) {
+      const int n = row0 + r * 8 + g;
+      if (n < p.N) {
+        qn[r] = ldg_stream_v4(p.packed + (size_t)n * words_per_row + (kabs >> 3));
+        szn[r] = __ldg(p.sz + (size_t)grp * p.N + n);
+      } else {
+        qn[r] = make_uint4(0, 0, 0, 0);
+        szn[r] = 0;
+      }
+    }
+  };
+
+  int my = cs + wk;
+  if (my < ce) prefetch(my);
+
+  for (int stage0 = cs; stage0 < ce; stage0 += STAGE) {
+    const int nch = min(STAGE, ce - stage0);
+    __syncthreads();  // the previous stage's fragments have been consumed
+    // Stage activations: 16-byte units of 8 columns, permuted to (k0,k4,k1,k5,k2,k6,k3,k7)
+    // and stored at [chunk][c][mb][half][g][t] so that a warp's fragment load is contiguous.
+    const int units = nch * 16;
+    for (int idx = tid; idx < TOK * units; idx += THREADS) {
+      const int m = idx / units, u = idx - m * units;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < p.M) {
+        const uint4 in = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)(stage0 * kChunk + u * 8));
+        v.x = prmt(in.x, in.z, 0x5410);  // (k0, k4)
+        v.y = prmt(in.x, in.z, 0x7632);  // (k1, k5)
+        v.z = prmt(in.y, in.w, 0x5410);  // (k2, k6)
+        v.w = prmt(in.y, in.w, 0x7632);  // (k3, k7)
+      }
+      const int kc = u >> 4, tt = (u >> 2) & 3, c = u & 3;
+      const int mb = m / (HR * 8), hr = (m / 8) % HR, gg = m & 7;
+      xs[((((kc * 4 + c) * MB + mb) * HR + hr) * 8 + gg) * 4 + tt] = v;
+    }
+    __syncthreads();
+
+#pragma unroll 1
+    for (int j = 0; j < STAGE / kWarpsK; ++j) {
+      if (my >= stage0 + nch) break;
+      uint4 q[kRowGroups];
+      ScaleZero sp[kRowGroups];
+#pragma unroll
+      for (int r = 0; r < kRowGroups; ++r) {
+        q[r] = qn[r];
+        const __half2 h = *reinterpret_cast<const __half2*>(&szn[r]);
+        sp[r] = make_scale_zero(__low2half(h), __high2half(h));
+      }
+      if (my + kWarpsK < ce) prefetch(my + kWarpsK);
+      const int kc = my - stage0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 alo[MB], ahi[MB];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const int base = (((kc * 4 + c) * MB + mb) * HR) * 32 + lane;
+          alo[mb] = xs[base];
+          ahi[mb] = HALF ? make_uint4(0, 0, 0, 0) : xs[base + 32];
+        }
+#pragma unroll
+        for (int r = 0; r < kRowGroups; ++r) {
+          const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
+          __half2 v[4];
+          dequant8(word, sp[r], v);
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            mma_m16n8k16(acc[mb][r], alo[mb].x, ahi[mb].x, alo[mb].y, ahi[mb].y, h2_as_u32(v[0]), h2_as_u32(v[1]));
+            mma_m16n8k16(acc[mb][r], alo[mb].z, ahi[mb].z, alo[mb].w, ahi[mb].w, h2_as_u32(v[2]), h2_as_u32(v[3]));
+          }
+        }
+      }
+      my += kWarpsK;
+    }
+  }
+
+  // ---- reduce the K-warps of this block: red[wk][wn][m][32 rows] ----
+  constexpr int MROWS = MB * 16;
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+    for (int r = 0; r < kRowGroups; ++r) {
+      float* base = red + (((size_t)(wk * WN + wn) * MROWS + mb * 16 + g) * 32 + r * 8 + 2 * t);
+      *reinterpret_cast<float2*>(base) = make_float2(acc[mb][r][0], acc[mb][r][1]);
+      if (!HALF) *reinterpret_cast<float2*>(base + 8 * 32) = make_float2(acc[mb][r][2], acc[mb][r][3]);
+    }
+  __syncthreads();
+
+  const int nl = tid & 31;                 // row inside a 32-row warp tile
+  const int grp_m = tid >> 5;              // THREADS/32 (m, wn) pairs per pass
+  const bool direct = p.k_split == 1;
+  for (int e = grp_m; e < WN * p.M; e += THREADS / 32) {
+    const int wn2 = e / p.M, m = e - wn2 * p.M;
+    const int n = blockIdx.x * ROWS + wn2 * 32 + nl;
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kWarpsK; ++k) s += red[((size_t)(k * WN + wn2) * MROWS + m) * 32 + nl];
+    if (n < p.N) {
+      if (direct) {
+        if (p.bias) s += h2f(p.bias[n]);
+        p.y[(size_t)m * p.N + n] = f2h(s);
+      } else {
+        p.partials[((size_t)split * p.M + m) * p.N + n] = s;
+      }
+    }
+  }
+  if (direct) return;
+
+  // ---- cross-slice reduction by the block that arrives last ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int prev = atomicAdd(p.counters + blockIdx.x, 1);
+    s_last = (prev == p.k_split - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = grp_m; e < WN * p.M; e += THREADS / 32) {
+    const int wn2 = e / p.M, m = e - wn2 * p.M;
+    const int n = blockIdx.x * ROWS + wn2 * 32 + nl;
+    if (n >= p.N) continue;
+    float s = 0.0f;
+    for (int k = 0; k < p.k_split; ++k) s += __ldcg(p.partials + ((size_t)k * p.M + m) * p.N + n);
+    if (p.bias) s += h2f(p.bias[n]);
+    p.y[(size_t)m * p.N + n] = f2h(s);
+  }
+  if (tid == 0) p.counters[blockIdx.x] = 0;  // ready for the next call
+}
+
+struct DecodePlan {
+  int mb;        // 16-row token blocks
+  bool half;     // M <= 8
+  int wn;        // warps along rows
+  int stage;     // staged chunks
+  int rows;      // rows per block
+  int row_blocks;
+  int k_split;
+  int chunks_per_split;
+  size_t smem;
+};
+
+static DecodePlan plan_decode(int M, int N, int K, int k_split_req) {
+  DecodePlan pl{};
+  pl.mb = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
+  pl.half = M <= 8;
+  pl.wn = M <= 8 ? 1 : 2;
+  pl.stage = pl.mb == 1 ? 8 : 4;
+  pl.rows = pl.wn * 32;
+  pl.row_blocks = (N + pl.rows - 1) / pl.rows;
+  const int chunks = K / kChunk;
+  int ks = k_split_req;
+  if (ks <= 0) {
+    // Aim at roughly 512 resident warps' worth of blocks over the 148 SMs while
+    // keeping at least one chunk per K-warp in every slice.
+    const int target_blocks = kSmCount * (pl.wn == 1 ? 6 : 3);
+    ks = (target_blocks + pl.row_blocks / 2) / pl.row_blocks;
+  }
+  ks = ks < 1 ? 1 : ks;
+  int cps = (chunks + ks - 1) / ks;
+  if (cps < kWarpsK && chunks >= kWarpsK) cps = kWarpsK;
+  pl.chunks_per_split = cps;
+  pl.k_split = (chunks + cps - 1) / cps;
+  const int hr = pl.half ? 1 : 2;
+  pl.smem = (size_t)pl.stage * 4 * pl.mb * hr * 32 * 16 + (size_t)kWarpsK * pl.wn * pl.mb * 16 * 32 * sizeof(float);
+  return pl;
+}
+
+constexpr size_t kCounterBytes = 16384;  // room for 4096 row blocks
+
+template <int MB, bool HALF, int WN, int STAGE>
+static int launch_decode(const DecodeParams& p, const DecodePlan& pl, cudaStream_t st) {
+  auto kern = w4a16_decode_kernel<MB, HALF, WN, STAGE>;
+  if (pl.smem > 48 * 1024) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  }
+  dim3 grid(pl.row_blocks, pl.k_split);
+  kern<<<grid, WN * kWarpsK * 32, pl.smem, st>>>(p);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split) {
+  if (M <= 0 || M > 64 || N <= 0 || K <= 0 || K % kChunk != 0) return 0;
+  const DecodePlan pl = plan_decode(M, N, K, k_split);
+  return kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
+}
+
+extern "C" size_t mp_w4a16_decode_workspace_bytes(int M, int N, int K) {
+  return mp_w4a16_decode_workspace_bytes_ex(M, N, K, 0);
+}
+
+extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                         const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                         void* workspace, size_t workspace_bytes, int k_split,
+                                         mp_stream_t stream) {
+  if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
+  if (M > 64 || K % kChunk != 0 || group % 32 != 0 || K % group != 0 || N % 8 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 2)) return MP_ERR_ALIGNMENT;
+  const DecodePlan pl = plan_decode(M, N, K, k_split);
+  if ((size_t)pl.row_blocks * sizeof(int) > kCounterBytes) return MP_ERR_UNSUPPORTED;
+  DecodeParams p{};
+  p.x = static_cast<const __half*>(x_f16);
+  p.packed = static_cast<const uint32_t*>(packed_i32);
+  p.sz = static_cast<const uint32_t*>(sz_f16x2);
+  p.bias = static_cast<const __half*>(bias_f16);
+  p.y = static_cast<__half*>(y_f16);
+  p.M = M; p.N = N; p.K = K; p.group = group;
+  p.chunks = K / kChunk;
+  p.chunks_per_split = pl.chunks_per_split;
+  p.k_split = pl.k_split;
+  if (pl.k_split > 1) {
+    const size_t need = kCounterBytes + (size_t)pl.k_split * M * N * sizeof(float);
+    if (!workspace || workspace_bytes < need) return MP_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return MP_ERR_ALIGNMENT;
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kCounterBytes);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pl.mb == 1 && pl.half) return launch_decode<1, true, 1, 8>(p, pl, st);
+  if (pl.mb == 1) return launch_decode<1, false, 2, 8>(p, pl, st);
+  if (pl.mb == 2) return launch_decode<2, false, 2, 4>(p, pl, st);
+  return launch_decode<4, false, 2, 4>(p, pl, st);
+}
+
+extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                      const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                      void* workspace, size_t workspace_bytes, mp_stream_t stream) {
+  return mp_w4a16_linear_decode_ex(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
+                                   workspace_bytes, 0, stream);
+}

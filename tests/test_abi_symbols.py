@@ -1,0 +1,61 @@
+"""The shared library loads on a CPU-only box and exports what the header declares."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    names = set()
+    for h in (ROOT / "include").glob("*.h"):
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        names |= set(re.findall(r"\b(mp_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from mindpipe_b200 import build
+    return build.build()
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = ctypes.CDLL(str(built_lib))
+    syms = declared_symbols()
+    assert len(syms) >= 10
+    for name in sorted(syms):
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+
+
+def test_ctypes_table_matches_header(built_lib):
+    from mindpipe_b200 import _lib
+    assert set(_lib.SIGNATURES) == declared_symbols()
+    lib = _lib.load()
+    assert lib.mp_abi_version() >= 1
+    assert lib.mp_status_string(0) == b"ok"
+    assert b"workspace" in lib.mp_status_string(-4)
+
+
+def test_argument_validation_needs_no_gpu(built_lib):
+    """Null pointers and bad shapes are rejected before anything touches a device."""
+    from mindpipe_b200 import _lib
+    lib = _lib.load()
+    assert lib.mp_w4a16_quantize(None, 8, 128, 128, None, None, None, None) == -1
+    assert lib.mp_act_quant_per_token(None, 4, 64, None, None, None, None) == -1
+    assert lib.mp_w4a16_decode_workspace_bytes(16, 4096, 4096) > 0
+    assert lib.mp_w4a16_decode_workspace_bytes(128, 4096, 4096) == 0     # decode kernel is M <= 64
+    assert lib.mp_w4a16_decode_workspace_bytes(1, 4096, 100) == 0        # K must be a multiple of 128
+    with pytest.raises(_lib.MindPipeKernelError, match="invalid argument"):
+        _lib.check(-1, "probe", M=1)
+
+
+def test_ops_reject_cpu_tensors():
+    import torch
+    from mindpipe_b200 import ops
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.act_quant_per_token(torch.zeros(2, 64, dtype=torch.float16))
+    with pytest.raises(TypeError):
+        ops.act_quant_per_token([1, 2, 3])

@@ -1,0 +1,55 @@
+"""GPU parity of the W8A8 pieces against the CPU oracle (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from mindpipe_b200 import synth
+from oracle import pseudo_quant as O
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.uint16)
+
+
+def _check_quant(x16: np.ndarray):
+    from mindpipe_b200 import ops
+    q, s, f = ops.act_quant_per_token(dev(x16), want_codes=True, want_fake=True)
+    fake, codes, sc = O.absmax_quant_last_dim(x16)
+    assert np.array_equal(q.cpu().numpy(), codes)                                  # int8 codes bit-exact
+    assert np.array_equal(s.cpu().numpy(), sc.astype(np.float32).reshape(s.shape))  # fp16 scale, widened
+    assert np.array_equal(bits(f.cpu().numpy()), bits(fake))
+
+
+def test_act_quant_golden(golden):
+    g = golden("w8a8_small.npz")
+    _check_quant(g["x"])            # includes an all-zero token and x20 outlier channels
+    from mindpipe_b200 import ops
+    _, _, f = ops.act_quant_per_token(dev(g["x"]), want_codes=False, want_fake=True)
+    assert np.array_equal(bits(f.cpu().numpy()), bits(g["x_fake"]))
+    _, _, wf = ops.act_quant_per_token(dev(g["w"]), want_codes=False, want_fake=True)
+    assert np.array_equal(bits(wf.cpu().numpy()), bits(g["w_fake"]))   # per-channel weights: same arithmetic
+
+
+@pytest.mark.parametrize("m,k", [(1, 8), (3, 64), (5, 1000), (17, 4096), (4, 14336), (2, 28672)])
+def test_act_quant_shapes(m, k):
+    _check_quant(synth.outlier_activation(m, k, seed=m, index=k).numpy())
+
+
+def test_act_quant_cfg3_full_size():
+    """Config 3: X[4096,4096] fp16 N(0,1), 1 % of channels x20, per-token dynamic int8."""
+    _check_quant(synth.outlier_activation(4096, 4096, seed=0, index=100).numpy())
+
+
+def test_act_quant_3d_and_empty():
+    from mindpipe_b200 import ops
+    x = synth.normal_activation(6, 256, seed=1).reshape(2, 3, 256).cuda()
+    q, s, _ = ops.act_quant_per_token(x)
+    assert q.shape == (2, 3, 256) and s.shape == (2, 3)
+    q, s, _ = ops.act_quant_per_token(torch.zeros(0, 64, dtype=torch.float16, device="cuda"))
+    assert q.shape == (0, 64) and s.shape == (0,)
