@@ -193,6 +193,9 @@ def run_ours(args, rank, world, local_rank):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
+    # Weights are static from here on, so the decode kernels may prefetch them while the
+    # previous kernel of the stream drains (programmatic dependent launch).
+    from mindpipe_b200 import _lib
     # ---- build the pool: quantise seeded weights on the GPU with the product's own kernel ----
     pool = []
     for s in range(POOL_SETS):
@@ -211,6 +214,7 @@ def run_ours(args, rank, world, local_rank):
     x_dev = {name: t.to(dev) for name, t in x_host.items()}
     y_host = {name: torch.empty((M_DECODE, n), dtype=torch.float16).pin_memory() for name, (n, k) in layer_shapes()}
     torch.cuda.synchronize()
+    _lib.load().mp_set_programmatic_launch(1 if args.pdl else 0)
 
     ws_bytes = max(ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) for _, (n, k) in layer_shapes())
     ws = ops.new_workspace(ws_bytes, dev)          # the seven linears run back to back on one stream
@@ -262,14 +266,16 @@ def run_ours(args, rank, world, local_rank):
             y_host[name].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        e2e_step(pool[i % POOL_SETS])
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(pool[(args.warmup + i) % POOL_SETS])
-    barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = float("nan")
+    if not args.no_e2e:
+        for i in range(args.warmup):
+            e2e_step(pool[i % POOL_SETS])
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_step(pool[(args.warmup + i) % POOL_SETS])
+        barrier()
+        e2e_s = time.perf_counter() - t0
 
     t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist is not None:
@@ -321,14 +327,19 @@ def run_ours(args, rank, world, local_rank):
 
 
 def main():
+    global POOL_SETS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--pool-sets", type=int, default=POOL_SETS, help="layer sets in the weight pool")
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch for the decode linears")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    POOL_SETS = max(2, args.pool_sets)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -90,11 +90,37 @@ size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split);
 int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                            const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                            void* workspace, size_t workspace_bytes, mp_stream_t stream);
-/* Same, with the K split and rows per block chosen by the caller (0 = automatic). */
+/*
+ * Same, with the K split chosen by the caller.  k_split == 0 is automatic: for
+ * M <= 16 a thread-block-cluster kernel that reduces the K split through
+ * distributed shared memory and touches no workspace; otherwise (M > 16, or
+ * an explicit k_split >= 1) the workspace kernel.
+ */
 int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                               const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                               void* workspace, size_t workspace_bytes, int k_split,
                               mp_stream_t stream);
+
+/*
+ * Prefill variant (any M; meant for M > 64): the same linear on the fp16 tensor
+ * cores (tcgen05 kind::f16, fp32 accumulators in TMEM), activations fed by TMA,
+ * int4 unpack + group dequant fused in as a producer stage that writes the
+ * dequantised tile straight into shared memory.  K % 64 == 0, group % 64 == 0.
+ * error_word as for mp_w8a8_gemm.
+ */
+int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                            const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                            int* error_word, mp_stream_t stream);
+
+/*
+ * Programmatic dependent launch for the decode linears (default off; returns
+ * the previous setting).  When on, a decode kernel may begin fetching its
+ * WEIGHTS while the preceding kernel of the stream is still finishing;
+ * activations, bias and outputs are only touched after that kernel has
+ * completed.  Enable it only when no kernel still in flight writes the weight
+ * buffers (weights are loaded once and then static, as in serving).
+ */
+int mp_set_programmatic_launch(int enabled);
 
 /* ------------------------------------------------------------------- W8A8 */
 
@@ -114,6 +140,92 @@ int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const v
  */
 int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i8, void* scale_f32,
                            void* fake_f16, mp_stream_t stream);
+
+/*
+ * y[M,N] = f16( (qx[M,K] . w[N,K]^T as int32) * x_scale[m] * w_scale[n] (+ bias[n]) )
+ * on the int8 tensor cores (tcgen05 kind::i8, int32 accumulators in TMEM).
+ * Stands in for torch_npu.npu_quant_matmul as called by
+ * AscendW8A8DynamicLinearMethod.apply
+ * (acceleration/runtime_patches/vllm_ascend.patch:4007-4015), with the weight
+ * kept in the reference's [out, in] layout.  Together with
+ * mp_act_quant_per_token it is the real-int twin of SmoothQuantLinear.forward
+ * (algorithm/quantization/ptq/smoothquant/source/smoothquant/fake_quant.py:84-88).
+ * K % 16 == 0; all pointers 16-byte aligned.  error_word (device int, may be
+ * NULL) is set to a non-zero value if a bounded device-side wait gives up.
+ */
+int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const void* w_i8, const void* w_scale_f32,
+                 const void* bias_f16, void* y_f16, int M, int N, int K, int* error_word,
+                 mp_stream_t stream);
+
+/*
+ * Raw accumulators acc[M,N] = qx . w^T as int32: npu_quant_matmul with
+ * output_dtype=int32 (acceleration/runtime_patches/vllm.patch:756-760), and
+ * the bit-exact check of the tensor-core path.
+ */
+int mp_w8a8_gemm_i32(const void* qx_i8, const void* w_i8, void* acc_i32, int M, int N, int K,
+                     int* error_word, mp_stream_t stream);
+
+/* -------------------------------------------------------------------- MoE */
+
+/*
+ * Router: softmax over fp32 logits[T,E], top-k, renormalise, cast to f16 --
+ * the in-repository statement of the Mixtral router,
+ * FlatQuantMixtralSparseMoeBlock._route
+ * (algorithm/quantization/qat/flatquant/source/flatquant/model_tools/mixtral_utils.py:330-333,349).
+ * idx_i32 [T,k], weights_f16 [T,k].  k <= 8.
+ */
+int mp_moe_router_topk(const void* logits_f32, int T, int E, int k, void* idx_i32, void* weights_f16,
+                       mp_stream_t stream);
+
+/*
+ * Sizes of the routing buffers for `max_rows` routed rows (T * k) over
+ * `num_local_experts` experts: the number of ints in the plan, and the number
+ * of rows of the expert-sorted buffers (every expert's segment is padded to a
+ * multiple of 128 rows).
+ */
+size_t mp_moe_plan_ints(int num_local_experts, int max_rows);
+int mp_moe_padded_rows(int num_local_experts, int max_rows);
+
+/*
+ * Routing + gather + per-token int8 quantisation for the experts
+ * [expert_lo, expert_hi) this GPU owns: the role of
+ * torch_npu.npu_moe_init_routing_quant in _run_expert_tile
+ * (acceleration/runtime_patches/vllm_ascend.patch:2369-2379), i.e. lines
+ * 174-183 of SmoothQuantPackedMoeExperts.forward (fake_quant.py).
+ *   plan_i32          ints: counts[E] | cursors[E] | segment offsets[E+1] |
+ *                     tile count | expert of each 128-row tile
+ *   dest_row_i32      [T*k] row of entry (t,j) in the sorted buffers, -1 if
+ *                     its expert is not local
+ *   routed_q_i8       [padded_rows, H] int8 codes; routed_scale_f32 [padded_rows]
+ * H % 16 == 0.
+ */
+int mp_moe_route_gather_quant(const void* hidden_f16, const void* topk_ids_i32, int T, int H, int k,
+                              int expert_lo, int expert_hi, void* plan_i32, void* dest_row_i32,
+                              void* routed_q_i8, void* routed_scale_f32, mp_stream_t stream);
+
+/*
+ * The expert MLP on routed, quantised rows: grouped int8 GEMM1 (gate|up) with
+ * the SwiGLU epilogue, per-token re-quantisation, grouped int8 GEMM2 with the
+ * dequant epilogue -- npu_grouped_matmul_swiglu_quant + npu_grouped_matmul of
+ * _run_expert_tile (vllm_ascend.patch:2391-2412), i.e. fake_quant.py:184-187.
+ *   w13_q_i8 [E, 2I, H] (gate rows first, then up), w13_scale_f32 [E, 2I]
+ *   w2_q_i8  [E, H, I],                             w2_scale_f32  [E, H]
+ *   d_out_f16 [padded_rows, H]
+ */
+size_t mp_moe_expert_stage_workspace_bytes(int padded_rows, int I);
+int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
+                        int padded_rows, int H, int I, int num_local_experts,
+                        const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
+                        const void* w2_scale_f32, void* d_out_f16, void* workspace,
+                        size_t workspace_bytes, int* error_word, mp_stream_t stream);
+
+/*
+ * out[t] = sum_j f16(d[dest_row(t,j)] * w[t,j]) in fp16, experts in ascending
+ * order: npu_moe_token_unpermute (vllm_ascend.patch:2415-2419), i.e.
+ * fake_quant.py:188-189.  Entries with dest_row < 0 are skipped.
+ */
+int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,
+                   const void* topk_weights_f16, int T, int H, int k, void* out_f16, mp_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -30,7 +30,18 @@ SIGNATURES = {
     "mp_w4a16_decode_workspace_bytes_ex": (_Z, [_I, _I, _I, _I]),
     "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
+    "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "mp_set_programmatic_launch": (_I, [_I]),
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
+    "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_w8a8_gemm_i32": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_moe_router_topk": (_I, [_P, _I, _I, _I, _P, _P, _P]),
+    "mp_moe_plan_ints": (_Z, [_I, _I]),
+    "mp_moe_padded_rows": (_I, [_I, _I]),
+    "mp_moe_route_gather_quant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "mp_moe_expert_stage_workspace_bytes": (_Z, [_I, _I]),
+    "mp_moe_expert_stage": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
+    "mp_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
 }
 
 

@@ -1,0 +1,314 @@
+// W8A8 MoE expert path: router, routing plan, gather + per-token quant,
+// SwiGLU re-quant and weighted combine.  The two grouped int8 GEMMs live in
+// w8a8_gemm.cu; this file holds the HBM-bound stages around them and the
+// entry point that chains them.
+//
+// Reference semantics: SmoothQuantPackedMoeExperts.forward
+// (algorithm/quantization/ptq/smoothquant/source/smoothquant/fake_quant.py:165-191);
+// real-int pipeline shape: _run_expert_tile
+// (acceleration/runtime_patches/vllm_ascend.patch:2356-2422) =
+// routing+quant -> grouped GEMM1 + SwiGLU + re-quant -> grouped GEMM2 -> unpermute.
+//
+// Layout: routed rows are sorted by expert; every expert's segment starts at
+// a multiple of 128 rows, so a 128-row GEMM tile never straddles experts.
+#include "common.cuh"
+#include "moe_api.cuh"
+
+namespace mp {
+
+constexpr int kTileRows = 128;
+constexpr int kMaxExperts = 256;
+
+// softmax(fp32) -> top-k -> renormalise -> fp16, one thread per token
+// (algorithm/quantization/qat/flatquant/source/flatquant/model_tools/mixtral_utils.py:330-333,349).
+__global__ void moe_router_topk_kernel(const float* __restrict__ logits, int T, int E, int k,
+                                       int* __restrict__ idx, __half* __restrict__ w) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const float* l = logits + (size_t)t * E;
+  float mx = -INFINITY;
+  for (int e = 0; e < E; ++e) mx = fmaxf(mx, l[e]);
+  float sum = 0.0f;
+  for (int e = 0; e < E; ++e) sum += expf(l[e] - mx);
+  float chosen_p[8];
+  int chosen[8];
+  float psum = 0.0f;
+  for (int j = 0; j < k; ++j) {
+    float best = -1.0f;
+    int bi = 0;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int i = 0; i < j; ++i) taken |= (chosen[i] == e);
+      const float pe = expf(l[e] - mx) / sum;
+      if (!taken && pe > best) { best = pe; bi = e; }     // strict >: ties go to the lower index
+    }
+    chosen[j] = bi;
+    chosen_p[j] = best;
+    psum += best;
+  }
+  for (int j = 0; j < k; ++j) {
+    idx[(size_t)t * k + j] = chosen[j];
+    w[(size_t)t * k + j] = f2h(chosen_p[j] / psum);
+  }
+}
+
+// counts[e] = routed entries whose expert is local expert e (experts [lo, hi)).
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_entries, int lo, int hi, int* __restrict__ counts) {
+  __shared__ int s_counts[kMaxExperts];
+  for (int i = threadIdx.x; i < hi - lo; i += blockDim.x) s_counts[i] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_entries; i += gridDim.x * blockDim.x) {
+    const int e = ids[i];
+    if (e >= lo && e < hi) atomicAdd(&s_counts[e - lo], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < hi - lo; i += blockDim.x)
+    if (s_counts[i]) atomicAdd(&counts[i], s_counts[i]);
+}
+
+// Padded segment offsets, the expert of every 128-row tile and the tile count.
+// plan layout (ints): [0,E) counts | [E,2E) cursors | [2E,3E+1) seg_offsets | 3E+1 num_tiles | 3E+2.. tile_expert
+__global__ void moe_plan_kernel(int* __restrict__ plan, int E, int max_tiles) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int* counts = plan;
+  int* cursors = plan + E;
+  int* seg = plan + 2 * E;
+  int* num_tiles = plan + 3 * E + 1;
+  int* tile_expert = plan + 3 * E + 2;
+  int off = 0, tiles = 0;
+  for (int e = 0; e < E; ++e) {
+    seg[e] = off;
+    cursors[e] = 0;
+    const int nt = (counts[e] + kTileRows - 1) / kTileRows;
+    for (int i = 0; i < nt && tiles < max_tiles; ++i) tile_expert[tiles++] = e;
+    off += nt * kTileRows;
+  }
+  seg[E] = off;
+  *num_tiles = tiles;
+}
+
+// One block per routed entry (t, j): claim a row in the expert's segment, record it, and
+// write the token's int8 codes and scale there -- the gather and the per-token quant of
+// npu_moe_init_routing_quant (acceleration/runtime_patches/vllm_ascend.patch:2369-2379)
+// in one pass.  Arithmetic as in act_quant.cu.
+__global__ void __launch_bounds__(256)
+moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict__ ids, int H, int k, int lo, int hi,
+                        int* __restrict__ plan, int E, int* __restrict__ dest_row,
+                        int8_t* __restrict__ routed_q, float* __restrict__ routed_scale) {
+  __shared__ float s_red[8];
+  __shared__ float s_scale;
+  __shared__ int s_dest;
+  const int entry = blockIdx.x;
+  const int e = ids[entry];
+  if (e < lo || e >= hi) {
+    if (threadIdx.x == 0) dest_row[entry] = -1;
+    return;
+  }
+  const int t = entry / k;
+  const __half* xr = hidden + (size_t)t * H;
+  const int chunks = H >> 3;
+  float amax = 0.0f;
+  for (int c = threadIdx.x; c < chunks; c += 256) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(__habs2(h2[j]));
+      amax = fmaxf(amax, fmaxf(f.x, f.y));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) v = fmaxf(v, s_red[i]);
+    const float eps = h2f(f2h(1e-5f));
+    s_scale = h2f(f2h(__fdiv_rn(fmaxf(v, eps), 127.0f)));
+    const int pos = atomicAdd(plan + E + (e - lo), 1);
+    s_dest = plan[2 * E + (e - lo)] + pos;
+    dest_row[entry] = s_dest;
+    routed_scale[s_dest] = s_scale;
+  }
+  __syncthreads();
+  const float sf = s_scale;
+  int8_t* qr = routed_q + (size_t)s_dest * H;
+  for (int c = threadIdx.x; c < chunks; c += 256) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half* h = reinterpret_cast<const __half*>(&raw);
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(h[j]), sf)))))) & 0xFFu) << (8 * j);
+      w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(h[j + 4]), sf)))))) & 0xFFu) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(qr + c * 8) = make_uint2(w0, w1);
+  }
+}
+
+// Second activation quant (fake_quant.py:186) with the row abs-max already
+// known from the GEMM1 epilogue: one pass over h.
+__global__ void __launch_bounds__(256)
+moe_requant_kernel(const __half* __restrict__ h, const unsigned int* __restrict__ absmax_bits, int I,
+                   const int* __restrict__ num_tiles, int8_t* __restrict__ q, float* __restrict__ scale) {
+  const int row = blockIdx.x;
+  if (row >= *num_tiles * kTileRows) return;
+  const float eps = h2f(f2h(1e-5f));
+  const float sf = h2f(f2h(__fdiv_rn(fmaxf(__uint_as_float(absmax_bits[row]), eps), 127.0f)));
+  if (threadIdx.x == 0) scale[row] = sf;
+  const __half* hr = h + (size_t)row * I;
+  int8_t* qr = q + (size_t)row * I;
+  for (int c = threadIdx.x; c < (I >> 3); c += 256) {
+    uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
+    const __half* hh = reinterpret_cast<const __half*>(&raw);
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hh[j]), sf)))))) & 0xFFu) << (8 * j);
+      w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hh[j + 4]), sf)))))) & 0xFFu) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(qr + c * 8) = make_uint2(w0, w1);
+  }
+}
+
+// out[t] = sum_j f16(d[dest(t,j)] * w[t,j]) with fp16 adds, visiting the token's experts in
+// ascending order as the reference's per-expert index_add_ does (fake_quant.py:188-189).
+// Entries routed elsewhere (dest < 0) contribute nothing.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __half* __restrict__ d, const int* __restrict__ dest_row, const int* __restrict__ ids,
+                   const __half* __restrict__ weights, int T, int H, int k, __half* __restrict__ out) {
+  const int t = blockIdx.x;
+  int order[8];
+  for (int j = 0; j < k; ++j) order[j] = j;
+  for (int a = 1; a < k; ++a)                      // insertion sort by expert id (k is tiny)
+    for (int b = a; b > 0 && ids[(size_t)t * k + order[b]] < ids[(size_t)t * k + order[b - 1]]; --b) {
+      const int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
+    }
+  for (int c = threadIdx.x; c < (H >> 3); c += 256) {
+    __half acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = f2h(0.0f);
+    for (int jj = 0; jj < k; ++jj) {
+      const int j = order[jj];
+      const int r = dest_row[(size_t)t * k + j];
+      if (r < 0) continue;
+      const __half wj = weights[(size_t)t * k + j];
+      uint4 raw = *reinterpret_cast<const uint4*>(d + (size_t)r * H + c * 8);
+      const __half* v = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = hadd_t(acc[i], hmul_t(v[i], wj));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + c * 8) = *reinterpret_cast<uint4*>(acc);
+  }
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" int mp_moe_router_topk(const void* logits_f32, int T, int E, int k, void* idx_i32, void* weights_f16,
+                                  mp_stream_t stream) {
+  if (!logits_f32 || !idx_i32 || !weights_f16 || T <= 0 || E <= 0 || k <= 0) return MP_ERR_INVALID_ARG;
+  if (k > 8 || k > E) return MP_ERR_UNSUPPORTED;
+  moe_router_topk_kernel<<<(T + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(logits_f32), T, E, k, static_cast<int*>(idx_i32), static_cast<__half*>(weights_f16));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" size_t mp_moe_plan_ints(int num_local_experts, int max_rows) {
+  const int max_tiles = max_rows / kTileRows + num_local_experts;
+  return (size_t)3 * num_local_experts + 2 + max_tiles;
+}
+
+extern "C" int mp_moe_padded_rows(int num_local_experts, int max_rows) {
+  return (max_rows / kTileRows + num_local_experts) * kTileRows;
+}
+
+extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* topk_ids_i32, int T, int H, int k,
+                                         int expert_lo, int expert_hi, void* plan_i32, void* dest_row_i32,
+                                         void* routed_q_i8, void* routed_scale_f32, mp_stream_t stream) {
+  if (!hidden_f16 || !topk_ids_i32 || !plan_i32 || !dest_row_i32 || !routed_q_i8 || !routed_scale_f32 || T <= 0 ||
+      H <= 0 || k <= 0)
+    return MP_ERR_INVALID_ARG;
+  const int E = expert_hi - expert_lo;
+  if (E <= 0 || E > kMaxExperts || H % 16 != 0 || k > 8) return MP_ERR_UNSUPPORTED;
+  if (!aligned(hidden_f16, 16) || !aligned(routed_q_i8, 16)) return MP_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* plan = static_cast<int*>(plan_i32);
+  const int n_entries = T * k;
+  const int padded = mp_moe_padded_rows(E, n_entries);
+  MP_CUDA_TRY(cudaMemsetAsync(plan, 0, sizeof(int) * E, st));
+  // padding rows get scale 0, so whatever codes they hold turn into zeros downstream
+  MP_CUDA_TRY(cudaMemsetAsync(routed_scale_f32, 0, sizeof(float) * padded, st));
+  int blocks = (n_entries + 255) / 256;
+  if (blocks > 4 * kSmCount) blocks = 4 * kSmCount;
+  moe_count_kernel<<<blocks, 256, 0, st>>>(static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi, plan);
+  MP_LAUNCH_CHECK();
+  moe_plan_kernel<<<1, 32, 0, st>>>(plan, E, padded / kTileRows);
+  MP_LAUNCH_CHECK();
+  moe_gather_quant_kernel<<<n_entries, 256, 0, st>>>(
+      static_cast<const __half*>(hidden_f16), static_cast<const int*>(topk_ids_i32), H, k, expert_lo, expert_hi, plan,
+      E, static_cast<int*>(dest_row_i32), static_cast<int8_t*>(routed_q_i8), static_cast<float*>(routed_scale_f32));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+// ---- expert stage on rows that are already routed and quantised ------------
+// Workspace (bytes, each part 256-byte aligned): h f16 [P, I] | absmax u32 [P] | q2 i8 [P, I] | scale2 f32 [P]
+static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+extern "C" size_t mp_moe_expert_stage_workspace_bytes(int padded_rows, int I) {
+  if (padded_rows <= 0 || I <= 0) return 0;
+  const size_t P = (size_t)padded_rows;
+  return align256(P * I * 2) + align256(P * 4) + align256(P * I) + align256(P * 4);
+}
+
+extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
+                                   int padded_rows, int H, int I, int num_local_experts,
+                                   const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
+                                   const void* w2_scale_f32, void* d_out_f16, void* workspace,
+                                   size_t workspace_bytes, int* error_word, mp_stream_t stream) {
+  if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || !w2_q_i8 || !w2_scale_f32 ||
+      !d_out_f16 || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
+    return MP_ERR_INVALID_ARG;
+  if (padded_rows % kTileRows != 0 || H % 16 != 0 || I % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < mp_moe_expert_stage_workspace_bytes(padded_rows, I)) return MP_ERR_WORKSPACE;
+  if (!aligned(workspace, 256) || !aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16) || !aligned(w2_q_i8, 16) ||
+      !aligned(d_out_f16, 16))
+    return MP_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = num_local_experts;
+  const size_t P = (size_t)padded_rows;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  __half* h = reinterpret_cast<__half*>(ws);
+  unsigned int* absmax = reinterpret_cast<unsigned int*>(ws + align256(P * I * 2));
+  int8_t* q2 = reinterpret_cast<int8_t*>(ws + align256(P * I * 2) + align256(P * 4));
+  float* scale2 = reinterpret_cast<float*>(ws + align256(P * I * 2) + align256(P * 4) + align256(P * I));
+  const int* plan = static_cast<const int*>(plan_i32);
+  const int* num_tiles = plan + 3 * E + 1;
+  const int* tile_expert = plan + 3 * E + 2;
+  int rc = launch_moe_gemm1_swiglu(routed_q_i8, static_cast<const float*>(routed_scale_f32), w13_q_i8,
+                                   static_cast<const float*>(w13_scale_f32), padded_rows, H, I, E, num_tiles,
+                                   tile_expert, h, absmax, error_word, st);
+  if (rc != MP_OK) return rc;
+  moe_requant_kernel<<<padded_rows, 256, 0, st>>>(h, absmax, I, num_tiles, q2, scale2);
+  MP_LAUNCH_CHECK();
+  return launch_moe_gemm2(q2, scale2, w2_q_i8, static_cast<const float*>(w2_scale_f32), padded_rows, I, H, E,
+                          num_tiles, tile_expert, d_out_f16, error_word, st);
+}
+
+extern "C" int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,
+                              const void* topk_weights_f16, int T, int H, int k, void* out_f16, mp_stream_t stream) {
+  if (!d_f16 || !dest_row_i32 || !topk_ids_i32 || !topk_weights_f16 || !out_f16 || T <= 0 || H <= 0 || k <= 0)
+    return MP_ERR_INVALID_ARG;
+  if (H % 8 != 0 || k > 8) return MP_ERR_UNSUPPORTED;
+  if (!aligned(d_f16, 16) || !aligned(out_f16, 16)) return MP_ERR_ALIGNMENT;
+  moe_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(d_f16), static_cast<const int*>(dest_row_i32), static_cast<const int*>(topk_ids_i32),
+      static_cast<const __half*>(topk_weights_f16), T, H, k, static_cast<__half*>(out_f16));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}

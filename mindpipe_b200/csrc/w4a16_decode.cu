@@ -16,6 +16,8 @@
 // bumps a per-row-block counter, and the block that arrives last adds the
 // slices in a fixed order (deterministic), adds the bias, writes fp16 and
 // re-arms the counter for the next call.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace mp {
@@ -213,6 +215,183 @@ w4a16_decode_kernel(const DecodeParams p) {
   if (tid == 0) p.counters[blockIdx.x] = 0;  // ready for the next call
 }
 
+
+// ---------------------------------------------------------------------------
+// M <= 16: split K across a thread-block cluster and reduce through
+// distributed shared memory -- no scratch, no atomics, no second pass.
+//
+// A block owns 128 output rows (one warp per 32 rows) and 1/CK of K; the CK
+// blocks of a cluster cover all of K for the same rows.  Each warp streams
+// its weights in batches of up to four 128-column chunks (16 independent
+// 128-bit loads per lane in flight), the block stages the matching slice of
+// the activations once per batch (shared by its four warps), and after the
+// last batch every block parks its [M x 128] fp32 partial tile in its own
+// shared memory.  After a cluster barrier, block r of the cluster sums
+// columns [r*128/CK, (r+1)*128/CK) over all CK partial tiles in rank order
+// (deterministic), adds the bias and writes fp16.
+//
+// The weight loads of the first batch are issued before
+// griddepcontrol.wait, so that under programmatic dependent launch they
+// overlap the tail of the preceding kernel; everything that touches x, bias
+// or y comes after it.
+constexpr int kBatch = 4;   // chunks per batch
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <bool HALF>
+__global__ void __launch_bounds__(128)
+w4a16_decode_cluster_kernel(const DecodeParams p) {
+  namespace cg = cooperative_groups;
+  constexpr int HR = HALF ? 1 : 2;
+  constexpr int MROWS = HALF ? 8 : 16;
+  __shared__ __align__(16) uint4 xs[kBatch * 4 * HR * 32];
+  __shared__ __align__(16) float red[MROWS * 128];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ck = static_cast<int>(cluster.num_blocks());
+  const int crank = static_cast<int>(cluster.block_rank());
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 128 + warp * 32;
+  const int cs = min(p.chunks, crank * p.chunks_per_split);
+  const int ce = min(p.chunks, cs + p.chunks_per_split);
+  const int words_per_row = p.K >> 3;
+
+  float acc[kRowGroups][4];
+#pragma unroll
+  for (int r = 0; r < kRowGroups; ++r)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
+
+  uint4 q[kBatch][kRowGroups];
+  uint32_t szv[kBatch][kRowGroups];
+  auto load_batch = [&](int c_begin) {
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int chunk = c_begin + b;
+      const int kabs = chunk * kChunk + t * 32;
+      const int grp = kabs / p.group;
+#pragma unroll
+      for (int r = 0; r < kRowGroups; ++r) {
+        const int n = row0 + r * 8 + g;
+        if (chunk < ce && n < p.N) {
+          q[b][r] = ldg_stream_v4(p.packed + (size_t)n * words_per_row + (kabs >> 3));
+          szv[b][r] = __ldg(p.sz + (size_t)grp * p.N + n);
+        } else {
+          q[b][r] = make_uint4(0, 0, 0, 0);
+          szv[b][r] = 0;
+        }
+      }
+    }
+  };
+
+  load_batch(cs);
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  for (int c_begin = cs; c_begin < ce; c_begin += kBatch) {
+    const int nch = min(kBatch, ce - c_begin);
+    if (c_begin != cs) {
+      __syncthreads();            // the previous batch's fragments have been consumed
+      load_batch(c_begin);
+    }
+    // stage x[:, batch columns] in fragment order (see the kernel above)
+    const int units = nch * 16;
+    for (int idx = tid; idx < MROWS * units; idx += 128) {
+      const int m = idx / units, u = idx - m * units;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < p.M) {
+        const uint4 in = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)(c_begin * kChunk + u * 8));
+        v.x = prmt(in.x, in.z, 0x5410);
+        v.y = prmt(in.x, in.z, 0x7632);
+        v.z = prmt(in.y, in.w, 0x5410);
+        v.w = prmt(in.y, in.w, 0x7632);
+      }
+      const int kc = u >> 4, tt = (u >> 2) & 3, c = u & 3;
+      const int hr = (m >> 3) % HR, gg = m & 7;
+      xs[(((kc * 4 + c) * HR + hr) * 8 + gg) * 4 + tt] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (b < nch) {
+        ScaleZero sp[kRowGroups];
+#pragma unroll
+        for (int r = 0; r < kRowGroups; ++r) {
+          const __half2 h = *reinterpret_cast<const __half2*>(&szv[b][r]);
+          sp[r] = make_scale_zero(__low2half(h), __high2half(h));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int base = ((b * 4 + c) * HR) * 32 + lane;
+          const uint4 alo = xs[base];
+          const uint4 ahi = HALF ? make_uint4(0, 0, 0, 0) : xs[base + 32];
+#pragma unroll
+          for (int r = 0; r < kRowGroups; ++r) {
+            const uint32_t word = c == 0 ? q[b][r].x : c == 1 ? q[b][r].y : c == 2 ? q[b][r].z : q[b][r].w;
+            __half2 v[4];
+            dequant8(word, sp[r], v);
+            mma_m16n8k16(acc[r], alo.x, ahi.x, alo.y, ahi.y, h2_as_u32(v[0]), h2_as_u32(v[1]));
+            mma_m16n8k16(acc[r], alo.z, ahi.z, alo.w, ahi.w, h2_as_u32(v[2]), h2_as_u32(v[3]));
+          }
+        }
+      }
+    }
+  }
+
+  // park this block's partial tile: red[m][128 rows of the block]
+#pragma unroll
+  for (int r = 0; r < kRowGroups; ++r) {
+    float* base = red + g * 128 + warp * 32 + r * 8 + 2 * t;
+    *reinterpret_cast<float2*>(base) = make_float2(acc[r][0], acc[r][1]);
+    if (!HALF) *reinterpret_cast<float2*>(base + 8 * 128) = make_float2(acc[r][2], acc[r][3]);
+  }
+  cluster.sync();
+  const int cols = 128 / ck;                       // columns this block finishes
+  for (int e = tid; e < p.M * cols; e += 128) {
+    const int m = e / cols, c = crank * cols + (e - m * cols);
+    const int n = blockIdx.x * 128 + c;
+    float part[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) part[r] = r < ck ? cluster.map_shared_rank(red, r)[m * 128 + c] : 0.0f;
+    float s = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s += part[r];      // rank order: deterministic
+    if (n < p.N) {
+      if (p.bias) s += h2f(p.bias[n]);
+      p.y[(size_t)m * p.N + n] = f2h(s);
+    }
+  }
+  cluster.sync();                                  // nobody leaves while its tile is being read
+}
+
+static bool g_programmatic_launch = false;
+
+template <bool HALF>
+static int launch_decode_cluster(const DecodeParams& p, int row_blocks, int ck, cudaStream_t st) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(row_blocks, ck, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 1;
+  attrs[0].val.clusterDim.y = ck;
+  attrs[0].val.clusterDim.z = 1;
+  int n_attrs = 1;
+  if (g_programmatic_launch) {
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    n_attrs = 2;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n_attrs;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_decode_cluster_kernel<HALF>, p));
+  return MP_OK;
+}
+
 struct DecodePlan {
   int mb;        // 16-row token blocks
   bool half;     // M <= 8
@@ -256,8 +435,13 @@ constexpr size_t kCounterBytes = 16384;  // room for 4096 row blocks
 template <int MB, bool HALF, int WN, int STAGE>
 static int launch_decode(const DecodeParams& p, const DecodePlan& pl, cudaStream_t st) {
   auto kern = w4a16_decode_kernel<MB, HALF, WN, STAGE>;
-  if (pl.smem > 48 * 1024) {
+  // Static + dynamic shared memory can pass the 48 KB default together; opt in once per device.
+  static thread_local int configured_device = -1;
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  if (configured_device != device) {
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+    configured_device = device;
   }
   dim3 grid(pl.row_blocks, pl.k_split);
   kern<<<grid, WN * kWarpsK * 32, pl.smem, st>>>(p);
@@ -286,8 +470,6 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
   if (M > 64 || K % kChunk != 0 || group % 32 != 0 || K % group != 0 || N % 8 != 0) return MP_ERR_UNSUPPORTED;
   if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 2)) return MP_ERR_ALIGNMENT;
-  const DecodePlan pl = plan_decode(M, N, K, k_split);
-  if ((size_t)pl.row_blocks * sizeof(int) > kCounterBytes) return MP_ERR_UNSUPPORTED;
   DecodeParams p{};
   p.x = static_cast<const __half*>(x_f16);
   p.packed = static_cast<const uint32_t*>(packed_i32);
@@ -296,6 +478,19 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   p.y = static_cast<__half*>(y_f16);
   p.M = M; p.N = N; p.K = K; p.group = group;
   p.chunks = K / kChunk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M <= 16 && k_split <= 0) {
+    // cluster split-K: the largest portable cluster (<= 8) that leaves every block a chunk
+    int ck = 8;
+    while (ck > 1 && p.chunks < ck) ck >>= 1;
+    p.chunks_per_split = (p.chunks + ck - 1) / ck;
+    p.k_split = ck;
+    const int row_blocks = (N + 127) / 128;
+    return M <= 8 ? launch_decode_cluster<true>(p, row_blocks, ck, st)
+                  : launch_decode_cluster<false>(p, row_blocks, ck, st);
+  }
+  const DecodePlan pl = plan_decode(M, N, K, k_split);
+  if ((size_t)pl.row_blocks * sizeof(int) > kCounterBytes) return MP_ERR_UNSUPPORTED;
   p.chunks_per_split = pl.chunks_per_split;
   p.k_split = pl.k_split;
   if (pl.k_split > 1) {
@@ -305,7 +500,6 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
     p.counters = static_cast<int*>(workspace);
     p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kCounterBytes);
   }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (pl.mb == 1 && pl.half) return launch_decode<1, true, 1, 8>(p, pl, st);
   if (pl.mb == 1) return launch_decode<1, false, 2, 8>(p, pl, st);
   if (pl.mb == 2) return launch_decode<2, false, 2, 4>(p, pl, st);
@@ -317,4 +511,10 @@ extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32,
                                       void* workspace, size_t workspace_bytes, mp_stream_t stream) {
   return mp_w4a16_linear_decode_ex(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
                                    workspace_bytes, 0, stream);
+}
+
+extern "C" int mp_set_programmatic_launch(int enabled) {
+  const int prev = g_programmatic_launch ? 1 : 0;
+  g_programmatic_launch = enabled != 0;
+  return prev;
 }

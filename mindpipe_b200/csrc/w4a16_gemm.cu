@@ -1,0 +1,288 @@
+// W4A16 prefill GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T on the fp16 tensor
+// cores, with the int4 unpack + group dequant fused in as a producer stage.
+//
+// One persistent CTA per SM, 10 warps:
+//   warp 0      TMA producer for the activation tile x[128 x 64] (128-byte swizzle)
+//   warp 1      MMA issuer: tcgen05.mma kind::f16, M=128, N=256, K=16, fp32 in TMEM
+//   warps 2-5   epilogue: tcgen05.ld -> (+bias) -> fp16 -> global (TMEM double buffered)
+//   warps 6-9   dequant producers: stream the packed int4 words of the weight tile
+//               [256 rows x 64 columns] from global memory with 128-bit loads, expand
+//               them with dequant8 (exactly f16((u - z) * s), the reference's Wdq) and
+//               store them into shared memory in the canonical K-major 128-byte-swizzle
+//               layout the MMA reads -- the dequantised weights never exist in HBM.
+//
+// A stage is full when the TMA bytes have landed and all four dequant warps have
+// arrived (after a fence that makes their generic-proxy stores visible to the
+// tensor core).  Every wait is bounded (see tc.cuh).
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace mp {
+
+using namespace tc;
+
+namespace w4 {
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;            // fp16 elements of K per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;   // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;   // 32 KB
+constexpr int kTmemCols = 2 * kBN;
+constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + 256;
+constexpr int kThreads = 320;
+}  // namespace w4
+
+struct W4GemmParams {
+  const uint32_t* packed;   // [N, K/8]
+  const uint32_t* sz;       // [K/group, N] (scale, zero) f16 pairs
+  const __half* bias;
+  __half* y;
+  int M, N, K, group;
+  int m_tiles, n_tiles, k_blocks;
+  int* error_word;
+};
+
+__global__ void __launch_bounds__(w4::kThreads, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams p) {
+  using namespace w4;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + kStages * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + kStages * kBBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
+  const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1 + 4);      // TMA producer's expect_tx arrival + four dequant warps
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull0 + 8 * b, 1);
+      mbar_init(tempty0 + 8 * b, 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      prefetch_tensormap(&tmap_x);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * kBM;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t full = full0 + 8 * stage;
+          mbar_arrive_expect_tx(full, kABytes);
+          tma_load_2d(smem_u32(sA + stage * kABytes), &tmap_x, full, kb * kBK, m0);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, kBM, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kBN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * kABytes));
+          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * kBBytes));
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+            umma_f16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);   // +32 bytes of K per step
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull0 + 8 * buf);
+        if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+      }
+    }
+  } else if (warp < 6) {
+    const int quarter = warp & 3;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
+      tcgen05_fence_after();
+      const int row = m_tile * kBM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int n0 = n_tile * kBN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        uint32_t packed_out[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int n = n0 + c0 + 2 * j;
+          float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+          if (p.bias) {
+            if (n < p.N) v0 += h2f(p.bias[n]);
+            if (n + 1 < p.N) v1 += h2f(p.bias[n + 1]);
+          }
+          packed_out[j] = h2_as_u32(__floats2half2_rn(v0, v1));
+        }
+        if (row_ok) {
+          __half* dst = p.y + (size_t)row * p.N + n0 + c0;
+          if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4*>(dst)[v] =
+                  make_uint4(packed_out[4 * v], packed_out[4 * v + 1], packed_out[4 * v + 2], packed_out[4 * v + 3]);
+          } else {
+            for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) {
+              const uint32_t w = packed_out[j >> 1];
+              dst[j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+      if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+    }
+  } else {
+    // ---- dequant producers: thread dt owns weight-tile rows dt and dt + 128 ----
+    const int dt = threadIdx.x - 6 * 32;            // 0..127
+    const int words_per_row = p.K >> 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+      const int n0 = (tile / p.m_tiles) * kBN;
+      const int n_a = n0 + dt, n_b = n0 + dt + 128;
+      const bool ok_a = n_a < p.N, ok_b = n_b < p.N;
+      const uint32_t* row_a = p.packed + (size_t)(ok_a ? n_a : 0) * words_per_row;
+      const uint32_t* row_b = p.packed + (size_t)(ok_b ? n_b : 0) * words_per_row;
+      // software pipeline: the words of k-block kb+1 are in flight while kb is expanded
+      uint4 qa[2], qb[2];
+      auto fetch = [&](int kb, uint4 (&a)[2], uint4 (&b)[2]) {
+        const int w0 = kb * (kBK / 8);
+        const bool k_ok = (kb + 1) * kBK <= p.K;
+        a[0] = (ok_a && k_ok) ? ldg_stream_v4(row_a + w0) : make_uint4(0, 0, 0, 0);
+        a[1] = (ok_a && k_ok) ? ldg_stream_v4(row_a + w0 + 4) : make_uint4(0, 0, 0, 0);
+        b[0] = (ok_b && k_ok) ? ldg_stream_v4(row_b + w0) : make_uint4(0, 0, 0, 0);
+        b[1] = (ok_b && k_ok) ? ldg_stream_v4(row_b + w0 + 4) : make_uint4(0, 0, 0, 0);
+      };
+      fetch(0, qa, qb);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        uint4 ca[2] = {qa[0], qa[1]}, cb[2] = {qb[0], qb[1]};
+        if (kb + 1 < p.k_blocks) fetch(kb + 1, qa, qb);
+        const int grp = (kb * kBK) / p.group;
+        const uint32_t sza = ok_a ? __ldg(p.sz + (size_t)grp * p.N + n_a) : 0u;
+        const uint32_t szb = ok_b ? __ldg(p.sz + (size_t)grp * p.N + n_b) : 0u;
+        const __half2 ha = *reinterpret_cast<const __half2*>(&sza), hb = *reinterpret_cast<const __half2*>(&szb);
+        const ScaleZero spa = make_scale_zero(__low2half(ha), __high2half(ha));
+        const ScaleZero spb = make_scale_zero(__low2half(hb), __high2half(hb));
+        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag))) { ok = false; break; }
+        unsigned char* tile_b = sB + stage * kBBytes;
+#pragma unroll
+        for (int half_sel = 0; half_sel < 2; ++half_sel) {
+          const int r = dt + half_sel * 128;                        // row inside the weight tile
+          unsigned char* row_base = tile_b + (r >> 3) * 1024 + (r & 7) * 128;
+          const ScaleZero& sp = half_sel ? spb : spa;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {                             // 16-byte chunk j = columns 8j..8j+7
+            const uint4& src = half_sel ? cb[j >> 2] : ca[j >> 2];
+            const uint32_t word = (j & 3) == 0 ? src.x : (j & 3) == 1 ? src.y : (j & 3) == 2 ? src.z : src.w;
+            __half2 v[4];
+            dequant8(word, sp, v);
+            const uint32_t a = h2_as_u32(v[0]), b = h2_as_u32(v[1]), c = h2_as_u32(v[2]), d = h2_as_u32(v[3]);
+            uint4 o;                                                // natural column order for the MMA
+            o.x = prmt(a, b, 0x5410);
+            o.y = prmt(c, d, 0x5410);
+            o.z = prmt(a, b, 0x7632);
+            o.w = prmt(c, d, 0x7632);
+            *reinterpret_cast<uint4*>(row_base + ((j ^ (r & 7)) << 4)) = o;   // 128-byte swizzle
+          }
+        }
+        fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * stage);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.error_word) atomicExch(p.error_word, 2);
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, w4::kTmemCols);
+  }
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                       const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                       int* error_word, mp_stream_t stream) {
+  if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
+  if (K % w4::kBK != 0 || group % w4::kBK != 0 || K % group != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 16)) return MP_ERR_ALIGNMENT;
+  CUtensorMap tx;
+  int rc = encode_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)K, (uint64_t)M,
+                                (uint64_t)K * 2, w4::kBK, w4::kBM);
+  if (rc != MP_OK) return rc;
+  W4GemmParams p{};
+  p.packed = static_cast<const uint32_t*>(packed_i32);
+  p.sz = static_cast<const uint32_t*>(sz_f16x2);
+  p.bias = static_cast<const __half*>(bias_f16);
+  p.y = static_cast<__half*>(y_f16);
+  p.M = M; p.N = N; p.K = K; p.group = group;
+  p.m_tiles = (M + w4::kBM - 1) / w4::kBM;
+  p.n_tiles = (N + w4::kBN - 1) / w4::kBN;
+  p.k_blocks = K / w4::kBK;
+  p.error_word = error_word;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  if (configured_device != device) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w4::kSmem));
+    configured_device = device;
+  }
+  const long long total = (long long)p.m_tiles * p.n_tiles;
+  const int grid = (int)(total < kSmCount ? total : kSmCount);
+  w4a16_gemm_kernel<<<grid, w4::kThreads, w4::kSmem, static_cast<cudaStream_t>(stream)>>>(tx, p);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}

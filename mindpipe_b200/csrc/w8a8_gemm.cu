@@ -1,0 +1,419 @@
+// W8A8 GEMM on the 5th-generation tensor cores: int8 x int8 -> int32 in TMEM,
+// then a scale epilogue.  One persistent CTA per SM, warp specialised:
+//
+//   warp 0     TMA producer: 128-byte-swizzled [128 x 128 B] activation tile and
+//              [BN x 128 B] weight tile per stage, multi-stage mbarrier ring
+//   warp 1     MMA issuer: tcgen05.mma kind::i8 (M=128, N=BN, K=32), four per
+//              stage; tcgen05.commit releases the stage / publishes the tile
+//   warps 2-5  epilogue: tcgen05.ld the int32 accumulators (TMEM is double
+//              buffered, so this overlaps the next tile's main loop), apply
+//              acc * s_token[m] * s_channel[n] (+bias) and store
+//
+// Both operands are K-major: activations q[M,K] and weights w[N,K] (the
+// reference's [out, in] layout).  The same kernel serves three uses, chosen
+// by the epilogue: fp16 output (the npu_quant_matmul role,
+// acceleration/runtime_patches/vllm_ascend.patch:4007-4015), raw int32
+// accumulators (its output_dtype=int32 passthrough,
+// acceleration/runtime_patches/vllm.patch:756-760), and the MoE gate/up GEMM
+// with the SwiGLU epilogue.  In grouped (MoE) mode every 128-row tile of the
+// expert-sorted activations belongs to one expert, whose weight rows start at
+// expert * rows_per_expert.
+//
+// Every mbarrier wait is bounded; on a timeout the block records an error
+// word, lets its copies land, frees its TMEM and returns.
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace mp {
+
+using namespace tc;
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;      // int8 elements (= bytes) of K per stage
+constexpr int kUmmaK = 32;    // K of one kind::i8 instruction
+
+enum : int { EPI_F16 = 0, EPI_I32 = 1, EPI_SWIGLU = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  const int* m_tiles_dev;      // grouped: number of 128-row tiles in use (device side)
+  const int* tile_expert;      // grouped: expert of each 128-row tile
+  int b_rows_per_expert;       // grouped: weight rows per expert (2I for gate/up, H for down)
+  int up_row_offset;           // SwiGLU: rows between a gate row and its up row (I)
+  const float* a_scale;        // [M] per-token scales
+  const float* b_scale;        // per-channel scales, indexed like the weight rows
+  const __half* bias;          // [N] or null
+  void* out;                   // f16 [M,N] or int32 [M,N]
+  unsigned int* row_absmax;    // SwiGLU: per-row max |h| as float bits (atomicMax target)
+  int* error_word;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kBarBytes = 256;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(192, 1)
+w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + STAGES * Cfg::kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * Cfg::kBBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull0 + 8 * b, 1);
+      mbar_init(tempty0 + 8 * b, 4);     // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
+  const int total = m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      prefetch_tensormap(&tmap_a);
+      prefetch_tensormap(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+        const int m0 = m_tile * kBM;
+        const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t full = full0 + 8 * stage;
+          mbar_arrive_expect_tx(full, Cfg::kABytes + Cfg::kBBytes);
+          tma_load_2d(smem_u32(sA + stage * Cfg::kABytes), &tmap_a, full, kb * kBK, m0);
+          if (EPI == EPI_SWIGLU) {
+            // gate rows then the matching up rows: the tile's columns [0,128) and [128,256)
+            const uint32_t dst = smem_u32(sB + stage * Cfg::kBBytes);
+            tma_load_2d(dst, &tmap_b, full, kb * kBK, e_row0 + n_tile * 128);
+            tma_load_2d(dst + 128 * kBK, &tmap_b, full, kb * kBK, e_row0 + p.up_row_offset + n_tile * 128);
+          } else {
+            tma_load_2d(smem_u32(sB + stage * Cfg::kBBytes), &tmap_b, full, kb * kBK, e_row0 + n_tile * BN);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(kIdescDFormatS32 | kIdescABFormatS8, kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * Cfg::kABytes));
+          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * Cfg::kBBytes));
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in 16-byte address units
+            umma_i8(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+          }
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull0 + 8 * buf);
+        if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;               // TMEM lanes [32*quarter, +32) belong to this warp
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      // the whole warp takes the same way out: the TMEM loads below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
+      tcgen05_fence_after();
+      const int row = m_tile * kBM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sa = (EPI != EPI_I32 && row_ok) ? p.a_scale[row] : 0.0f;
+      const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      if (EPI == EPI_SWIGLU) {
+        const int n0 = n_tile * 128;
+        float hmax = 0.0f;
+        __half* out = static_cast<__half*>(p.out);
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c0, rg);
+          tmem_ld_32x32(taddr + 128 + c0, ru);
+          tmem_ld_wait();
+          __align__(16) __half hv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + c0 + j;
+            const bool n_ok = n < p.N;
+            const float sg = n_ok ? __ldg(p.b_scale + e_row0 + n) : 0.0f;
+            const float su = n_ok ? __ldg(p.b_scale + e_row0 + p.up_row_offset + n) : 0.0f;
+            // the reference rounds gate/up (F.linear output), silu(gate) and the product to fp16
+            const __half g16 = f2h(static_cast<float>(static_cast<int>(rg[j])) * sa * sg);
+            const __half u16 = f2h(static_cast<float>(static_cast<int>(ru[j])) * sa * su);
+            const float gf = h2f(g16);
+            const __half s16 = f2h(gf / (1.0f + expf(-gf)));
+            const __half h16 = hmul_t(s16, u16);
+            hv[j] = h16;
+            hmax = fmaxf(hmax, fabsf(h2f(h16)));
+          }
+          if (row_ok) {
+            __half* dst = out + (size_t)row * p.N + n0 + c0;
+            if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<uint4*>(hv)[v];
+            } else {
+              for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = hv[j];
+            }
+          }
+        }
+        if (row_ok) atomicMax(p.row_absmax + row, __float_as_uint(hmax));
+      } else {
+        const int n0 = n_tile * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          if (EPI == EPI_I32) {
+            if (row_ok) {
+              int* dst = static_cast<int*>(p.out) + (size_t)row * p.N + n0 + c0;
+              if (n0 + c0 + 32 <= p.N && (p.N % 4) == 0) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                  reinterpret_cast<uint4*>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+              } else {
+                for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = static_cast<int>(r[j]);
+              }
+            }
+          } else {
+            __align__(16) __half hv[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = n0 + c0 + j;
+              const bool n_ok = n < p.N;
+              const float sb = n_ok ? __ldg(p.b_scale + e_row0 + n) : 0.0f;
+              float v = static_cast<float>(static_cast<int>(r[j])) * sa * sb;
+              if (p.bias && n_ok) v += h2f(p.bias[n]);
+              hv[j] = f2h(v);
+            }
+            if (row_ok) {
+              __half* dst = static_cast<__half*>(p.out) + (size_t)row * p.N + n0 + c0;
+              if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<uint4*>(hv)[v];
+              } else {
+                for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = hv[j];
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+      if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.error_word) atomicExch(p.error_word, 1);
+    // give copies still in flight time to land before the shared memory goes away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+    g_last_cuda_error = static_cast<int>(e != cudaSuccess ? e : cudaErrorUnknown);
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
+                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return MP_ERR_CUDA;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = 100000 + static_cast<int>(r);
+    return MP_ERR_CUDA;
+  }
+  return MP_OK;
+}
+
+struct GemmCall {
+  const void* a; const void* b;
+  int M, N, K;
+  int a_rows;                 // rows of the activation buffer (>= M; padded in grouped mode)
+  int b_rows_total;           // rows of the weight buffer
+  const float* a_scale; const float* b_scale; const __half* bias;
+  void* out;
+  const int* m_tiles_dev; const int* tile_expert; int b_rows_per_expert; int up_row_offset;
+  unsigned int* row_absmax;
+  int* error_word;
+};
+
+template <int BN, int EPI>
+static int launch_gemm(const GemmCall& c, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap ta, tb;
+  int rc = encode_tensor_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, (uint64_t)c.K, (uint64_t)c.a_rows,
+                                (uint64_t)c.K, kBK, kBM);
+  if (rc != MP_OK) return rc;
+  rc = encode_tensor_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, (uint64_t)c.K, (uint64_t)c.b_rows_total,
+                            (uint64_t)c.K, kBK, EPI == EPI_SWIGLU ? 128 : BN);
+  if (rc != MP_OK) return rc;
+  GemmParams p{};
+  p.M = c.M; p.N = c.N; p.K = c.K;
+  p.m_tiles = (c.a_rows + kBM - 1) / kBM;
+  p.n_tiles = (c.N + (EPI == EPI_SWIGLU ? 128 : BN) - 1) / (EPI == EPI_SWIGLU ? 128 : BN);
+  p.k_blocks = (c.K + kBK - 1) / kBK;
+  p.m_tiles_dev = c.m_tiles_dev; p.tile_expert = c.tile_expert;
+  p.b_rows_per_expert = c.b_rows_per_expert; p.up_row_offset = c.up_row_offset;
+  p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
+  p.row_absmax = c.row_absmax; p.error_word = c.error_word;
+  auto kern = w8a8_gemm_kernel<BN, EPI>;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  if (configured_device != device) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmem));
+    configured_device = device;
+  }
+  const long long total = (long long)p.m_tiles * p.n_tiles;
+  const int grid = (int)(total < kSmCount ? total : kSmCount);
+  kern<<<grid, 192, Cfg::kSmem, st>>>(ta, tb, p);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+static int check_gemm_args(const void* a, const void* b, void* out, int M, int N, int K) {
+  if (!a || !b || !out || M <= 0 || N <= 0 || K <= 0) return MP_ERR_INVALID_ARG;
+  if (K % 16 != 0) return MP_ERR_UNSUPPORTED;       // TMA needs 16-byte row pitches
+  if (!aligned(a, 16) || !aligned(b, 16) || !aligned(out, 16)) return MP_ERR_ALIGNMENT;
+  return MP_OK;
+}
+
+// Grouped GEMMs of the MoE expert chain (declared in moe_api.cuh).
+int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
+                            int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
+                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st) {
+  GemmCall c{};
+  c.a = routed_q; c.b = w13_q; c.M = padded_rows; c.N = I; c.K = H; c.a_rows = padded_rows;
+  c.b_rows_total = E * 2 * I;
+  c.a_scale = routed_scale; c.b_scale = w13_scale; c.out = h_out;
+  c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = 2 * I; c.up_row_offset = I;
+  c.row_absmax = row_absmax; c.error_word = error_word;
+  MP_CUDA_TRY(cudaMemsetAsync(row_absmax, 0, sizeof(unsigned int) * (size_t)padded_rows, st));
+  return launch_gemm<256, EPI_SWIGLU>(c, st);
+}
+
+int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
+                     int I, int H, int E, const int* num_tiles_dev, const int* tile_expert, void* d_out,
+                     int* error_word, cudaStream_t st) {
+  GemmCall c{};
+  c.a = q2; c.b = w2_q; c.M = padded_rows; c.N = H; c.K = I; c.a_rows = padded_rows; c.b_rows_total = E * H;
+  c.a_scale = scale2; c.b_scale = w2_scale; c.out = d_out;
+  c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = H;
+  c.error_word = error_word;
+  return launch_gemm<256, EPI_F16>(c, st);
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const void* w_i8, const void* w_scale_f32,
+                            const void* bias_f16, void* y_f16, int M, int N, int K, int* error_word,
+                            mp_stream_t stream) {
+  int rc = check_gemm_args(qx_i8, w_i8, y_f16, M, N, K);
+  if (rc != MP_OK) return rc;
+  if (!x_scale_f32 || !w_scale_f32) return MP_ERR_INVALID_ARG;
+  GemmCall c{};
+  c.a = qx_i8; c.b = w_i8; c.M = M; c.N = N; c.K = K; c.a_rows = M; c.b_rows_total = N;
+  c.a_scale = static_cast<const float*>(x_scale_f32); c.b_scale = static_cast<const float*>(w_scale_f32);
+  c.bias = static_cast<const __half*>(bias_f16); c.out = y_f16; c.error_word = error_word;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_F16>(c, st);
+  return launch_gemm<256, EPI_F16>(c, st);
+}
+
+extern "C" int mp_w8a8_gemm_i32(const void* qx_i8, const void* w_i8, void* acc_i32, int M, int N, int K,
+                                int* error_word, mp_stream_t stream) {
+  int rc = check_gemm_args(qx_i8, w_i8, acc_i32, M, N, K);
+  if (rc != MP_OK) return rc;
+  GemmCall c{};
+  c.a = qx_i8; c.b = w_i8; c.M = M; c.N = N; c.K = K; c.a_rows = M; c.b_rows_total = N;
+  c.out = acc_i32; c.error_word = error_word;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_I32>(c, st);
+  return launch_gemm<256, EPI_I32>(c, st);
+}

@@ -103,3 +103,211 @@ class VllmPackedInt4Linear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"w_bit=4, group_size={self.group_size}, asymmetric={self.weight_zero_point is not None}")
+
+
+class SmoothQuantLinear(nn.Module):
+    """Real-int twin of the reference's ``SmoothQuantLinear``
+    (algorithm/quantization/ptq/smoothquant/source/smoothquant/fake_quant.py:38-121).
+
+    Same constructor, ``from_float`` and ``forward(x)``; where the reference
+    keeps a fake-quantised fp16 ``weight`` and multiplies in fp16, this module
+    keeps the int8 codes and per-channel scales (buffer names of the W8A8
+    exporter, scripts/repro/export_fp16_to_ascend_w8a8_dynamic_probe.py:175-195:
+    ``weight``, ``weight_scale``, ``weight_offset``) and runs per-token int8
+    activation quantisation followed by the int8 tensor-core GEMM with an
+    int32-accumulate, scale epilogue.  The codes and scales are exactly those
+    of the reference's fp16 arithmetic (fake_quant.py:10-31).
+    """
+
+    def __init__(self, in_features, out_features, bias=True, weight_bits=8, activation_bits=8,
+                 act_quant="per_token", quantize_output=False, dtype=torch.float16):
+        super().__init__()
+        if act_quant != "per_token":
+            raise ValueError(f"Invalid act_quant: {act_quant}")
+        if int(weight_bits) != 8 or int(activation_bits) != 8:
+            raise ValueError("the integer kernels implement weight_bits=8, activation_bits=8")
+        if dtype != torch.float16:
+            raise ValueError("the integer kernels take fp16 activations")
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight_bits = int(weight_bits)
+        self.activation_bits = int(activation_bits)
+        self.register_buffer("weight", torch.zeros((out_features, in_features), dtype=torch.int8))
+        self.register_buffer("weight_scale", torch.zeros((out_features, 1), dtype=dtype))
+        self.register_buffer("weight_offset", torch.zeros((out_features, 1), dtype=dtype))
+        if bias:
+            self.register_buffer("bias", torch.zeros((out_features,), dtype=dtype))
+        else:
+            self.register_buffer("bias", None)
+        self.weight_quant_name = "per_channel"
+        self.act_quant_name = act_quant
+        self.quantize_output = bool(quantize_output)
+        self.output_quant_name = act_quant if quantize_output else "none"
+        self._weight_scale_fp32 = None
+
+    @staticmethod
+    @torch.no_grad()
+    def from_float(module, weight_bits=8, activation_bits=8, act_quant="per_token", quantize_output=False):
+        assert isinstance(module, nn.Linear)
+        new = SmoothQuantLinear(module.in_features, module.out_features, module.bias is not None,
+                                weight_bits=weight_bits, activation_bits=activation_bits, act_quant=act_quant,
+                                quantize_output=quantize_output, dtype=module.weight.dtype)
+        new = new.to(device=module.weight.device)
+        q, s, _ = ops.act_quant_per_token(module.weight.detach().contiguous())   # per output channel
+        new.weight = q
+        new.weight_scale = s.to(module.weight.dtype).reshape(-1, 1)
+        new.weight_offset = torch.zeros_like(new.weight_scale)
+        if module.bias is not None:
+            new.bias = module.bias.detach().clone()
+        return new
+
+    def process_weights_after_loading(self) -> None:
+        """fp32 copy of the per-channel scales, as the runtime method keeps
+        (acceleration/runtime_patches/vllm_ascend.patch:4029-4031)."""
+        self._weight_scale_fp32 = self.weight_scale.detach().flatten().to(torch.float32).contiguous()
+
+    def _apply(self, fn, *args, **kwargs):
+        self._weight_scale_fp32 = None
+        return super()._apply(fn, *args, **kwargs)
+
+    def dequantize(self) -> torch.Tensor:
+        """The reference's fake-quantised fp16 weight: ``f16(code * scale)``."""
+        return (self.weight.to(torch.float16) * self.weight_scale).to(torch.float16)
+
+    @torch.no_grad()
+    def forward(self, x):
+        """``x`` is an fp16 tensor, or a ``(int8 codes, per-token scale)`` pair produced upstream
+        (the tuple input of AscendW8A8DynamicLinearMethod.apply, vllm_ascend.patch:3945-3962)."""
+        if self._weight_scale_fp32 is None:
+            self.process_weights_after_loading()
+        if isinstance(x, tuple):
+            q, s = x
+            lead = q.shape[:-1]
+            q2 = q.reshape(-1, q.shape[-1])
+            s2 = s.reshape(-1).to(torch.float32)
+        else:
+            lead = x.shape[:-1]
+            x2 = x.reshape(-1, x.shape[-1])
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            q2, s2, _ = ops.act_quant_per_token(x2)
+        y = ops.w8a8_gemm(q2.contiguous(), s2.contiguous(), self.weight, self._weight_scale_fp32, self.bias)
+        if self.quantize_output:
+            _, _, y = ops.act_quant_per_token(y, want_codes=False, want_fake=True)
+        return y.reshape(*lead, self.out_features)
+
+    def __repr__(self):
+        return (f"SmoothQuantLinear({self.in_features}, {self.out_features}, bias={self.bias is not None}, "
+                f"weight_bits={self.weight_bits}, activation_bits={self.activation_bits}, "
+                f"weight_quant={self.weight_quant_name}, act_quant={self.act_quant_name}, "
+                f"output_quant={self.output_quant_name}, int8=True)")
+
+
+class W8A8DynamicLinearMethod:
+    """Linear-method style entry, mirroring ``AscendW8A8DynamicLinearMethod``
+    (acceleration/runtime_patches/vllm_ascend.patch:3933-4033): ``apply(layer, x, bias, tp_rank)``
+    where ``layer`` carries ``weight`` int8 ``[N,K]``, ``weight_scale`` and an optional
+    ``_ascend_quant_config`` dict with ``output_dtype``, ``pertoken_scale`` and ``return_scale``."""
+
+    def process_weights_after_loading(self, layer) -> None:
+        layer.weight_scale.data = layer.weight_scale.data.flatten()
+        layer.weight_scale_fp32 = layer.weight_scale.data.to(torch.float32).contiguous()
+        if hasattr(layer, "weight_offset"):
+            layer.weight_offset.data = layer.weight_offset.data.flatten()
+
+    @torch.no_grad()
+    def apply(self, layer, x, bias=None, tp_rank=0):
+        config = getattr(layer, "_ascend_quant_config", {})
+        output_shape = None
+        if not isinstance(x, tuple):
+            output_dtype = config.get("output_dtype", x.dtype)
+            if x.dim() > 2:
+                output_shape = x.shape[:-1]
+                x = x.reshape(-1, x.shape[-1])
+            quantized_x, dynamic_scale, _ = ops.act_quant_per_token(x.contiguous())
+        else:
+            output_dtype = config.get("output_dtype", getattr(layer, "params_dtype", torch.float16))
+            quantized_x, dynamic_scale = x
+        if not config.get("pertoken_scale", True):
+            raise NotImplementedError("pertoken_scale=False (static activation scale) is not part of this path")
+        if not hasattr(layer, "weight_scale_fp32"):
+            self.process_weights_after_loading(layer)
+        scale = dynamic_scale.flatten().to(torch.float32).contiguous()
+        if output_dtype == torch.int32:
+            output = ops.w8a8_gemm_i32(quantized_x.contiguous(), layer.weight)
+        elif output_dtype == torch.float16:
+            output = ops.w8a8_gemm(quantized_x.contiguous(), scale, layer.weight, layer.weight_scale_fp32, bias)
+        else:
+            raise NotImplementedError(f"output_dtype {output_dtype} (fp16 and int32 are implemented)")
+        if output_shape is not None:
+            output = output.reshape(*output_shape, output.shape[-1])
+            dynamic_scale = dynamic_scale.reshape(*output_shape)
+        return (output, dynamic_scale) if config.get("return_scale", False) else output
+
+
+class SmoothQuantPackedMoeExperts(nn.Module):
+    """Real-int twin of the reference's ``SmoothQuantPackedMoeExperts``
+    (fake_quant.py:124-198): same constructor (``gate_up_proj[E,2I,H]``, ``down_proj[E,H,I]``,
+    ``act_fn``), ``from_float`` and ``forward(hidden_states, top_k_index, top_k_weights)``.
+
+    The expert weights are stored as int8 codes with per-(expert, output row) scales; the
+    forward is routing + gather + per-token quant, grouped int8 GEMM1 with SwiGLU, re-quant,
+    grouped int8 GEMM2 and the weighted scatter-add.  ``expert_range`` restricts the module
+    to the experts one GPU owns (expert parallelism): rows routed elsewhere contribute zero.
+    """
+
+    def __init__(self, gate_up_proj, down_proj, act_fn=None, *, weight_bits=8, activation_bits=8,
+                 expert_range: tuple[int, int] | None = None, num_experts: int | None = None):
+        super().__init__()
+        if int(weight_bits) != 8 or int(activation_bits) != 8:
+            raise ValueError("the integer kernels implement weight_bits=8, activation_bits=8")
+        if act_fn is not None and not isinstance(act_fn, nn.SiLU) and getattr(act_fn, "__name__", "") != "silu":
+            raise ValueError("the fused epilogue implements SiLU (SwiGLU) experts")
+        local = int(gate_up_proj.shape[0])
+        self.expert_range = (0, local) if expert_range is None else (int(expert_range[0]), int(expert_range[1]))
+        if self.expert_range[1] - self.expert_range[0] != local:
+            raise ValueError("expert_range does not match the number of expert weight slabs")
+        self.num_experts = int(num_experts) if num_experts is not None else self.expert_range[1]
+        self.hidden_dim = int(gate_up_proj.shape[2])
+        self.intermediate_dim = int(down_proj.shape[2])
+        self.weight_bits = int(weight_bits)
+        self.activation_bits = int(activation_bits)
+        self.act_fn = act_fn
+        gq, gs = self._quantize(gate_up_proj)
+        dq, ds = self._quantize(down_proj)
+        self.register_buffer("gate_up_proj", gq)
+        self.register_buffer("gate_up_proj_scale", gs)
+        self.register_buffer("down_proj", dq)
+        self.register_buffer("down_proj_scale", ds)
+
+    @staticmethod
+    @torch.no_grad()
+    def _quantize(w):
+        if w.dtype == torch.int8:
+            raise TypeError("pass float expert weights; they are quantised here")
+        q, s, _ = ops.act_quant_per_token(w.detach().to(torch.float16).contiguous())   # per (expert, out row)
+        return q, s
+
+    @staticmethod
+    def from_float(module, weight_bits=8, activation_bits=8, expert_range=None, num_experts=None):
+        return SmoothQuantPackedMoeExperts(module.gate_up_proj.detach(), module.down_proj.detach(), module.act_fn,
+                                           weight_bits=weight_bits, activation_bits=activation_bits,
+                                           expert_range=expert_range, num_experts=num_experts)
+
+    @torch.no_grad()
+    def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor):
+        shape = hidden_states.shape
+        hs = hidden_states.reshape(-1, shape[-1]).contiguous()
+        ids = top_k_index.reshape(hs.shape[0], -1).to(torch.int32).contiguous()
+        w = top_k_weights.reshape(hs.shape[0], -1).to(torch.float16).contiguous()
+        lo, hi = self.expert_range
+        routing = ops.moe_route_gather_quant(hs, ids, lo, hi)
+        d = ops.moe_expert_stage(routing.routed_q, routing.routed_scale, routing.plan, hi - lo,
+                                 self.gate_up_proj, self.gate_up_proj_scale, self.down_proj, self.down_proj_scale)
+        out = ops.moe_combine(d, routing.dest_row, ids, w, hs.shape[0])
+        return out.reshape(shape)
+
+    def __repr__(self):
+        return (f"SmoothQuantPackedMoeExperts(num_experts={self.num_experts}, hidden_dim={self.hidden_dim}, "
+                f"intermediate_dim={self.intermediate_dim}, weight_bits={self.weight_bits}, "
+                f"activation_bits={self.activation_bits}, local_experts={self.expert_range})")

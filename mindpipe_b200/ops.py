@@ -17,6 +17,7 @@ from . import _lib
 
 _ws_lock = threading.Lock()
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_err_words: dict[int, torch.Tensor] = {}
 
 
 def _stream() -> int:
@@ -147,14 +148,39 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
     return y
 
 
+def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None):
+    """``y = x @ dequant(W)^T (+bias)`` on the fp16 tensor cores with the dequant fused in."""
+    x2 = _req(x, "x", torch.float16, 2)
+    p = _req(weight_packed, "weight_packed", torch.int32, 2)
+    sz = _req(scale_zero, "scale_zero", torch.float16, 3)
+    b = None if bias is None else _req(bias, "bias", torch.float16, 1)
+    m, k = x2.shape
+    n = p.shape[0]
+    groups = sz.shape[0]
+    if p.shape[1] * 8 != k or sz.shape[1] != n or k % groups:
+        raise ValueError(f"shape mismatch: x{tuple(x2.shape)} packed{tuple(p.shape)} sz{tuple(sz.shape)}")
+    y = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    if m == 0:
+        return y
+    st = _lib.load().mp_w4a16_linear_prefill(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
+                                             m, n, k, k // groups, _error_word(x2.device).data_ptr(), _stream())
+    _lib.check(st, "w4a16_linear_prefill", M=m, N=n, K=k, group=k // groups)
+    return y
+
+
 def w4a16_linear(x, weight_packed, scale_zero, bias=None):
     """W4A16 linear for any number of rows.
 
-    Rows are processed in slabs of at most 64 by the weight-streaming kernel.
+    Up to 64 rows go to the weight-streaming decode kernel, more to the
+    tensor-core prefill kernel; shapes the prefill kernel does not take
+    (K or the group size not a multiple of 64) are processed in 64-row slabs.
     """
-    m = x.shape[0]
+    m, k = x.shape
     if m <= 64:
         return w4a16_linear_decode(x, weight_packed, scale_zero, bias)
+    group = k // scale_zero.shape[0]
+    if k % 64 == 0 and group % 64 == 0:
+        return w4a16_linear_prefill(x, weight_packed, scale_zero, bias)
     outs = [w4a16_linear_decode(x[i:i + 64], weight_packed, scale_zero, bias) for i in range(0, m, 64)]
     return torch.cat(outs, dim=0)
 
@@ -176,3 +202,156 @@ def act_quant_per_token(x, *, want_codes: bool = True, want_fake: bool = False):
     st = _lib.load().mp_act_quant_per_token(xt.data_ptr(), m, k, _ptr(q), _ptr(s), _ptr(f), _stream())
     _lib.check(st, "act_quant_per_token", M=m, K=k)
     return q, s, f
+
+
+def _error_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the tensor-core kernels set when a bounded wait gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _err_words.get(idx)
+    if w is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("first use of a tensor-core op must happen outside CUDA graph capture")
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _err_words[idx] = w
+    return w
+
+
+def check_device_errors(device=None) -> None:
+    """Synchronise and raise if any kernel reported a device-side wait that gave up."""
+    torch.cuda.synchronize(device)
+    for idx, w in _err_words.items():
+        if int(w.item()) != 0:
+            w.zero_()
+            raise _lib.MindPipeKernelError(f"device {idx}: a bounded wait inside a tensor-core kernel timed out")
+
+
+def w8a8_gemm(qx, x_scale, weight_i8, weight_scale, bias=None):
+    """``f16((qx @ w^T) * x_scale[:,None] * w_scale[None,:] (+bias))`` with int32 accumulation."""
+    a = _req(qx, "qx", torch.int8, 2)
+    b = _req(weight_i8, "weight", torch.int8, 2)
+    sa = _req(x_scale, "x_scale", torch.float32, 1)
+    sb = _req(weight_scale, "weight_scale", torch.float32, 1)
+    bi = None if bias is None else _req(bias, "bias", torch.float16, 1)
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k or sa.numel() != m or sb.numel() != n:
+        raise ValueError(f"shape mismatch: qx{tuple(a.shape)} w{tuple(b.shape)} sx{tuple(sa.shape)} sw{tuple(sb.shape)}")
+    y = torch.empty((m, n), dtype=torch.float16, device=a.device)
+    if m == 0:
+        return y
+    st = _lib.load().mp_w8a8_gemm(a.data_ptr(), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), _ptr(bi), y.data_ptr(),
+                                  m, n, k, _error_word(a.device).data_ptr(), _stream())
+    _lib.check(st, "w8a8_gemm", M=m, N=n, K=k)
+    return y
+
+
+def w8a8_gemm_i32(qx, weight_i8):
+    """Raw int32 accumulators ``qx @ w^T``."""
+    a = _req(qx, "qx", torch.int8, 2)
+    b = _req(weight_i8, "weight", torch.int8, 2)
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k:
+        raise ValueError(f"shape mismatch: qx{tuple(a.shape)} w{tuple(b.shape)}")
+    acc = torch.empty((m, n), dtype=torch.int32, device=a.device)
+    if m == 0:
+        return acc
+    st = _lib.load().mp_w8a8_gemm_i32(a.data_ptr(), b.data_ptr(), acc.data_ptr(), m, n, k,
+                                      _error_word(a.device).data_ptr(), _stream())
+    _lib.check(st, "w8a8_gemm_i32", M=m, N=n, K=k)
+    return acc
+
+
+# -------------------------------------------------------------------- MoE
+def moe_router_topk(logits, top_k: int = 2):
+    """softmax(fp32) -> top-k -> renormalise -> fp16.  Returns ``(index int32[T,k], weights f16[T,k])``."""
+    lg = _req(logits, "logits", torch.float32, 2)
+    t, e = lg.shape
+    idx = torch.empty((t, top_k), dtype=torch.int32, device=lg.device)
+    w = torch.empty((t, top_k), dtype=torch.float16, device=lg.device)
+    if t:
+        st = _lib.load().mp_moe_router_topk(lg.data_ptr(), t, e, top_k, idx.data_ptr(), w.data_ptr(), _stream())
+        _lib.check(st, "moe_router_topk", T=t, E=e, k=top_k)
+    return idx, w
+
+
+class MoeRouting:
+    """Device-side result of routing + gather + quant for the experts one GPU owns."""
+
+    __slots__ = ("plan", "dest_row", "routed_q", "routed_scale", "padded_rows", "num_local_experts")
+
+    def __init__(self, plan, dest_row, routed_q, routed_scale, padded_rows, num_local_experts):
+        self.plan, self.dest_row, self.routed_q, self.routed_scale = plan, dest_row, routed_q, routed_scale
+        self.padded_rows, self.num_local_experts = padded_rows, num_local_experts
+
+    @property
+    def counts(self):
+        return self.plan[: self.num_local_experts]
+
+    @property
+    def segment_offsets(self):
+        e = self.num_local_experts
+        return self.plan[2 * e: 3 * e + 1]
+
+
+def moe_route_gather_quant(hidden, top_k_index, expert_lo: int, expert_hi: int) -> MoeRouting:
+    """Sort the routed rows of experts ``[expert_lo, expert_hi)`` by expert and quantise them per token."""
+    hs = _req(hidden, "hidden_states", torch.float16, 2)
+    ids = _req(top_k_index, "top_k_index", torch.int32, 2)
+    t, h = hs.shape
+    k = ids.shape[1]
+    if ids.shape[0] != t:
+        raise ValueError("top_k_index and hidden_states disagree on the number of tokens")
+    e = expert_hi - expert_lo
+    lib = _lib.load()
+    padded = lib.mp_moe_padded_rows(e, t * k)
+    plan = torch.empty(lib.mp_moe_plan_ints(e, t * k), dtype=torch.int32, device=hs.device)
+    dest = torch.empty(t * k, dtype=torch.int32, device=hs.device)
+    rq = torch.empty((padded, h), dtype=torch.int8, device=hs.device)
+    rs = torch.empty(padded, dtype=torch.float32, device=hs.device)
+    st = lib.mp_moe_route_gather_quant(hs.data_ptr(), ids.data_ptr(), t, h, k, expert_lo, expert_hi, plan.data_ptr(),
+                                       dest.data_ptr(), rq.data_ptr(), rs.data_ptr(), _stream())
+    _lib.check(st, "moe_route_gather_quant", T=t, H=h, k=k, experts=(expert_lo, expert_hi))
+    return MoeRouting(plan, dest, rq, rs, padded, e)
+
+
+def moe_expert_stage(routed_q, routed_scale, plan, num_local_experts: int, w13_q, w13_scale, w2_q, w2_scale):
+    """Grouped GEMM1 + SwiGLU + re-quant + grouped GEMM2 on expert-sorted int8 rows -> f16 ``[padded_rows, H]``."""
+    rq = _req(routed_q, "routed_q", torch.int8, 2)
+    rs = _req(routed_scale, "routed_scale", torch.float32, 1)
+    pl = _req(plan, "plan", torch.int32, 1)
+    w13 = _req(w13_q, "w13", torch.int8, 3)
+    s13 = _req(w13_scale, "w13_scale", torch.float32, 2)
+    w2 = _req(w2_q, "w2", torch.int8, 3)
+    s2 = _req(w2_scale, "w2_scale", torch.float32, 2)
+    padded, h = rq.shape
+    e, two_i, h2 = w13.shape
+    i = two_i // 2
+    if e != num_local_experts or h2 != h or tuple(w2.shape) != (e, h, i) or tuple(s13.shape) != (e, two_i) or \
+            tuple(s2.shape) != (e, h) or rs.numel() != padded:
+        raise ValueError("expert weight / routed buffer shapes are inconsistent")
+    lib = _lib.load()
+    nbytes = lib.mp_moe_expert_stage_workspace_bytes(padded, i)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=rq.device)
+    d = torch.empty((padded, h), dtype=torch.float16, device=rq.device)
+    st = lib.mp_moe_expert_stage(rq.data_ptr(), rs.data_ptr(), pl.data_ptr(), padded, h, i, e, w13.data_ptr(),
+                                 s13.data_ptr(), w2.data_ptr(), s2.data_ptr(), d.data_ptr(), ws.data_ptr(), nbytes,
+                                 _error_word(rq.device).data_ptr(), _stream())
+    _lib.check(st, "moe_expert_stage", padded_rows=padded, H=h, I=i, E=e)
+    return d
+
+
+def moe_combine(d, dest_row, top_k_index, top_k_weights, num_tokens: int):
+    """``out[t] = sum_j f16(d[dest(t,j)] * w[t,j])`` (fp16 adds, experts ascending)."""
+    dd = _req(d, "d", torch.float16, 2)
+    dr = _req(dest_row, "dest_row", torch.int32, 1)
+    ids = _req(top_k_index, "top_k_index", torch.int32, 2)
+    w = _req(top_k_weights, "top_k_weights", torch.float16, 2)
+    k = ids.shape[1]
+    h = dd.shape[1]
+    out = torch.empty((num_tokens, h), dtype=torch.float16, device=dd.device)
+    if num_tokens:
+        st = _lib.load().mp_moe_combine(dd.data_ptr(), dr.data_ptr(), ids.data_ptr(), w.data_ptr(), num_tokens, h, k,
+                                        out.data_ptr(), _stream())
+        _lib.check(st, "moe_combine", T=num_tokens, H=h, k=k)
+    return out

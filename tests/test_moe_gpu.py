@@ -1,0 +1,112 @@
+"""GPU parity of the W8A8 MoE expert path against the CPU oracle (through the C ABI).
+
+Bit-exact: router indices, routed int8 rows and their scales, routing plan.
+fp16 outputs: relative Frobenius error <= 1e-2 against the reference's
+``SmoothQuantPackedMoeExperts.forward`` (golden fixture / oracle).
+"""
+import numpy as np
+import pytest
+import torch
+
+from mindpipe_b200 import synth
+from oracle import pseudo_quant as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_router_matches_reference(golden):
+    from mindpipe_b200 import ops
+    g = golden("moe_small.npz")
+    idx, w = ops.moe_router_topk(dev(g["logits"]), 2)
+    assert np.array_equal(idx.cpu().numpy(), g["top_k_index"].astype(np.int32))
+    assert np.allclose(w.float().cpu().numpy(), g["top_k_weights"].astype(np.float32), atol=1e-3)
+    lg = synth.router_logits(8192, 8, seed=0).numpy()            # config 4 router input
+    idx, w = ops.moe_router_topk(dev(lg), 2)
+    oi, ow = O.router_top2(lg, 2)
+    assert np.array_equal(idx.cpu().numpy(), oi.astype(np.int32))
+    assert np.allclose(w.float().cpu().numpy(), ow.astype(np.float32), atol=1e-3)
+
+
+@pytest.mark.parametrize("lo,hi", [(0, 8), (2, 5), (7, 8)])
+def test_route_gather_quant_bit_exact(lo, hi):
+    from mindpipe_b200 import ops
+    t, h, e, k = 777, 256, 8, 2
+    hs = synth.outlier_activation(t, h, seed=3).numpy()
+    ids, _ = O.router_top2(synth.router_logits(t, e, seed=3).numpy(), k)
+    ids = ids.astype(np.int32)
+    r = ops.moe_route_gather_quant(dev(hs), dev(ids), lo, hi)
+    torch.cuda.synchronize()
+    counts = r.counts.cpu().numpy()
+    seg = r.segment_offsets.cpu().numpy()
+    dest = r.dest_row.cpu().numpy().reshape(t, k)
+    assert np.array_equal(counts, np.bincount(ids.ravel(), minlength=e)[lo:hi])
+    assert (seg % 128 == 0).all() and seg[0] == 0
+    assert np.array_equal(np.diff(seg), (counts + 127) // 128 * 128)
+    _, codes, sc = O.absmax_quant_last_dim(hs)
+    rq, rs = r.routed_q.cpu().numpy(), r.routed_scale.cpu().numpy()
+    local = (ids >= lo) & (ids < hi)
+    assert (dest[~local] == -1).all()
+    rows = dest[local]
+    assert len(np.unique(rows)) == rows.size                       # a permutation: no row claimed twice
+    ex = ids[local] - lo
+    assert ((rows >= seg[ex]) & (rows < seg[ex] + counts[ex])).all()
+    tok = np.nonzero(local)[0]
+    assert np.array_equal(rq[rows], codes[tok])                     # int8 activations bit-exact
+    assert np.array_equal(rs[rows], sc[tok, 0].astype(np.float32))
+    pad = np.ones(r.padded_rows, dtype=bool)
+    pad[rows] = False
+    assert (rs[pad] == 0).all()                                     # padding rows are neutralised
+
+
+def _module_case(e, h, i, t, seed, expert_range=None):
+    from mindpipe_b200 import ops
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+    shape = synth.MoeShape(num_experts=e, hidden=h, ffn=i, top_k=2, tokens=t)
+    gu, dn = synth.moe_weights(shape, seed=seed, std=0.05)
+    hs = synth.normal_activation(t, h, seed=seed, index=11)
+    idx, w = ops.moe_router_topk(synth.router_logits(t, e, seed=seed).cuda(), 2)
+    lo, hi = (0, e) if expert_range is None else expert_range
+    mod = SmoothQuantPackedMoeExperts(gu[lo:hi].cuda(), dn[lo:hi].cuda(), torch.nn.SiLU(),
+                                      expert_range=(lo, hi), num_experts=e)
+    out = mod(hs.cuda(), idx, w)
+    ops.check_device_errors()
+    return gu.numpy(), dn.numpy(), hs.numpy(), idx.cpu().numpy(), w.cpu().numpy(), out.cpu().numpy()
+
+
+def test_moe_module_matches_reference_golden(golden):
+    from mindpipe_b200 import ops
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+    g = golden("moe_small.npz")
+    src = type("Src", (), {})()
+    src.gate_up_proj, src.down_proj, src.act_fn = dev(g["gate_up"]), dev(g["down"]), torch.nn.SiLU()
+    mod = SmoothQuantPackedMoeExperts.from_float(src)
+    assert np.array_equal(mod.gate_up_proj.cpu().numpy(), O.absmax_quant_last_dim(g["gate_up"])[1])
+    out = mod(dev(g["hidden"]), dev(g["top_k_index"]), dev(g["top_k_weights"]))
+    ops.check_device_errors()
+    assert O.rel_frobenius(out.cpu().numpy(), g["out"]) <= TOL      # expert 3 is never hit in this fixture
+
+
+@pytest.mark.parametrize("e,h,i,t", [(8, 512, 1024, 512), (4, 256, 384, 1000), (8, 128, 256, 3)])
+def test_moe_module_vs_oracle(e, h, i, t):
+    gu, dn, hs, idx, w, out = _module_case(e, h, i, t, seed=e + t)
+    guf, _, _ = O.absmax_quant_last_dim(gu)
+    dnf, _, _ = O.absmax_quant_last_dim(dn)
+    ref = O.moe_experts_forward(hs, idx.astype(np.int64), w, guf, dnf)
+    assert O.rel_frobenius(out, ref) <= TOL
+
+
+def test_moe_expert_ranges_sum_to_full_output():
+    """Expert parallelism: the outputs of disjoint expert ranges add up (in fp16) to the full output."""
+    full = _module_case(8, 256, 512, 600, seed=9)[-1]
+    parts = [_module_case(8, 256, 512, 600, seed=9, expert_range=r)[-1] for r in ((0, 4), (4, 8))]
+    assert np.array_equal((parts[0] + parts[1]).astype(np.float16), full)
+    quarters = [_module_case(8, 256, 512, 600, seed=9, expert_range=(j, j + 2))[-1] for j in (0, 2, 4, 6)]
+    acc = np.zeros_like(full, dtype=np.float32)
+    for q in quarters:                                               # each token has two non-zero addends
+        acc += q.astype(np.float32)
+    assert np.array_equal(acc.astype(np.float16), full)

@@ -137,7 +137,9 @@ def test_decode_linearity_property_full_size():
     x = synth.normal_activation(8, k, seed=5, index=2).cuda()
     y = ops.w4a16_linear_decode(x, packed, sz)
     y2 = ops.w4a16_linear_decode(x * 2, packed, sz)
-    assert torch.equal(y2, y * 2)           # scaling by a power of two is exact end to end
+    # scaling by a power of two is exact end to end, except where an output falls in the
+    # fp16 subnormal range (spacing 2^-24), whose rounding is not scale invariant
+    assert (y2.float() - 2 * y.float()).abs().max().item() <= 2.0 ** -23
     ref = (x.float() @ ops.w4a16_dequant(packed, scale, zero, n, k).float().T)
     err = (y.float() - ref).norm() / ref.norm()
     assert err.item() <= TOL
@@ -171,3 +173,55 @@ def test_errors_are_loud():
     with pytest.raises(ValueError):
         ops.w4a16_linear_decode(x, torch.zeros(8, 16, dtype=torch.int32, device="cuda"),
                                 torch.zeros(1, 8, 2, dtype=torch.float16, device="cuda"))
+
+
+# ---------------------------------------------------------------- prefill (tcgen05) kernel
+def _prefill_case(n, k, m, group=128, seed=0, bias=False, rows=None):
+    from mindpipe_b200 import ops
+    w = synth.normal_weight(n, k, seed=seed, index=1).numpy()
+    x = synth.normal_activation(m, k, seed=seed, index=2).numpy()
+    b = (synth.normal_activation(1, n, seed=seed, index=3).numpy()[0] * np.float16(0.1)).astype(np.float16) if bias else None
+    (packed, scale, zero, gs), (wdq, s, z, u) = quantize_both(w, group)
+    sz = ops.w4a16_prepare(scale, zero, k)
+    y = ops.w4a16_linear_prefill(dev(x), packed, sz, None if b is None else dev(b))
+    ops.check_device_errors()
+    y = y.cpu().numpy()
+    if rows is not None:
+        return y[rows], O.linear_f16(x[rows], wdq, b)
+    return y, O.linear_f16(x, wdq, b)
+
+
+@pytest.mark.parametrize("m,n,k,group", [
+    (128, 256, 64, 64),        # one tile, one k-block
+    (128, 256, 512, 128),      # k loop beyond the ring depth
+    (65, 256, 256, 128),       # ragged M
+    (300, 520, 1024, 128),     # ragged M and N, several tiles
+    (1024, 2048, 256, 64),     # more tiles than one wave of CTAs? (8 x 8 = 64) no; both TMEM buffers via 2 tiles/CTA below
+    (2048, 4864, 128, 128),    # 16 x 19 = 304 tiles over 148 CTAs: every CTA walks 2-3 tiles
+    (1, 8, 64, 64),
+])
+def test_prefill_vs_oracle(m, n, k, group):
+    y, ref = _prefill_case(n, k, m, group=group, bias=True)
+    assert y.shape == ref.shape
+    assert O.rel_frobenius(y, ref) <= TOL
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_prefill_cfg2_m2048_row_sample(n, k):
+    """Config 2 at M=2048: every output row is produced, a seeded sample of rows is checked."""
+    rows = np.random.default_rng(n + k).choice(2048, 96, replace=False)
+    y, ref = _prefill_case(n, k, 2048, seed=2, rows=rows)
+    assert O.rel_frobenius(y, ref) <= TOL
+
+
+def test_linear_dispatch_uses_prefill_above_64_rows(golden):
+    from mindpipe_b200 import ops
+    w = synth.normal_weight(256, 512, seed=4, index=1).cuda()
+    x = synth.normal_activation(200, 512, seed=4, index=2).cuda()
+    packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+    sz = ops.w4a16_prepare(scale, zero, 512)
+    y = ops.w4a16_linear(x, packed, sz)
+    slabs = torch.cat([ops.w4a16_linear_decode(x[i:i + 64], packed, sz) for i in range(0, 200, 64)])
+    ops.check_device_errors()
+    err = (y.float() - slabs.float()).norm() / slabs.float().norm()
+    assert err.item() <= 2e-3                      # tensor-core vs streaming kernel: same Wdq, different sum order

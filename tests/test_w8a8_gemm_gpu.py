@@ -1,0 +1,140 @@
+"""GPU parity of the tcgen05 int8 GEMM (through the C ABI).
+
+int32 accumulators: bit-exact against exact integer matmul of the same codes
+(computed in float64, exact below 2^53).  fp16 outputs: relative Frobenius
+error <= 1e-2 against the reference's fake-quant forward as restated by the
+oracle (``SmoothQuantLinear.forward``); against the same-arithmetic int
+pipeline of the oracle the outputs agree to fp16 rounding.
+"""
+import numpy as np
+import pytest
+import torch
+
+from mindpipe_b200 import synth
+from oracle import pseudo_quant as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def exact_acc(qx, qw):
+    return (qx.astype(np.float64) @ qw.astype(np.float64).T).astype(np.int64)
+
+
+def rand_i8(shape, seed):
+    rng = np.random.default_rng(seed)
+    return rng.integers(-127, 128, size=shape, dtype=np.int8)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 128),      # one tile, one k-block
+    (128, 128, 512),      # k loop, ring wrap-around (4 k-blocks, 6 stages)
+    (128, 256, 1024),     # 8 k-blocks: every stage reused
+    (256, 384, 256),      # several tiles per CTA? no: several CTAs
+    (100, 72, 144),       # ragged M, N, K (K % 16 == 0)
+    (1, 8, 16),           # smallest legal problem
+    (300, 1000, 4096),
+])
+def test_int32_accumulators_bit_exact(m, n, k):
+    from mindpipe_b200 import ops
+    qx, qw = rand_i8((m, k), 1), rand_i8((n, k), 2)
+    acc = ops.w8a8_gemm_i32(dev(qx), dev(qw))
+    ops.check_device_errors()
+    assert np.array_equal(acc.cpu().numpy().astype(np.int64), exact_acc(qx, qw))
+
+
+def test_int32_many_tiles_per_cta_and_both_tmem_buffers():
+    """More tiles than SMs: every CTA walks several tiles, alternating accumulator buffers."""
+    from mindpipe_b200 import ops
+    m, n, k = 2048, 4096, 256          # 16 x 16 = 256 tiles of 128 x 256 over 148 CTAs
+    qx, qw = rand_i8((m, k), 3), rand_i8((n, k), 4)
+    acc = ops.w8a8_gemm_i32(dev(qx), dev(qw))
+    ops.check_device_errors()
+    assert np.array_equal(acc.cpu().numpy().astype(np.int64), exact_acc(qx, qw))
+
+
+def _w8a8_case(m, n, k, seed, bias=False):
+    from mindpipe_b200 import ops
+    x = synth.outlier_activation(m, k, seed=seed, index=100).numpy()
+    w = synth.normal_weight(n, k, seed=seed, index=0).numpy()
+    b = (synth.normal_activation(1, n, seed=seed, index=7).numpy()[0] * np.float16(0.1)).astype(np.float16) if bias else None
+    wfake, qw, sw = O.absmax_quant_last_dim(w)
+    qx_d, sx_d, _ = ops.act_quant_per_token(dev(x))
+    qw_d, sw_d, _ = ops.act_quant_per_token(dev(w))            # per-channel weights: the same arithmetic
+    assert np.array_equal(qw_d.cpu().numpy(), qw)
+    y = ops.w8a8_gemm(qx_d, sx_d, qw_d, sw_d, None if b is None else dev(b))
+    ops.check_device_errors()
+    return x, wfake, qw, sw, b, qx_d, sx_d, y.cpu().numpy()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 128, 256), (333, 520, 1024), (512, 1024, 4096)])
+def test_w8a8_fp16_output_vs_reference_forward(m, n, k):
+    x, wfake, qw, sw, b, qx_d, sx_d, y = _w8a8_case(m, n, k, seed=m, bias=True)
+    ref = O.smoothquant_linear_forward(x, wfake, b)                 # the reference's fake-quant forward
+    assert O.rel_frobenius(y, ref) <= TOL
+    same = O.w8a8_int_forward(qx_d.cpu().numpy(), sx_d.cpu().numpy(), qw, sw, b)
+    assert O.rel_frobenius(y, same) <= 1e-3
+
+
+def test_w8a8_cfg3_attention_proj_full_size():
+    """Config 3, 4096x4096 at M=4096: int32 accumulators on a row sample, fp16 output on all rows."""
+    from mindpipe_b200 import ops
+    m = n = k = 4096
+    x, wfake, qw, sw, b, qx_d, sx_d, y = _w8a8_case(m, n, k, seed=0)
+    acc = ops.w8a8_gemm_i32(qx_d, dev(qw))
+    ops.check_device_errors()
+    qx = qx_d.cpu().numpy()
+    _, codes, _ = O.absmax_quant_last_dim(x)
+    assert np.array_equal(qx, codes)                                # int8 activations bit-exact
+    rows = np.random.default_rng(0).choice(m, 256, replace=False)
+    assert np.array_equal(acc.cpu().numpy()[rows].astype(np.int64), exact_acc(qx[rows], qw))
+    ref = O.smoothquant_linear_forward(x[rows], wfake)
+    assert O.rel_frobenius(y[rows], ref) <= TOL
+
+
+@pytest.mark.parametrize("n,k", [(1024, 4096), (14336, 4096), (4096, 14336)])
+def test_w8a8_cfg3_other_shapes_row_sample(n, k):
+    m = 4096
+    x, wfake, qw, sw, b, qx_d, sx_d, y = _w8a8_case(m, n, k, seed=1)
+    rows = np.random.default_rng(1).choice(m, 64, replace=False)
+    ref = O.smoothquant_linear_forward(x[rows], wfake)
+    assert O.rel_frobenius(y[rows], ref) <= TOL
+
+
+def test_smoothquant_linear_module_matches_reference_golden(golden):
+    """SmoothQuantLinear twin (int8 weights) vs the reference module's outputs on the golden case."""
+    from mindpipe_b200 import ops
+    from mindpipe_b200.modules import SmoothQuantLinear, W8A8DynamicLinearMethod
+    g = golden("w8a8_small.npz")
+    lin = torch.nn.Linear(256, 16, bias=True).half().cuda()
+    with torch.no_grad():
+        lin.weight.copy_(dev(g["w"]))
+        lin.bias.copy_(dev(g["bias"]))
+    m = SmoothQuantLinear.from_float(lin)
+    assert m.weight.dtype == torch.int8
+    assert np.array_equal(m.dequantize().cpu().numpy(), g["w_fake"])      # values (int8 drops the sign of -0.0)
+    y = m(dev(g["x"]))
+    ops.check_device_errors()
+    assert O.rel_frobenius(y.cpu().numpy(), g["y"]) <= TOL
+    mq = SmoothQuantLinear.from_float(lin, quantize_output=True)
+    assert O.rel_frobenius(mq(dev(g["x"])).cpu().numpy(), g["y_outq"]) <= TOL
+    y3 = m(dev(g["x"]).reshape(1, 7, 256))
+    assert y3.shape == (1, 7, 16)
+    # linear-method entry: tensor input, (codes, scale) tuple input, return_scale, int32 passthrough
+    method = W8A8DynamicLinearMethod()
+    layer = type("Layer", (), {})()
+    layer.weight, layer.weight_scale = m.weight, m.weight_scale.clone()
+    method.process_weights_after_loading(layer)
+    out = method.apply(layer, dev(g["x"]), bias=m.bias)
+    assert torch.equal(out, y)
+    q, s, _ = ops.act_quant_per_token(dev(g["x"]))
+    layer._ascend_quant_config = {"output_dtype": torch.float16, "return_scale": True}
+    out2, s2 = method.apply(layer, (q, s), bias=m.bias)
+    assert torch.equal(out2, y) and torch.equal(s2, s)
+    layer._ascend_quant_config = {"output_dtype": torch.int32}
+    acc = method.apply(layer, (q, s))
+    assert np.array_equal(acc.cpu().numpy(), O.int32_accumulate(q.cpu().numpy(), m.weight.cpu().numpy()))
