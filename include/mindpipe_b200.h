@@ -113,6 +113,30 @@ int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32, const voi
                             int* error_word, mp_stream_t stream);
 
 /*
+ * The workspace split-K decode linear for callers that cannot allocate device
+ * memory.  (No counterpart in the reference; it exists for hosts of this
+ * library -- a plugin inside another runtime's forward pass, code that runs
+ * where cudaMalloc is off limits or under a frozen memory budget -- that have
+ * no scratch buffer to hand in.)  Same arguments and results as
+ * mp_w4a16_linear_decode minus the workspace: the split-K counters and partial
+ * sums live in a fixed 8 MiB array inside the library, which every GPU that
+ * loads the library holds until the process exits.  The call allocates
+ * nothing.  Limits and rules:
+ *   - M <= 64 as for the decode kernel; shapes whose partial sums do not fit
+ *     the array (16 KiB + k_split * M * N * 4 bytes > 8 MiB, see
+ *     mp_w4a16_linear_decode_static_max_bytes) return MP_ERR_WORKSPACE;
+ *   - the first call on each device looks up the array's device address; make
+ *     that first call before any stream capture;
+ *   - all calls on a device share the array: two calls that can run at the
+ *     same time on that device (different streams) race.  Calls ordered on
+ *     one stream are fine; the counters are cleared at the start of each call.
+ */
+size_t mp_w4a16_linear_decode_static_max_bytes(void);
+int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                  const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                  mp_stream_t stream);
+
+/*
  * Programmatic dependent launch for the decode linears (default off; returns
  * the previous setting).  When on, a decode kernel may begin fetching its
  * WEIGHTS while the preceding kernel of the stream is still finishing;

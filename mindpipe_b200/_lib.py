@@ -31,6 +31,8 @@ SIGNATURES = {
     "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
     "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
+    "mp_w4a16_linear_decode_static_max_bytes": (_Z, []),
+    "mp_w4a16_linear_decode_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_set_programmatic_launch": (_I, [_I]),
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),

@@ -18,6 +18,8 @@
 // re-arms the counter for the next call.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mp {
@@ -517,4 +519,74 @@ extern "C" int mp_set_programmatic_launch(int enabled) {
   const int prev = g_programmatic_launch ? 1 : 0;
   g_programmatic_launch = enabled != 0;
   return prev;
+}
+
+// ---------------------------------------------------------------------------
+// Split-K decode linear for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to obtain scratch for the split-K
+// partial sums: a plugin running inside another runtime's forward pass whose
+// memory pool is closed to it, code executing in a context where cudaMalloc is
+// off limits (inside a capture region set up by someone else, in a callback, in
+// a process with a frozen memory budget).  For them the workspace of the
+// split-K kernel lives in the fixed array below, which every GPU that loads the
+// library holds until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB: counters + partial sums
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// The array's name is only a host-side handle; the address kernels can use comes
+// from the runtime, once per device, with that device current.
+static int static_scratch_for_current_device(void** out) {
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return MP_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    MP_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
+    if (ptr == nullptr) return MP_ERR_CUDA;
+    g_static_scratch_ptr[device] = ptr;
+  }
+  *out = g_static_scratch_ptr[device];
+  return MP_OK;
+}
+
+extern "C" size_t mp_w4a16_linear_decode_static_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                             const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                             mp_stream_t stream) {
+  if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
+  if (M > 64 || K % kChunk != 0 || group % 32 != 0 || K % group != 0 || N % 8 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 2)) return MP_ERR_ALIGNMENT;
+  const DecodePlan pl = plan_decode(M, N, K, 0);
+  if ((size_t)pl.row_blocks * sizeof(int) > kCounterBytes) return MP_ERR_UNSUPPORTED;
+  const size_t need = kCounterBytes + (pl.k_split > 1 ? (size_t)pl.k_split * M * N * sizeof(float) : 0);
+  if (need > kStaticScratchBytes) return MP_ERR_WORKSPACE;     // beyond the fixed scratch: use the workspace entry point
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != MP_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left; the arrival counters must start at zero.
+  MP_CUDA_TRY(cudaMemsetAsync(scratch, 0, kCounterBytes, st));
+  DecodeParams p{};
+  p.x = static_cast<const __half*>(x_f16);
+  p.packed = static_cast<const uint32_t*>(packed_i32);
+  p.sz = static_cast<const uint32_t*>(sz_f16x2);
+  p.bias = static_cast<const __half*>(bias_f16);
+  p.y = static_cast<__half*>(y_f16);
+  p.M = M; p.N = N; p.K = K; p.group = group;
+  p.chunks = K / kChunk;
+  p.chunks_per_split = pl.chunks_per_split;
+  p.k_split = pl.k_split;
+  p.counters = static_cast<int*>(scratch);
+  p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kCounterBytes);
+  if (pl.mb == 1 && pl.half) return launch_decode<1, true, 1, 8>(p, pl, st);
+  if (pl.mb == 1) return launch_decode<1, false, 2, 8>(p, pl, st);
+  if (pl.mb == 2) return launch_decode<2, false, 2, 4>(p, pl, st);
+  return launch_decode<4, false, 2, 4>(p, pl, st);
 }

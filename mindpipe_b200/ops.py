@@ -148,6 +148,34 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
     return y
 
 
+def w4a16_linear_decode_static(x, weight_packed, scale_zero, bias=None, out=None):
+    """Decode linear that takes no scratch from the caller and allocates none.
+
+    For hosts that cannot allocate device memory (a plugin inside another
+    runtime's forward pass, code running where ``cudaMalloc`` is off limits):
+    the split-K scratch is a fixed 8 MiB array inside the library.  Pass
+    ``out`` to keep this wrapper allocation-free as well.  Shapes whose
+    partial sums exceed the array raise (status "workspace"); calls that may
+    overlap on one device share the array and would race.
+    """
+    x2 = _req(x, "x", torch.float16, 2)
+    p = _req(weight_packed, "weight_packed", torch.int32, 2)
+    sz = _req(scale_zero, "scale_zero", torch.float16, 3)
+    b = None if bias is None else _req(bias, "bias", torch.float16, 1)
+    m, k = x2.shape
+    n = p.shape[0]
+    groups = sz.shape[0]
+    if p.shape[1] * 8 != k or sz.shape[1] != n or k % groups:
+        raise ValueError(f"shape mismatch: x{tuple(x2.shape)} packed{tuple(p.shape)} sz{tuple(sz.shape)}")
+    y = torch.empty((m, n), dtype=torch.float16, device=x2.device) if out is None else _req(out, "out", torch.float16, 2)
+    if y.shape != (m, n):
+        raise ValueError(f"out must be [{m}, {n}]")
+    st = _lib.load().mp_w4a16_linear_decode_static(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
+                                                   m, n, k, k // groups, _stream())
+    _lib.check(st, "w4a16_linear_decode_static", M=m, N=n, K=k, group=k // groups)
+    return y
+
+
 def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None):
     """``y = x @ dequant(W)^T (+bias)`` on the fp16 tensor cores with the dequant fused in."""
     x2 = _req(x, "x", torch.float16, 2)
