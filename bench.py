@@ -326,6 +326,106 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------
+def run_suite(args, local_rank):
+    """Per-kernel numbers for the other configs (one JSON line each, after the headline line)."""
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+    def timed(fn, iters, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e-3
+
+    def emit(**kw):
+        print(json.dumps(kw), flush=True)
+
+    want = set(args.suite.split(","))
+    if "decode" in want or "all" in want:
+        for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008), (8192, 8192), (28672, 8192), (8192, 28672)]:
+            copies = max(2, int(300e6 // (n * k // 2)) + 1)           # rotate > 2x L2 of packed weights
+            mods = []
+            for c in range(copies):
+                w = synth.normal_weight(n, k, seed=c, index=0).to(dev)
+                packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+                mods.append((packed, ops.w4a16_prepare(scale, zero, k)))
+                del w
+            for m in (1, 16):
+                x = synth.normal_activation(m, k, seed=0).to(dev)
+                y = torch.empty((m, n), dtype=torch.float16, device=dev)
+                g = torch.cuda.CUDAGraph()
+                for pk, sz in mods:
+                    ops.w4a16_linear_decode(x, pk, sz, out=y)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g):
+                    for pk, sz in mods:
+                        ops.w4a16_linear_decode(x, pk, sz, out=y)
+                t = timed(g.replay, 20) / copies
+                b = w4a16_bytes(n, k, m)
+                emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
+                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"])
+            del mods
+    if "prefill" in want or "all" in want:
+        for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
+            w = synth.normal_weight(n, k, seed=0, index=0).to(dev)
+            packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+            sz = ops.w4a16_prepare(scale, zero, k)
+            x = synth.normal_activation(2048, k, seed=0).to(dev)
+            t = timed(lambda: ops.w4a16_linear_prefill(x, packed, sz), 20)
+            fl = 2 * 2048 * n * k
+            emit(suite="w4a16_prefill", N=n, K=k, M=2048, us=t * 1e6, tflops=fl / t / 1e12,
+                 frac_of_measured_bf16_burst=fl / t / 1e12 / peaks["bf16_tflops"])
+    if "w8a8" in want or "all" in want:
+        for (n, k) in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
+            m = 4096
+            w = synth.normal_weight(n, k, seed=0, index=0).to(dev)
+            qw, sw, _ = ops.act_quant_per_token(w)
+            x = synth.outlier_activation(m, k, seed=0).to(dev)
+            qx, sx, _ = ops.act_quant_per_token(x)
+            t_q = timed(lambda: ops.act_quant_per_token(x), 20)
+            t_g = timed(lambda: ops.w8a8_gemm(qx, sx, qw, sw), 20)
+            op = 2 * m * n * k
+            emit(suite="w8a8", N=n, K=k, M=m, act_quant_us=t_q * 1e6, act_quant_gbs=3 * m * k / t_q / 1e9,
+                 gemm_us=t_g * 1e6, gemm_tops=op / t_g / 1e12, linear_tops=op / (t_g + t_q) / 1e12,
+                 note="int8 dense peak is 2x the bf16 figure nominally (4.5 vs 2.25 POP/s)")
+    if "moe" in want or "all" in want:
+        shape = synth.MIXTRAL_8X7B
+        gus, dns = [], []
+        mod = None
+        for e in range(shape.num_experts):                      # quantise expert by expert to bound memory
+            gu, dn = synth.moe_weights(shape, seed=0, experts=range(e, e + 1))
+            m1 = SmoothQuantPackedMoeExperts(gu.to(dev), dn.to(dev), torch.nn.SiLU(), expert_range=(e, e + 1),
+                                             num_experts=shape.num_experts)
+            gus.append((m1.gate_up_proj, m1.gate_up_proj_scale))
+            dns.append((m1.down_proj, m1.down_proj_scale))
+            mod = m1
+        mod.gate_up_proj = torch.cat([g[0] for g in gus])
+        mod.gate_up_proj_scale = torch.cat([g[1] for g in gus])
+        mod.down_proj = torch.cat([d[0] for d in dns])
+        mod.down_proj_scale = torch.cat([d[1] for d in dns])
+        mod.expert_range = (0, shape.num_experts)
+        del gus, dns
+        hs = synth.normal_activation(shape.tokens, shape.hidden, seed=0).to(dev)
+        idx, wts = ops.moe_router_topk(synth.router_logits(shape.tokens, shape.num_experts, seed=0).to(dev), 2)
+        t = timed(lambda: mod(hs, idx, wts), 5, warm=2)
+        ops.check_device_errors()
+        opsn = 2 * (2 * shape.tokens) * shape.hidden * 2 * shape.ffn + 2 * (2 * shape.tokens) * shape.ffn * shape.hidden
+        emit(suite="moe_w8a8", tokens=shape.tokens, ms=t * 1e3, tokens_per_s=shape.tokens / t, tops=opsn / t / 1e12)
+
+
 def main():
     global POOL_SETS
     ap = argparse.ArgumentParser()
@@ -337,6 +437,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--pool-sets", type=int, default=POOL_SETS, help="layer sets in the weight pool")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch for the decode linears")
+    ap.add_argument("--suite", default="", help="comma list of extra per-kernel lines: decode,prefill,w8a8,moe,all")
+    ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     POOL_SETS = max(2, args.pool_sets)
@@ -346,7 +448,10 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:
-        run_ours(args, rank, world, local_rank)
+        if not args.suite_only:
+            run_ours(args, rank, world, local_rank)
+        if args.suite and rank == 0:
+            run_suite(args, local_rank)
 
 
 if __name__ == "__main__":

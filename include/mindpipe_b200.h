@@ -251,6 +251,17 @@ int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, c
 int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,
                    const void* topk_weights_f16, int T, int H, int k, void* out_f16, mp_stream_t stream);
 
+/*
+ * dst row i = src row row_map[i] (rows of row_bytes bytes; 4, or a multiple of
+ * 16); a negative map entry gives a zero row.  The row permutation an
+ * expert-parallel rank applies to what its peers sent (source-major) to get
+ * expert-sorted rows, and back -- the re-ordering torch_npu.npu_moe_init_routing_v2
+ * performs with active_expert_range after an all-gather dispatch
+ * (acceleration/runtime_patches/vllm_ascend.patch:3158-3214).
+ */
+int mp_gather_rows(const void* src, const void* row_map_i32, int n_dst_rows, int row_bytes, void* dst,
+                   mp_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

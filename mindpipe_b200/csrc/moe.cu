@@ -204,9 +204,44 @@ moe_combine_kernel(const __half* __restrict__ d, const int* __restrict__ dest_ro
   }
 }
 
+// dst row i = src row map[i] (16-byte vectors); map[i] < 0 leaves zeros.  Used to compact
+// the rows an expert-parallel rank receives from its peers into expert-sorted order, and back.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ map, int vec_per_row,
+                   uint4* __restrict__ dst) {
+  const int row = blockIdx.x;
+  const int s = map[row];
+  for (int v = threadIdx.x; v < vec_per_row; v += 256)
+    dst[(size_t)row * vec_per_row + v] = s >= 0 ? src[(size_t)s * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+}
+
+__global__ void gather_words_kernel(const uint32_t* __restrict__ src, const int* __restrict__ map, int n,
+                                    uint32_t* __restrict__ dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = map[i] >= 0 ? src[map[i]] : 0u;
+}
+
 }  // namespace mp
 
 using namespace mp;
+
+extern "C" int mp_gather_rows(const void* src, const void* row_map_i32, int n_dst_rows, int row_bytes, void* dst,
+                              mp_stream_t stream) {
+  if (!src || !row_map_i32 || !dst || n_dst_rows < 0 || row_bytes <= 0) return MP_ERR_INVALID_ARG;
+  if (n_dst_rows == 0) return MP_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (row_bytes == 4) {
+    gather_words_kernel<<<(n_dst_rows + 255) / 256, 256, 0, st>>>(
+        static_cast<const uint32_t*>(src), static_cast<const int*>(row_map_i32), n_dst_rows, static_cast<uint32_t*>(dst));
+  } else {
+    if (row_bytes % 16 != 0) return MP_ERR_UNSUPPORTED;
+    if (!aligned(src, 16) || !aligned(dst, 16)) return MP_ERR_ALIGNMENT;
+    gather_rows_kernel<<<n_dst_rows, 256, 0, st>>>(static_cast<const uint4*>(src), static_cast<const int*>(row_map_i32),
+                                                   row_bytes / 16, static_cast<uint4*>(dst));
+  }
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
 
 extern "C" int mp_moe_router_topk(const void* logits_f32, int T, int E, int k, void* idx_i32, void* weights_f16,
                                   mp_stream_t stream) {

@@ -222,43 +222,46 @@ w4a16_decode_kernel(const DecodeParams p) {
 // M <= 16: split K across a thread-block cluster and reduce through
 // distributed shared memory -- no scratch, no atomics, no second pass.
 //
-// A block owns 128 output rows (one warp per 32 rows) and 1/CK of K; the CK
-// blocks of a cluster cover all of K for the same rows.  Each warp streams
-// its weights in batches of up to four 128-column chunks (16 independent
-// 128-bit loads per lane in flight), the block stages the matching slice of
-// the activations once per batch (shared by its four warps), and after the
-// last batch every block parks its [M x 128] fp32 partial tile in its own
-// shared memory.  After a cluster barrier, block r of the cluster sums
-// columns [r*128/CK, (r+1)*128/CK) over all CK partial tiles in rank order
-// (deterministic), adds the bias and writes fp16.
+// A block of 8 warps owns 64 output rows (two row-warps of 32 rows) and 1/CK of
+// K; the CK blocks of a cluster cover all of K for the same rows.  Work is cut
+// fine so that thousands of warps are in flight: one warp step is one
+// 128-column chunk of 32 rows (four independent 128-bit loads per lane); the
+// four K-warps of a block take four consecutive chunks per round, and the
+// matching slice of the activations is staged once per round and shared by the
+// two row-warps.  After the last round the K-warps are summed in shared
+// memory, every block parks its [M x 64] fp32 tile, and after a cluster
+// barrier block r sums columns [r*64/CK, (r+1)*64/CK) over the CK tiles in
+// rank order (deterministic), adds the bias and writes fp16.
 //
-// The weight loads of the first batch are issued before
-// griddepcontrol.wait, so that under programmatic dependent launch they
-// overlap the tail of the preceding kernel; everything that touches x, bias
-// or y comes after it.
-constexpr int kBatch = 4;   // chunks per batch
-
+// The first round's weight loads are issued before griddepcontrol.wait, so
+// that under programmatic dependent launch they overlap the tail of the
+// preceding kernel; everything that touches x, bias or y comes after it.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+constexpr int kClusterRows = 64;    // output rows per block of the cluster kernel
+
 template <bool HALF>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 4)
 w4a16_decode_cluster_kernel(const DecodeParams p) {
   namespace cg = cooperative_groups;
   constexpr int HR = HALF ? 1 : 2;
   constexpr int MROWS = HALF ? 8 : 16;
-  __shared__ __align__(16) uint4 xs[kBatch * 4 * HR * 32];
-  __shared__ __align__(16) float red[MROWS * 128];
+  __shared__ __align__(16) uint4 xs[kWarpsK * 4 * HR * 32];            // one round: 4 chunks
+  __shared__ __align__(16) float red4[kWarpsK * MROWS * kClusterRows]; // per K-warp partial tiles
+  __shared__ __align__(16) float red[MROWS * kClusterRows];            // this block's tile
 
   cg::cluster_group cluster = cg::this_cluster();
   const int ck = static_cast<int>(cluster.num_blocks());
   const int crank = static_cast<int>(cluster.block_rank());
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 128 + warp * 32;
+  const int wk = warp & 3, wn = warp >> 2;
+  const int row0 = blockIdx.x * kClusterRows + wn * 32;
   const int cs = min(p.chunks, crank * p.chunks_per_split);
   const int ce = min(p.chunks, cs + p.chunks_per_split);
   const int words_per_row = p.K >> 3;
+  const bool group_is_chunk = p.group == kChunk;
 
   float acc[kRowGroups][4];
 #pragma unroll
@@ -266,45 +269,48 @@ w4a16_decode_cluster_kernel(const DecodeParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
 
-  uint4 q[kBatch][kRowGroups];
-  uint32_t szv[kBatch][kRowGroups];
-  auto load_batch = [&](int c_begin) {
+  // per-lane base pointers: row (row0 + 8r + g), 16-byte column slot t
+  const uint32_t* wbase[kRowGroups];
+  bool row_ok[kRowGroups];
 #pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const int chunk = c_begin + b;
-      const int kabs = chunk * kChunk + t * 32;
-      const int grp = kabs / p.group;
+  for (int r = 0; r < kRowGroups; ++r) {
+    const int n = row0 + r * 8 + g;
+    row_ok[r] = n < p.N;
+    wbase[r] = p.packed + (size_t)(row_ok[r] ? n : 0) * words_per_row + t * 4;
+  }
+
+  uint4 q[kRowGroups];
+  uint32_t szv[kRowGroups];
+  auto load_chunk = [&](int chunk) {
+    const int grp = group_is_chunk ? chunk : (chunk * kChunk + t * 32) / p.group;
 #pragma unroll
-      for (int r = 0; r < kRowGroups; ++r) {
-        const int n = row0 + r * 8 + g;
-        if (chunk < ce && n < p.N) {
-          q[b][r] = ldg_stream_v4(p.packed + (size_t)n * words_per_row + (kabs >> 3));
-          szv[b][r] = __ldg(p.sz + (size_t)grp * p.N + n);
-        } else {
-          q[b][r] = make_uint4(0, 0, 0, 0);
-          szv[b][r] = 0;
-        }
+    for (int r = 0; r < kRowGroups; ++r) {
+      if (chunk < ce && row_ok[r]) {
+        q[r] = ldg_stream_v4(wbase[r] + chunk * (kChunk / 8));
+        szv[r] = __ldg(p.sz + (size_t)grp * p.N + row0 + r * 8 + g);
+      } else {
+        q[r] = make_uint4(0, 0, 0, 0);
+        szv[r] = 0;
       }
     }
   };
 
-  load_batch(cs);
+  load_chunk(cs + wk);
   grid_launch_dependents();
   grid_dependency_wait();
 
-  for (int c_begin = cs; c_begin < ce; c_begin += kBatch) {
-    const int nch = min(kBatch, ce - c_begin);
+  for (int c_begin = cs; c_begin < ce; c_begin += kWarpsK) {
     if (c_begin != cs) {
-      __syncthreads();            // the previous batch's fragments have been consumed
-      load_batch(c_begin);
+      __syncthreads();                       // the previous round's fragments have been consumed
+      load_chunk(c_begin + wk);
     }
-    // stage x[:, batch columns] in fragment order (see the kernel above)
-    const int units = nch * 16;
-    for (int idx = tid; idx < MROWS * units; idx += 128) {
-      const int m = idx / units, u = idx - m * units;
+    // stage x[:, 4 chunks] in fragment order: 64 units of 8 columns per row
+    for (int idx = tid; idx < MROWS * 64; idx += 256) {
+      const int m = idx >> 6, u = idx & 63;
+      const int col = c_begin * kChunk + u * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (m < p.M) {
-        const uint4 in = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + (size_t)(c_begin * kChunk + u * 8));
+      if (m < p.M && col < p.K) {
+        const uint4 in = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + col);
         v.x = prmt(in.x, in.z, 0x5410);
         v.y = prmt(in.x, in.z, 0x7632);
         v.z = prmt(in.y, in.w, 0x5410);
@@ -315,48 +321,50 @@ w4a16_decode_cluster_kernel(const DecodeParams p) {
       xs[(((kc * 4 + c) * HR + hr) * 8 + gg) * 4 + tt] = v;
     }
     __syncthreads();
+    if (c_begin + wk < ce) {
+      ScaleZero sp[kRowGroups];
 #pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      if (b < nch) {
-        ScaleZero sp[kRowGroups];
+      for (int r = 0; r < kRowGroups; ++r) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&szv[r]);
+        sp[r] = make_scale_zero(__low2half(h), __high2half(h));
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int base = ((wk * 4 + c) * HR) * 32 + lane;
+        const uint4 alo = xs[base];
+        const uint4 ahi = HALF ? make_uint4(0, 0, 0, 0) : xs[base + 32];
 #pragma unroll
         for (int r = 0; r < kRowGroups; ++r) {
-          const __half2 h = *reinterpret_cast<const __half2*>(&szv[b][r]);
-          sp[r] = make_scale_zero(__low2half(h), __high2half(h));
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int base = ((b * 4 + c) * HR) * 32 + lane;
-          const uint4 alo = xs[base];
-          const uint4 ahi = HALF ? make_uint4(0, 0, 0, 0) : xs[base + 32];
-#pragma unroll
-          for (int r = 0; r < kRowGroups; ++r) {
-            const uint32_t word = c == 0 ? q[b][r].x : c == 1 ? q[b][r].y : c == 2 ? q[b][r].z : q[b][r].w;
-            __half2 v[4];
-            dequant8(word, sp[r], v);
-            mma_m16n8k16(acc[r], alo.x, ahi.x, alo.y, ahi.y, h2_as_u32(v[0]), h2_as_u32(v[1]));
-            mma_m16n8k16(acc[r], alo.z, ahi.z, alo.w, ahi.w, h2_as_u32(v[2]), h2_as_u32(v[3]));
-          }
+          const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
+          __half2 v[4];
+          dequant8(word, sp[r], v);
+          mma_m16n8k16(acc[r], alo.x, ahi.x, alo.y, ahi.y, h2_as_u32(v[0]), h2_as_u32(v[1]));
+          mma_m16n8k16(acc[r], alo.z, ahi.z, alo.w, ahi.w, h2_as_u32(v[2]), h2_as_u32(v[3]));
         }
       }
     }
   }
 
-  // park this block's partial tile: red[m][128 rows of the block]
+  // sum the four K-warps: red4[wk][m][64 rows of the block]
 #pragma unroll
   for (int r = 0; r < kRowGroups; ++r) {
-    float* base = red + g * 128 + warp * 32 + r * 8 + 2 * t;
+    float* base = red4 + (wk * MROWS + g) * kClusterRows + wn * 32 + r * 8 + 2 * t;
     *reinterpret_cast<float2*>(base) = make_float2(acc[r][0], acc[r][1]);
-    if (!HALF) *reinterpret_cast<float2*>(base + 8 * 128) = make_float2(acc[r][2], acc[r][3]);
+    if (!HALF) *reinterpret_cast<float2*>(base + 8 * kClusterRows) = make_float2(acc[r][2], acc[r][3]);
+  }
+  __syncthreads();
+  for (int e = tid; e < MROWS * kClusterRows; e += 256) {
+    red[e] = (red4[e] + red4[MROWS * kClusterRows + e]) +
+             (red4[2 * MROWS * kClusterRows + e] + red4[3 * MROWS * kClusterRows + e]);
   }
   cluster.sync();
-  const int cols = 128 / ck;                       // columns this block finishes
-  for (int e = tid; e < p.M * cols; e += 128) {
+  const int cols = kClusterRows / ck;              // columns this block finishes
+  for (int e = tid; e < p.M * cols; e += 256) {
     const int m = e / cols, c = crank * cols + (e - m * cols);
-    const int n = blockIdx.x * 128 + c;
+    const int n = blockIdx.x * kClusterRows + c;
     float part[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) part[r] = r < ck ? cluster.map_shared_rank(red, r)[m * 128 + c] : 0.0f;
+    for (int r = 0; r < 8; ++r) part[r] = r < ck ? cluster.map_shared_rank(red, r)[m * kClusterRows + c] : 0.0f;
     float s = 0.0f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) s += part[r];      // rank order: deterministic
@@ -374,7 +382,7 @@ template <bool HALF>
 static int launch_decode_cluster(const DecodeParams& p, int row_blocks, int ck, cudaStream_t st) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(row_blocks, ck, 1);
-  cfg.blockDim = dim3(128, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attrs[2];
@@ -457,6 +465,7 @@ using namespace mp;
 
 extern "C" size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split) {
   if (M <= 0 || M > 64 || N <= 0 || K <= 0 || K % kChunk != 0) return 0;
+  if (M <= 16 && k_split <= 0) return 0;     // cluster kernel: reduces through distributed shared memory
   const DecodePlan pl = plan_decode(M, N, K, k_split);
   return kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
 }
@@ -487,7 +496,7 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
     while (ck > 1 && p.chunks < ck) ck >>= 1;
     p.chunks_per_split = (p.chunks + ck - 1) / ck;
     p.k_split = ck;
-    const int row_blocks = (N + 127) / 128;
+    const int row_blocks = (N + kClusterRows - 1) / kClusterRows;
     return M <= 8 ? launch_decode_cluster<true>(p, row_blocks, ck, st)
                   : launch_decode_cluster<false>(p, row_blocks, ck, st);
   }

@@ -1,0 +1,172 @@
+"""Expert-parallel W8A8 MoE layer: one process per GPU, NCCL all-to-all dispatch / combine.
+
+Experts are partitioned evenly over the ranks of a process group (rank ``p``
+owns experts ``[p*E/P, (p+1)*E/P)``); tokens stay data-sharded.  A forward on
+each rank is
+
+1. route + gather + per-token int8 quantisation of the local tokens over ALL
+   experts (``ops.moe_route_gather_quant``): rows sorted by expert, every
+   expert segment padded to a multiple of 128 rows;
+2. exchange of the per-expert row counts, then ``all_to_all_single`` of the
+   int8 rows and of their fp32 scales -- the chunk for rank ``p`` is the
+   contiguous run of its experts' segments, so nothing is re-packed before
+   sending (activations travel as int8, the reference's "prequantize before
+   communication", acceleration/runtime_patches/vllm_ascend.patch:1668-1682);
+3. on the receiver, a row gather turns the source-major layout into
+   expert-sorted rows (padding dropped), the expert stage runs on them
+   (grouped int8 GEMM1 + SwiGLU + re-quant + grouped GEMM2), and the inverse
+   gather puts the fp16 results back in arrival order;
+4. ``all_to_all_single`` back (fp16) and the weighted combine at the token's
+   home rank (``ops.moe_combine``), which indexes the returned rows with the
+   ``dest_row`` table of step 1.
+
+The layout arithmetic is pure Python over the exchanged counts
+(:func:`plan_exchange`), so it is tested on CPU with ``gloo`` ranks; the
+all-to-all role is that of the reference runtime's all-to-all dispatcher
+(``TokenDispatcherWithAll2AllV``, vllm_ascend.patch:3228-3236).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+TILE = 128
+
+
+def expert_partition(num_experts: int, world_size: int) -> list[tuple[int, int]]:
+    """Contiguous, disjoint, complete expert ranges, one per rank."""
+    if num_experts % world_size != 0:
+        raise ValueError(f"{num_experts} experts do not divide over {world_size} ranks")
+    per = num_experts // world_size
+    return [(r * per, (r + 1) * per) for r in range(world_size)]
+
+
+def _pad(n: np.ndarray | int):
+    return (n + TILE - 1) // TILE * TILE
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: list[int]        # rows sent to each rank (padded segments of its experts)
+    recv_splits: list[int]        # rows received from each rank
+    gather_map: np.ndarray        # int32 [padded_rows]: expert-sorted row -> row in the receive buffer (-1 = padding)
+    scatter_map: np.ndarray       # int32 [recv_rows]: receive-buffer row -> expert-sorted row (-1 = padding)
+    plan_ints: np.ndarray         # int32 device plan: counts | cursors | segment offsets | tile count | tile experts
+    padded_rows: int              # rows of the expert-sorted buffers (multiple of 128, >= 128)
+    recv_rows: int
+
+
+def plan_exchange(send_counts: np.ndarray, recv_counts: np.ndarray, plan_len: int | None = None) -> ExchangePlan:
+    """Layout of one dispatch from the per-expert row counts.
+
+    ``send_counts[p, e]``: rows this rank routes to local expert ``e`` of rank ``p``;
+    ``recv_counts[s, e]``: rows rank ``s`` routes to this rank's local expert ``e``.
+    Segments are padded to 128 rows on the wire, exactly as the router laid them out.
+    """
+    send_counts = np.asarray(send_counts, dtype=np.int64)
+    recv_counts = np.asarray(recv_counts, dtype=np.int64)
+    world, e_loc = recv_counts.shape
+    send_splits = _pad(send_counts).sum(axis=1)
+    recv_pad = _pad(recv_counts)                      # [s, e] rows on the wire
+    recv_splits = recv_pad.sum(axis=1)
+    recv_rows = int(recv_splits.sum())
+    # offset of segment (s, e) inside the receive buffer
+    seg_start = np.zeros((world, e_loc), dtype=np.int64)
+    off = 0
+    for s in range(world):
+        for e in range(e_loc):
+            seg_start[s, e] = off
+            off += recv_pad[s, e]
+    per_expert = recv_counts.sum(axis=0)              # real rows per local expert
+    padded = _pad(per_expert)
+    padded_rows = max(int(padded.sum()), TILE)
+    gather_map = np.full(padded_rows, -1, dtype=np.int32)
+    scatter_map = np.full(max(recv_rows, 1), -1, dtype=np.int32)
+    seg_off = np.zeros(e_loc + 1, dtype=np.int64)
+    pos = 0
+    for e in range(e_loc):
+        seg_off[e] = pos
+        cur = pos
+        for s in range(world):
+            c = int(recv_counts[s, e])
+            src = np.arange(seg_start[s, e], seg_start[s, e] + c, dtype=np.int64)
+            gather_map[cur:cur + c] = src
+            scatter_map[src] = np.arange(cur, cur + c, dtype=np.int32)
+            cur += c
+        pos += int(padded[e])
+    seg_off[e_loc] = pos
+    tiles = []
+    for e in range(e_loc):
+        tiles += [e] * int(padded[e] // TILE)
+    n_ints = 3 * e_loc + 2 + max(len(tiles), padded_rows // TILE)
+    if plan_len is not None:
+        n_ints = max(n_ints, plan_len)
+    plan = np.zeros(n_ints, dtype=np.int32)
+    plan[:e_loc] = per_expert
+    plan[2 * e_loc:3 * e_loc + 1] = seg_off
+    plan[3 * e_loc + 1] = len(tiles)
+    plan[3 * e_loc + 2:3 * e_loc + 2 + len(tiles)] = tiles
+    return ExchangePlan([int(v) for v in send_splits], [int(v) for v in recv_splits], gather_map,
+                        scatter_map[:recv_rows] if recv_rows else scatter_map[:0], plan, padded_rows, recv_rows)
+
+
+class ExpertParallelMoE(torch.nn.Module):
+    """W8A8 MoE experts sharded over a process group (drop-in for the single-GPU module's ``forward``).
+
+    ``experts`` is a :class:`mindpipe_b200.modules.SmoothQuantPackedMoeExperts` built with
+    ``expert_range`` = this rank's range; only its int8 buffers are used here.
+    """
+
+    def __init__(self, experts, num_experts: int, group=None):
+        super().__init__()
+        self.experts = experts
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_experts = int(num_experts)
+        self.ranges = expert_partition(self.num_experts, self.world)
+        if tuple(experts.expert_range) != self.ranges[self.rank]:
+            raise ValueError(f"rank {self.rank} must hold experts {self.ranges[self.rank]}, got {experts.expert_range}")
+        self.e_loc = self.num_experts // self.world
+
+    @torch.no_grad()
+    def forward(self, hidden_states, top_k_index, top_k_weights):
+        from . import ops
+        shape = hidden_states.shape
+        hs = hidden_states.reshape(-1, shape[-1]).contiguous()
+        t, h = hs.shape
+        ids = top_k_index.reshape(t, -1).to(torch.int32).contiguous()
+        w = top_k_weights.reshape(t, -1).to(torch.float16).contiguous()
+        dev = hs.device
+        # 1. local routing over all experts
+        routing = ops.moe_route_gather_quant(hs, ids, 0, self.num_experts)
+        send_counts = routing.counts.reshape(self.world, self.e_loc).contiguous()
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        both = torch.stack([send_counts, recv_counts]).cpu().numpy()          # the one host read of the layer
+        plan = plan_exchange(both[0], both[1])
+        # 2. dispatch: int8 rows + fp32 scales
+        n_send = sum(plan.send_splits)
+        recv_q = torch.empty((max(plan.recv_rows, 1), h), dtype=torch.int8, device=dev)[:plan.recv_rows]
+        recv_s = torch.empty(max(plan.recv_rows, 1), dtype=torch.float32, device=dev)[:plan.recv_rows]
+        dist.all_to_all_single(recv_q, routing.routed_q[:n_send], plan.recv_splits, plan.send_splits, group=self.group)
+        dist.all_to_all_single(recv_s, routing.routed_scale[:n_send], plan.recv_splits, plan.send_splits,
+                               group=self.group)
+        # 3. expert stage on expert-sorted rows
+        gmap = torch.from_numpy(plan.gather_map).to(dev, non_blocking=True)
+        smap = torch.from_numpy(plan.scatter_map).to(dev, non_blocking=True)
+        plan_dev = torch.from_numpy(plan.plan_ints).to(dev, non_blocking=True)
+        q_sorted = ops.gather_rows(recv_q, gmap) if plan.recv_rows else torch.zeros((plan.padded_rows, h), dtype=torch.int8, device=dev)
+        s_sorted = ops.gather_rows(recv_s, gmap) if plan.recv_rows else torch.zeros(plan.padded_rows, dtype=torch.float32, device=dev)
+        ex = self.experts
+        d_sorted = ops.moe_expert_stage(q_sorted, s_sorted, plan_dev, self.e_loc, ex.gate_up_proj,
+                                        ex.gate_up_proj_scale, ex.down_proj, ex.down_proj_scale)
+        d_recv = ops.gather_rows(d_sorted, smap) if plan.recv_rows else d_sorted[:0]
+        # 4. return + combine at home
+        back = torch.empty((routing.padded_rows, h), dtype=torch.float16, device=dev)
+        dist.all_to_all_single(back[:n_send], d_recv, plan.send_splits, plan.recv_splits, group=self.group)
+        out = ops.moe_combine(back, routing.dest_row, ids, w, t)
+        return out.reshape(shape)

@@ -138,12 +138,16 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
         raise ValueError(f"shape mismatch: x{tuple(x2.shape)} packed{tuple(p.shape)} sz{tuple(sz.shape)}")
     lib = _lib.load()
     nbytes = lib.mp_w4a16_decode_workspace_bytes_ex(m, n, k, k_split)
-    ws = _workspace(nbytes, x2.device) if workspace is None else _req(workspace, "workspace", torch.uint8, 1)
+    if workspace is not None:
+        ws = _req(workspace, "workspace", torch.uint8, 1)
+    else:
+        ws = _workspace(nbytes, x2.device) if nbytes else None      # M <= 16 needs no scratch
     y = torch.empty((m, n), dtype=torch.float16, device=x2.device) if out is None else _req(out, "out", torch.float16, 2)
     if y.shape != (m, n):
         raise ValueError(f"out must be [{m}, {n}]")
     st = lib.mp_w4a16_linear_decode_ex(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
-                                       m, n, k, k // groups, ws.data_ptr(), ws.numel(), k_split, _stream())
+                                       m, n, k, k // groups, _ptr(ws), 0 if ws is None else ws.numel(), k_split,
+                                       _stream())
     _lib.check(st, "w4a16_linear_decode", M=m, N=n, K=k, group=k // groups)
     return y
 
@@ -383,3 +387,17 @@ def moe_combine(d, dest_row, top_k_index, top_k_weights, num_tokens: int):
                                         out.data_ptr(), _stream())
         _lib.check(st, "moe_combine", T=num_tokens, H=h, k=k)
     return out
+
+
+def gather_rows(src, row_map, out=None):
+    """``dst[i] = src[row_map[i]]`` for a 1-D or 2-D ``src``; negative map entries give zero rows."""
+    m = _req(row_map, "row_map", torch.int32, 1)
+    if not src.is_cuda or not src.is_contiguous():
+        raise ValueError("src must be a contiguous CUDA tensor")
+    row_bytes = src.element_size() * (src.shape[1] if src.dim() == 2 else 1)
+    shape = (m.numel(),) + tuple(src.shape[1:])
+    dst = torch.empty(shape, dtype=src.dtype, device=src.device) if out is None else out
+    if m.numel():
+        st = _lib.load().mp_gather_rows(src.data_ptr(), m.data_ptr(), m.numel(), row_bytes, dst.data_ptr(), _stream())
+        _lib.check(st, "gather_rows", rows=m.numel(), row_bytes=row_bytes)
+    return dst

@@ -45,7 +45,9 @@ def test_argument_validation_needs_no_gpu(built_lib):
     lib = _lib.load()
     assert lib.mp_w4a16_quantize(None, 8, 128, 128, None, None, None, None) == -1
     assert lib.mp_act_quant_per_token(None, 4, 64, None, None, None, None) == -1
-    assert lib.mp_w4a16_decode_workspace_bytes(16, 4096, 4096) > 0
+    assert lib.mp_w4a16_decode_workspace_bytes(16, 4096, 4096) == 0      # M <= 16: no scratch at all
+    assert lib.mp_w4a16_decode_workspace_bytes(32, 4096, 4096) > 0
+    assert lib.mp_w4a16_decode_workspace_bytes_ex(16, 4096, 4096, 4) > 0
     assert lib.mp_w4a16_decode_workspace_bytes(128, 4096, 4096) == 0     # decode kernel is M <= 64
     assert lib.mp_w4a16_decode_workspace_bytes(1, 4096, 100) == 0        # K must be a multiple of 128
     with pytest.raises(_lib.MindPipeKernelError, match="invalid argument"):

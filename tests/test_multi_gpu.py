@@ -1,0 +1,69 @@
+"""Multi-GPU parity (needs >= 2 GPUs; skipped otherwise): expert-parallel MoE and
+column-parallel W4A16 against the single-GPU path, over NCCL, one process per GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from mindpipe_b200 import ops, synth
+        from mindpipe_b200.column_parallel import ColumnParallelW4A16Linear
+        from mindpipe_b200.expert_parallel import ExpertParallelMoE, expert_partition
+        from mindpipe_b200.modules import SmoothQuantPackedMoeExperts, VllmPackedInt4Linear
+        dev = torch.device("cuda", rank)
+        # ---- expert-parallel MoE vs the single-GPU module ----
+        shape = synth.MoeShape(num_experts=8, hidden=256, ffn=512, top_k=2, tokens=64 * world + 10)
+        gu, dn = synth.moe_weights(shape, seed=1, std=0.05)
+        hs = synth.normal_activation(shape.tokens, shape.hidden, seed=1, index=11).to(dev)
+        idx, w = ops.moe_router_topk(synth.router_logits(shape.tokens, shape.num_experts, seed=1).to(dev), 2)
+        full = SmoothQuantPackedMoeExperts(gu.to(dev), dn.to(dev), torch.nn.SiLU())
+        ref = full(hs, idx, w)
+        lo, hi = expert_partition(shape.num_experts, world)[rank]
+        local = SmoothQuantPackedMoeExperts(gu[lo:hi].to(dev), dn[lo:hi].to(dev), torch.nn.SiLU(),
+                                            expert_range=(lo, hi), num_experts=shape.num_experts)
+        ep = ExpertParallelMoE(local, shape.num_experts)
+        # tokens are data-sharded: uneven shards on purpose
+        bounds = [0] + [shape.tokens * (r + 1) // world + (3 if r == 0 else 0) for r in range(world - 1)] + [shape.tokens]
+        a, b = bounds[rank], bounds[rank + 1]
+        out = ep(hs[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
+        ops.check_device_errors()
+        ok_moe = torch.equal(out, ref[a:b])           # same kernels, same rows: identical
+        # ---- column-parallel W4A16 vs single GPU ----
+        n, k = 1024, 2048
+        wt = synth.normal_weight(n, k, seed=2).to(dev)
+        packed, scale, zero, _ = ops.w4a16_quantize(wt, 128)
+        single = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k, out_features=n,
+                                      zero_point=zero)
+        x = synth.normal_activation(8, k, seed=2).to(dev)
+        cp = ColumnParallelW4A16Linear.from_full(packed, scale, zero, None, k, device=dev)
+        ok_col = torch.equal(cp(x), single(x))
+        ret[rank] = (bool(ok_moe), bool(ok_col))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_expert_parallel_and_column_parallel_match_single_gpu():
+    world = min(torch.cuda.device_count(), 4)
+    while 8 % world:
+        world -= 1
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert all(v == (True, True) for v in dict(ret).values()), dict(ret)

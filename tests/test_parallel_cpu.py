@@ -1,0 +1,142 @@
+"""Host-side logic of the multi-GPU paths, on CPU: pure layout arithmetic plus
+world_size-2 ``gloo`` runs of the dispatch / return exchange and the column gather."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mindpipe_b200.column_parallel import assemble_gathered, shard_packed_linear, shard_rows
+from mindpipe_b200.expert_parallel import TILE, expert_partition, plan_exchange
+
+
+def test_expert_partition_is_disjoint_and_complete():
+    for e, p in [(8, 1), (8, 2), (8, 4), (8, 8), (64, 8)]:
+        ranges = expert_partition(e, p)
+        owned = [x for lo, hi in ranges for x in range(lo, hi)]
+        assert owned == list(range(e))                      # every expert on exactly one rank, none extra
+    with pytest.raises(ValueError):
+        expert_partition(8, 3)
+
+
+def test_plan_exchange_layout():
+    rng = np.random.default_rng(0)
+    world, e_loc = 4, 2
+    send = rng.integers(0, 300, size=(world, e_loc))
+    recv = rng.integers(0, 300, size=(world, e_loc))
+    recv[2] = 0                                             # a peer that sends nothing
+    recv[:, 1][recv[:, 1] > 250] = 0
+    pl = plan_exchange(send, recv)
+    pad = lambda a: (a + TILE - 1) // TILE * TILE
+    assert pl.send_splits == list(pad(send).sum(axis=1))
+    assert pl.recv_splits == list(pad(recv).sum(axis=1))
+    assert pl.recv_rows == sum(pl.recv_splits)
+    per_expert = recv.sum(axis=0)
+    assert pl.padded_rows == max(int(pad(per_expert).sum()), TILE)
+    # the gather map is a bijection between real received rows and real sorted rows
+    real_sorted = np.nonzero(pl.gather_map >= 0)[0]
+    assert real_sorted.size == per_expert.sum()
+    assert np.array_equal(pl.scatter_map[pl.gather_map[real_sorted]], real_sorted)
+    assert (pl.scatter_map >= 0).sum() == per_expert.sum()
+    # plan ints: counts | cursors | offsets | tile count | tile experts
+    assert np.array_equal(pl.plan_ints[:e_loc], per_expert)
+    seg = pl.plan_ints[2 * e_loc:3 * e_loc + 1]
+    assert seg[0] == 0 and np.array_equal(np.diff(seg), pad(per_expert))
+    n_tiles = pl.plan_ints[3 * e_loc + 1]
+    assert n_tiles == pad(per_expert).sum() // TILE
+    tiles = pl.plan_ints[3 * e_loc + 2:3 * e_loc + 2 + n_tiles]
+    assert np.array_equal(np.bincount(tiles, minlength=e_loc), pad(per_expert) // TILE)
+    # rows of expert e in sorted order come from sources in ascending rank order
+    for e in range(e_loc):
+        rows = pl.gather_map[seg[e]:seg[e] + per_expert[e]]
+        assert (np.diff(rows) > 0).all()
+
+
+def test_plan_exchange_no_rows():
+    pl = plan_exchange(np.zeros((2, 1), int), np.zeros((2, 1), int))
+    assert pl.recv_rows == 0 and pl.padded_rows == TILE and pl.plan_ints[3 * 1 + 1] == 0
+    assert (pl.gather_map == -1).all()
+
+
+def test_column_shards_and_assembly():
+    n, k8 = 64, 16
+    packed = torch.arange(n * k8, dtype=torch.int32).reshape(n, k8)
+    scale = torch.rand(n, 4).half()
+    parts = [shard_packed_linear(packed, scale, None, None, 4, r) for r in range(4)]
+    assert torch.equal(torch.cat([p[0] for p in parts]), packed)
+    assert shard_rows(28672, 8, 7) == (25088, 28672)
+    with pytest.raises(ValueError):
+        shard_rows(10, 4, 0)
+    y = torch.randn(5, 64)
+    gathered = torch.stack([y[:, r * 16:(r + 1) * 16] for r in range(4)])
+    assert torch.equal(assemble_gathered(gathered), y)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ep_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(rank)
+        e, k, t, h = 4, 2, 37 + 5 * rank, 8
+        e_loc = e // world
+        ids = torch.stack([torch.randperm(e)[:k] for _ in range(t)]).to(torch.int32)
+        hidden = torch.randn(t, h)
+        # CPU stand-in for the router kernel: sort entries by expert into 128-padded segments
+        counts = torch.bincount(ids.flatten().long(), minlength=e)
+        pad = (counts + TILE - 1) // TILE * TILE
+        seg = torch.cat([torch.zeros(1, dtype=torch.long), pad.cumsum(0)])
+        dest = torch.empty(t * k, dtype=torch.long)
+        cursor = seg[:-1].clone()
+        for i, ex in enumerate(ids.flatten().tolist()):
+            dest[i] = cursor[ex]
+            cursor[ex] += 1
+        routed = torch.zeros(int(seg[-1]), h)
+        routed[dest] = hidden.repeat_interleave(k, dim=0)
+        send_counts = counts.reshape(world, e_loc).to(torch.int32)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts)
+        pl = plan_exchange(send_counts.numpy(), recv_counts.numpy())
+        recv = torch.empty(pl.recv_rows, h)
+        dist.all_to_all_single(recv, routed[:sum(pl.send_splits)], pl.recv_splits, pl.send_splits)
+        gmap = torch.from_numpy(pl.gather_map).long()
+        sorted_rows = torch.zeros(pl.padded_rows, h)
+        sorted_rows[gmap >= 0] = recv[gmap[gmap >= 0]]
+        # fake expert stage: expert e scales its rows by (global expert id + 1)
+        seg_loc = pl.plan_ints[2 * e_loc:3 * e_loc + 1]
+        out_sorted = torch.zeros_like(sorted_rows)
+        for le in range(e_loc):
+            cnt = int(pl.plan_ints[le])
+            out_sorted[seg_loc[le]:seg_loc[le] + cnt] = sorted_rows[seg_loc[le]:seg_loc[le] + cnt] * (rank * e_loc + le + 1)
+        smap = torch.from_numpy(pl.scatter_map).long()
+        d_recv = torch.zeros(pl.recv_rows, h)
+        d_recv[smap >= 0] = out_sorted[smap[smap >= 0]]
+        back = torch.zeros(int(seg[-1]), h)
+        dist.all_to_all_single(back[:sum(pl.send_splits)], d_recv, pl.send_splits, pl.recv_splits)
+        got = back[dest].reshape(t, k, h).sum(dim=1)
+        want = (hidden[:, None, :] * (ids[:, :, None].float() + 1)).sum(dim=1)
+        ret[rank] = bool(torch.allclose(got, want, atol=1e-5))
+        # column-parallel gather with a fake local linear
+        y_full = torch.arange(3 * 8, dtype=torch.float32).reshape(3, 8)
+        lo, hi = shard_rows(8, world, rank)
+        gathered = torch.empty(world * 3, hi - lo)
+        dist.all_gather_into_tensor(gathered, y_full[:, lo:hi].contiguous())
+        ret[rank] = ret[rank] and bool(torch.equal(assemble_gathered(gathered.view(world, 3, hi - lo)), y_full))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_exchange_world2_gloo():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_ep_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert dict(ret) == {0: True, 1: True}
