@@ -172,6 +172,62 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def measure_moe(world, rank, dev, dist, iters=5):
+    """Mixtral-8x7B-shaped W8A8 MoE layer (8 experts, hidden 4096, ffn 14336, top-2, 8192 tokens):
+    experts sharded over the ranks, tokens data-sharded, all-to-all dispatch/combine.  tokens/s of the
+    whole job = 8192 / (max over ranks of the layer time)."""
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+    shape = synth.MIXTRAL_8X7B
+    if shape.num_experts % world:
+        return {"skipped": f"{shape.num_experts} experts do not divide over {world} ranks"}
+    per = shape.num_experts // world
+    lo, hi = rank * per, (rank + 1) * per
+    parts = []
+    for e in range(lo, hi):                                    # expert by expert: bounded host/device memory
+        gu, dn = synth.moe_weights(shape, seed=0, experts=range(e, e + 1))
+        parts.append(SmoothQuantPackedMoeExperts(gu.to(dev), dn.to(dev), torch.nn.SiLU(), expert_range=(e, e + 1),
+                                                 num_experts=shape.num_experts))
+    mod = parts[0]
+    mod.gate_up_proj = torch.cat([m.gate_up_proj for m in parts])
+    mod.gate_up_proj_scale = torch.cat([m.gate_up_proj_scale for m in parts])
+    mod.down_proj = torch.cat([m.down_proj for m in parts])
+    mod.down_proj_scale = torch.cat([m.down_proj_scale for m in parts])
+    mod.expert_range = (lo, hi)
+    del parts
+    t_loc = shape.tokens // world
+    hs = synth.normal_activation(shape.tokens, shape.hidden, seed=0)[rank * t_loc:(rank + 1) * t_loc].to(dev)
+    logits = synth.router_logits(shape.tokens, shape.num_experts, seed=0)[rank * t_loc:(rank + 1) * t_loc].to(dev)
+    idx, wts = ops.moe_router_topk(logits, shape.top_k)
+    if world > 1:
+        from mindpipe_b200.expert_parallel import ExpertParallelMoE
+        layer = ExpertParallelMoE(mod, shape.num_experts)
+    else:
+        layer = mod
+    for _ in range(2):
+        layer(hs, idx, wts)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        layer(hs, idx, wts)
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    int8_ops = 2 * (shape.top_k * shape.tokens) * shape.hidden * 2 * shape.ffn + \
+        2 * (shape.top_k * shape.tokens) * shape.ffn * shape.hidden
+    return {"config": "mixtral-8x7b-shaped layer, 8192 tokens, top-2, experts sharded over the ranks (all-to-all)",
+            "ms_per_layer": ms, "tokens_per_s": shape.tokens / (ms * 1e-3), "int8_tops": int8_ops / (ms * 1e-3) / 1e12,
+            "n_gpus": world}
+
+
 def workload_config():
     return {"workload": "llama2-7b decoder-layer linear set (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008), "
                         f"W4A16 asymmetric int4 g{GROUP}, decode M={M_DECODE}",
@@ -220,9 +276,33 @@ def run_ours(args, rank, world, local_rank):
     ws = ops.new_workspace(ws_bytes, dev)          # the seven linears run back to back on one stream
     y_dev = {name: torch.empty((M_DECODE, n), dtype=torch.float16, device=dev) for name, (n, k) in layer_shapes()}
 
+    side = [torch.cuda.Stream(device=dev) for _ in range(2)]
+
+    def launch(name, mod):
+        ops.w4a16_linear_decode(x_dev[name], mod.weight_packed, mod._scale_zero, workspace=ws, out=y_dev[name])
+
     def step(layer):
-        for name, mod in layer:
-            ops.w4a16_linear_decode(x_dev[name], mod.weight_packed, mod._scale_zero, workspace=ws, out=y_dev[name])
+        """The layer's dependency structure: q, k, v side by side; o; gate, up side by side; down."""
+        mods = dict(layer)
+        main = torch.cuda.current_stream()
+
+        def parallel(names):
+            if not args.concurrent:
+                for n in names:
+                    launch(n, mods[n])
+                return
+            for s_, n in zip(side, names[1:]):
+                s_.wait_stream(main)
+                with torch.cuda.stream(s_):
+                    launch(n, mods[n])
+            launch(names[0], mods[names[0]])
+            for s_ in side[:len(names) - 1]:
+                main.wait_stream(s_)
+
+        parallel(["q_proj", "k_proj", "v_proj"])
+        launch("o_proj", mods["o_proj"])
+        parallel(["gate_proj", "up_proj"])
+        launch("down_proj", mods["down_proj"])
 
     # ---- one CUDA graph per layer set: the kernels, without host launch gaps ----
     for layer in pool[:2]:
@@ -282,6 +362,13 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
 
+    moe_extra = None
+    if args.moe:
+        try:
+            moe_extra = measure_moe(world, rank, dev, dist)
+        except Exception as err:          # the headline number must not depend on the extra
+            moe_extra = {"error": f"{type(err).__name__}: {err}"[:200]}
+
     if rank == 0:
         bytes_step = step_bytes(M_DECODE)
         value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
@@ -311,6 +398,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "tflops": world * step_flops(M_DECODE) * args.steps / (ms * 1e-3) / 1e12,
+            "moe_w8a8": moe_extra,
         }
         if world == 1 and not args.no_cpu_baseline:
             cores = torch.get_num_threads()
@@ -398,7 +486,14 @@ def run_suite(args, local_rank):
             t_q = timed(lambda: ops.act_quant_per_token(x), 20)
             t_g = timed(lambda: ops.w8a8_gemm(qx, sx, qw, sw), 20)
             op = 2 * m * n * k
-            emit(suite="w8a8", N=n, K=k, M=m, act_quant_us=t_q * 1e6, act_quant_gbs=3 * m * k / t_q / 1e9,
+            lib_tops = None
+            try:                                   # library int8 GEMM: a timing yardstick only
+                wt = qw.t().contiguous()
+                t_l = timed(lambda: torch._int_mm(qx, wt), 20)
+                lib_tops = op / t_l / 1e12
+            except Exception:
+                pass
+            emit(suite="w8a8", N=n, K=k, M=m, library_int8_gemm_tops=lib_tops, act_quant_us=t_q * 1e6, act_quant_gbs=3 * m * k / t_q / 1e9,
                  gemm_us=t_g * 1e6, gemm_tops=op / t_g / 1e12, linear_tops=op / (t_g + t_q) / 1e12,
                  note="int8 dense peak is 2x the bf16 figure nominally (4.5 vs 2.25 POP/s)")
     if "moe" in want or "all" in want:
@@ -437,6 +532,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--pool-sets", type=int, default=POOL_SETS, help="layer sets in the weight pool")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch for the decode linears")
+    ap.add_argument("--concurrent", type=int, default=1,
+                    help="run q/k/v and gate/up of a layer on parallel streams inside the captured step")
+    ap.add_argument("--moe", type=int, default=1, help="also measure the expert-parallel MoE layer (extra key)")
     ap.add_argument("--suite", default="", help="comma list of extra per-kernel lines: decode,prefill,w8a8,moe,all")
     ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
     args = ap.parse_args()

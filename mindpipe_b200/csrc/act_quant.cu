@@ -8,13 +8,16 @@
 //   s    = f16( max(absmax, f16(1e-5)) / 127 )
 //   code = rint( f16( x / s ) )         (division in fp32, rounded to fp16 first)
 //   fake = f16( code * s )
-// The row is read with 128-bit loads, reduced with warp shuffles, and re-read
-// (an L1/L2 hit) for the second pass, so HBM sees it once.
+// The row is read with 128-bit loads, reduced with warp shuffles and kept in
+// registers for the rounding step (rows up to 16384 columns), so it is read once.
 #include "common.cuh"
 
 namespace mp {
 
-template <int THREADS>
+// NV = 128-bit vectors per thread.  NV > 0: the row (K <= THREADS * 8 * NV) is held in
+// registers between the abs-max and the rounding step, so global memory is read once;
+// NV == 0: any K, second pass re-reads the row (an L1/L2 hit).
+template <int THREADS, int NV>
 __global__ void __launch_bounds__(THREADS)
 act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
                  float* __restrict__ scale, __half* __restrict__ fake) {
@@ -23,15 +26,27 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   const int row = blockIdx.x;
   const __half* xr = x + (size_t)row * K;
   const int chunks = K >> 3;
+  constexpr int NREG = NV > 0 ? NV : 1;
+  uint4 held[NREG];
   float amax = 0.0f;
-  for (int c = threadIdx.x; c < chunks; c += THREADS) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+  auto absmax_of = [&](const uint4& raw) {
     const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 f = __half22float2(__habs2(h2[j]));
       amax = fmaxf(amax, fmaxf(f.x, f.y));
     }
+  };
+  if (NV > 0) {
+#pragma unroll
+    for (int v = 0; v < NREG; ++v) {
+      const int c = threadIdx.x + v * THREADS;
+      held[v] = c < chunks ? *reinterpret_cast<const uint4*>(xr + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int v = 0; v < NREG; ++v) absmax_of(held[v]);
+  } else {
+    for (int c = threadIdx.x; c < chunks; c += THREADS) absmax_of(*reinterpret_cast<const uint4*>(xr + c * 8));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -50,8 +65,7 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   }
   __syncthreads();
   const float sf = s_scale;
-  for (int c = threadIdx.x; c < chunks; c += THREADS) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+  auto emit = [&](int c, const uint4& raw) {
     const __half* h = reinterpret_cast<const __half*>(&raw);
     float code[8];
 #pragma unroll
@@ -69,11 +83,20 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
       *reinterpret_cast<uint2*>(q + (size_t)row * K + c * 8) = o;
     }
     if (fake) {
-      __half out[8];
+      __align__(16) __half out[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) out[j] = f2h(__fmul_rn(code[j], sf));
       *reinterpret_cast<uint4*>(fake + (size_t)row * K + c * 8) = *reinterpret_cast<uint4*>(out);
     }
+  };
+  if (NV > 0) {
+#pragma unroll
+    for (int v = 0; v < NREG; ++v) {
+      const int c = threadIdx.x + v * THREADS;
+      if (c < chunks) emit(c, held[v]);
+    }
+  } else {
+    for (int c = threadIdx.x; c < chunks; c += THREADS) emit(c, *reinterpret_cast<const uint4*>(xr + c * 8));
   }
 }
 
@@ -92,11 +115,17 @@ extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i
   float* sc = static_cast<float*>(scale_f32);
   __half* fk = static_cast<__half*>(fake_f16);
   if (K <= 1024) {
-    act_quant_kernel<128><<<M, 128, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_kernel<128, 1><<<M, 128, 0, st>>>(x, M, K, q, sc, fk);
+  } else if (K <= 2048) {
+    act_quant_kernel<256, 1><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 4096) {
-    act_quant_kernel<256><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_kernel<256, 2><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
+  } else if (K <= 8192) {
+    act_quant_kernel<512, 2><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+  } else if (K <= 16384) {
+    act_quant_kernel<512, 4><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
   } else {
-    act_quant_kernel<512><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_kernel<512, 0><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
   }
   MP_LAUNCH_CHECK();
   return MP_OK;

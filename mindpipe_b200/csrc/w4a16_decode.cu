@@ -22,6 +22,10 @@
 
 #include "common.cuh"
 
+#ifndef MP_TRACE_POINT
+#define MP_TRACE_POINT(i)   // debugging builds may record a timestamp here
+#endif
+
 namespace mp {
 
 constexpr int kWarpsK = 4;        // warps along K inside a block
@@ -222,16 +226,20 @@ w4a16_decode_kernel(const DecodeParams p) {
 // M <= 16: split K across a thread-block cluster and reduce through
 // distributed shared memory -- no scratch, no atomics, no second pass.
 //
-// A block of 8 warps owns 64 output rows (two row-warps of 32 rows) and 1/CK of
-// K; the CK blocks of a cluster cover all of K for the same rows.  Work is cut
-// fine so that thousands of warps are in flight: one warp step is one
-// 128-column chunk of 32 rows (four independent 128-bit loads per lane); the
-// four K-warps of a block take four consecutive chunks per round, and the
-// matching slice of the activations is staged once per round and shared by the
-// two row-warps.  After the last round the K-warps are summed in shared
-// memory, every block parks its [M x 64] fp32 tile, and after a cluster
-// barrier block r sums columns [r*64/CK, (r+1)*64/CK) over the CK tiles in
-// rank order (deterministic), adds the bias and writes fp16.
+// A block of 16 warps (4 row-warps x 4 K-warps) owns 128 output rows and 1/CK
+// of K; the CK blocks of a cluster cover all of K for the same rows.  Work is
+// cut fine so that thousands of warps are in flight on a problem of a few
+// megabytes: one warp step is one 128-column chunk of 32 rows (four independent
+// 128-bit loads per lane).  Per round the block stages the four chunks of
+// activations its K-warps need once, for all four row-warps; every per-warp
+// index is computed once, outside the round loop.  The reduction is a push:
+// block r of the cluster owns output columns [r*128/CK, (r+1)*128/CK); after
+// its last round every warp stores its accumulator fragments straight into
+// the owner's shared memory (one slot per (block, K-warp), so nothing is
+// overwritten), one cluster barrier makes the stores visible, and each owner
+// adds its 4*CK slots in a fixed order (deterministic), adds the bias and
+// writes fp16.  A barrier arrive at kernel entry, waited on just before the
+// first remote store, guarantees every block of the cluster is running.
 //
 // The first round's weight loads are issued before griddepcontrol.wait, so
 // that under programmatic dependent launch they overlap the tail of the
@@ -239,21 +247,23 @@ w4a16_decode_kernel(const DecodeParams p) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-constexpr int kClusterRows = 64;    // output rows per block of the cluster kernel
+constexpr int kClusterRows = 128;   // output rows per block of the cluster kernel
+constexpr int kClusterThreads = 512;
 
 template <bool HALF>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(kClusterThreads, 2)
 w4a16_decode_cluster_kernel(const DecodeParams p) {
   namespace cg = cooperative_groups;
   constexpr int HR = HALF ? 1 : 2;
   constexpr int MROWS = HALF ? 8 : 16;
   __shared__ __align__(16) uint4 xs[kWarpsK * 4 * HR * 32];            // one round: 4 chunks
-  __shared__ __align__(16) float red4[kWarpsK * MROWS * kClusterRows]; // per K-warp partial tiles
-  __shared__ __align__(16) float red[MROWS * kClusterRows];            // this block's tile
+  // slots[(src block * 4 + K-warp)][m][column of this owner]: 4*CK slots of MROWS x (128/CK) floats
+  __shared__ __align__(16) float slots[kWarpsK * MROWS * kClusterRows];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int ck = static_cast<int>(cluster.num_blocks());
   const int crank = static_cast<int>(cluster.block_rank());
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "I am running"; waited on before the pushes
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int wk = warp & 3, wn = warp >> 2;
@@ -269,58 +279,65 @@ w4a16_decode_cluster_kernel(const DecodeParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
 
-  // per-lane base pointers: row (row0 + 8r + g), 16-byte column slot t
-  const uint32_t* wbase[kRowGroups];
-  bool row_ok[kRowGroups];
-#pragma unroll
-  for (int r = 0; r < kRowGroups; ++r) {
-    const int n = row0 + r * 8 + g;
-    row_ok[r] = n < p.N;
-    wbase[r] = p.packed + (size_t)(row_ok[r] ? n : 0) * words_per_row + t * 4;
-  }
+  // per-lane weight pointer: row (row0 + g), 16-byte column slot t, this warp's first chunk; the
+  // other row groups are 8 rows further each.  N % 8 == 0, so a row group is valid as a whole.
+  const int rows_left = p.N - row0;                                      // valid rows of this warp
+  const int vec_per_row = words_per_row >> 2;                            // uint4 per weight row
+  const uint4* wptr = reinterpret_cast<const uint4*>(p.packed) +
+                      (size_t)(rows_left > 0 ? row0 + g : 0) * vec_per_row + t + (cs + wk) * (kChunk / 32);
+  const uint32_t* szptr = p.sz + (rows_left > 0 ? row0 + g : 0);
+
+  // staging slot of this thread: unit u (8 columns) of token row m_lo (and m_lo + 8)
+  const int st_u = tid & 63, st_m = tid >> 6;                           // 64 units x 8 rows per pass
+  const int st_dst = (((st_u >> 4) * 4 + (st_u & 3)) * HR * 8 + st_m) * 4 + ((st_u >> 2) & 3);
+  const __half* st_src = p.x + (size_t)st_m * p.K + st_u * 8;
 
   uint4 q[kRowGroups];
   uint32_t szv[kRowGroups];
   auto load_chunk = [&](int chunk) {
     const int grp = group_is_chunk ? chunk : (chunk * kChunk + t * 32) / p.group;
+    const uint32_t* sp = szptr + (size_t)grp * p.N;
 #pragma unroll
     for (int r = 0; r < kRowGroups; ++r) {
-      if (chunk < ce && row_ok[r]) {
-        q[r] = ldg_stream_v4(wbase[r] + chunk * (kChunk / 8));
-        szv[r] = __ldg(p.sz + (size_t)grp * p.N + row0 + r * 8 + g);
+      if (chunk < ce && r * 8 < rows_left) {
+        q[r] = ldg_stream_v4(wptr + (size_t)r * 8 * vec_per_row);
+        szv[r] = __ldg(sp + r * 8);
       } else {
         q[r] = make_uint4(0, 0, 0, 0);
         szv[r] = 0;
       }
     }
+    wptr += kWarpsK * (kChunk / 32);                                    // next round: four chunks on
   };
 
+  MP_TRACE_POINT(0);
   load_chunk(cs + wk);
   grid_launch_dependents();
   grid_dependency_wait();
+  MP_TRACE_POINT(1);
 
   for (int c_begin = cs; c_begin < ce; c_begin += kWarpsK) {
     if (c_begin != cs) {
       __syncthreads();                       // the previous round's fragments have been consumed
       load_chunk(c_begin + wk);
     }
-    // stage x[:, 4 chunks] in fragment order: 64 units of 8 columns per row
-    for (int idx = tid; idx < MROWS * 64; idx += 256) {
-      const int m = idx >> 6, u = idx & 63;
-      const int col = c_begin * kChunk + u * 8;
+    // stage x[:, 4 chunks]: unit (m, u) -> fragment order [chunk][c][half][g][t], nibble-permuted
+#pragma unroll
+    for (int hr = 0; hr < HR; ++hr) {
+      const int m = st_m + hr * 8;
+      const int col = c_begin * kChunk + st_u * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (m < p.M && col < p.K) {
-        const uint4 in = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + col);
+        const uint4 in = *reinterpret_cast<const uint4*>(st_src + (size_t)hr * 8 * p.K + c_begin * kChunk);
         v.x = prmt(in.x, in.z, 0x5410);
         v.y = prmt(in.x, in.z, 0x7632);
         v.z = prmt(in.y, in.w, 0x5410);
         v.w = prmt(in.y, in.w, 0x7632);
       }
-      const int kc = u >> 4, tt = (u >> 2) & 3, c = u & 3;
-      const int hr = (m >> 3) % HR, gg = m & 7;
-      xs[(((kc * 4 + c) * HR + hr) * 8 + gg) * 4 + tt] = v;
+      xs[st_dst + hr * 32] = v;
     }
     __syncthreads();
+    MP_TRACE_POINT(2);
     if (c_begin + wk < ce) {
       ScaleZero sp[kRowGroups];
 #pragma unroll
@@ -345,35 +362,34 @@ w4a16_decode_cluster_kernel(const DecodeParams p) {
     }
   }
 
-  // sum the four K-warps: red4[wk][m][64 rows of the block]
+  MP_TRACE_POINT(3);
+  // push the fragments to the owners of their columns
+  const int cols = kClusterRows / ck;              // columns each block owns
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // every block of the cluster has started
+  MP_TRACE_POINT(4);
 #pragma unroll
   for (int r = 0; r < kRowGroups; ++r) {
-    float* base = red4 + (wk * MROWS + g) * kClusterRows + wn * 32 + r * 8 + 2 * t;
-    *reinterpret_cast<float2*>(base) = make_float2(acc[r][0], acc[r][1]);
-    if (!HALF) *reinterpret_cast<float2*>(base + 8 * kClusterRows) = make_float2(acc[r][2], acc[r][3]);
+    const int n_local = wn * 32 + r * 8 + 2 * t;
+    const int owner = n_local / cols, c_in = n_local - owner * cols;
+    float* dst = cluster.map_shared_rank(slots, owner) + ((size_t)((crank * kWarpsK + wk) * MROWS + g) * cols + c_in);
+    *reinterpret_cast<float2*>(dst) = make_float2(acc[r][0], acc[r][1]);
+    if (!HALF) *reinterpret_cast<float2*>(dst + 8 * cols) = make_float2(acc[r][2], acc[r][3]);
   }
-  __syncthreads();
-  for (int e = tid; e < MROWS * kClusterRows; e += 256) {
-    red[e] = (red4[e] + red4[MROWS * kClusterRows + e]) +
-             (red4[2 * MROWS * kClusterRows + e] + red4[3 * MROWS * kClusterRows + e]);
-  }
-  cluster.sync();
-  const int cols = kClusterRows / ck;              // columns this block finishes
-  for (int e = tid; e < p.M * cols; e += 256) {
-    const int m = e / cols, c = crank * cols + (e - m * cols);
-    const int n = blockIdx.x * kClusterRows + c;
-    float part[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) part[r] = r < ck ? cluster.map_shared_rank(red, r)[m * kClusterRows + c] : 0.0f;
+  MP_TRACE_POINT(5);
+  cluster.sync();                                  // remote stores are visible; nobody is written to after this
+  MP_TRACE_POINT(6);
+  const int n_slots = ck * kWarpsK;
+  for (int e = tid; e < p.M * cols; e += kClusterThreads) {
+    const int m = e / cols, c = e - m * cols;
+    const int n = blockIdx.x * kClusterRows + crank * cols + c;
     float s = 0.0f;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) s += part[r];      // rank order: deterministic
+    for (int sl = 0; sl < n_slots; ++sl) s += slots[(sl * MROWS + m) * cols + c];   // fixed order: deterministic
     if (n < p.N) {
       if (p.bias) s += h2f(p.bias[n]);
       p.y[(size_t)m * p.N + n] = f2h(s);
     }
   }
-  cluster.sync();                                  // nobody leaves while its tile is being read
+  MP_TRACE_POINT(7);
 }
 
 static bool g_programmatic_launch = false;
@@ -382,7 +398,7 @@ template <bool HALF>
 static int launch_decode_cluster(const DecodeParams& p, int row_blocks, int ck, cudaStream_t st) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(row_blocks, ck, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.blockDim = dim3(kClusterThreads, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attrs[2];
@@ -491,9 +507,11 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   p.chunks = K / kChunk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M <= 16 && k_split <= 0) {
-    // cluster split-K: the largest portable cluster (<= 8) that leaves every block a chunk
-    int ck = 8;
-    while (ck > 1 && p.chunks < ck) ck >>= 1;
+    // cluster split-K: the smallest power of two (<= 8, the portable limit) that puts about two
+    // 16-warp blocks on every SM, as long as every block keeps at least one chunk per K-warp
+    const int row_blocks_ = (N + kClusterRows - 1) / kClusterRows;
+    int ck = 1;
+    while (ck < 8 && row_blocks_ * ck < 2 * kSmCount && p.chunks >= 2 * ck * kWarpsK) ck <<= 1;
     p.chunks_per_split = (p.chunks + ck - 1) / ck;
     p.k_split = ck;
     const int row_blocks = (N + kClusterRows - 1) / kClusterRows;

@@ -1,17 +1,17 @@
 // W4A16 prefill GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T on the fp16 tensor
 // cores, with the int4 unpack + group dequant fused in as a producer stage.
 //
-// One persistent CTA per SM, 10 warps:
+// One persistent CTA per SM, 14 warps:
 //   warp 0      TMA producer for the activation tile x[128 x 64] (128-byte swizzle)
 //   warp 1      MMA issuer: tcgen05.mma kind::f16, M=128, N=256, K=16, fp32 in TMEM
 //   warps 2-5   epilogue: tcgen05.ld -> (+bias) -> fp16 -> global (TMEM double buffered)
-//   warps 6-9   dequant producers: stream the packed int4 words of the weight tile
+//   warps 6-13  dequant producers: stream the packed int4 words of the weight tile
 //               [256 rows x 64 columns] from global memory with 128-bit loads, expand
 //               them with dequant8 (exactly f16((u - z) * s), the reference's Wdq) and
 //               store them into shared memory in the canonical K-major 128-byte-swizzle
 //               layout the MMA reads -- the dequantised weights never exist in HBM.
 //
-// A stage is full when the TMA bytes have landed and all four dequant warps have
+// A stage is full when the TMA bytes have landed and all dequant warps have
 // arrived (after a fence that makes their generic-proxy stores visible to the
 // tensor core).  Every wait is bounded (see tc.cuh).
 #include "common.cuh"
@@ -31,7 +31,8 @@ constexpr int kABytes = kBM * kBK * 2;   // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;   // 32 KB
 constexpr int kTmemCols = 2 * kBN;
 constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + 256;
-constexpr int kThreads = 320;
+constexpr int kThreads = 448;
+constexpr int kDequantWarps = 8;
 }  // namespace w4
 
 struct W4GemmParams {
@@ -60,7 +61,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full0 + 8 * s, 1 + 4);      // TMA producer's expect_tx arrival + four dequant warps
+      mbar_init(full0 + 8 * s, 1 + kDequantWarps);   // TMA producer's expect_tx arrival + the dequant warps
       mbar_init(empty0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -161,9 +162,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
               reinterpret_cast<uint4*>(dst)[v] =
                   make_uint4(packed_out[4 * v], packed_out[4 * v + 1], packed_out[4 * v + 2], packed_out[4 * v + 3]);
           } else {
-            for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {                     // static indices keep the values in registers
               const uint32_t w = packed_out[j >> 1];
-              dst[j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+              if (n0 + c0 + j < p.N)
+                dst[j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
             }
           }
         }
@@ -174,59 +177,53 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       if (++buf == 2) { buf = 0; buf_phase ^= 1; }
     }
   } else {
-    // ---- dequant producers: thread dt owns weight-tile rows dt and dt + 128 ----
-    const int dt = threadIdx.x - 6 * 32;            // 0..127
+    // ---- dequant producers: thread dt owns row dt of the weight tile ----
+    const int dt = threadIdx.x - 6 * 32;            // 0..255
     const int words_per_row = p.K >> 3;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    const int row_off = (dt >> 3) * 1024 + (dt & 7) * 128;   // row dt of a K-major tile with 128-byte rows
+    const int sw = dt & 7;
     for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-      const int n0 = (tile / p.m_tiles) * kBN;
-      const int n_a = n0 + dt, n_b = n0 + dt + 128;
-      const bool ok_a = n_a < p.N, ok_b = n_b < p.N;
-      const uint32_t* row_a = p.packed + (size_t)(ok_a ? n_a : 0) * words_per_row;
-      const uint32_t* row_b = p.packed + (size_t)(ok_b ? n_b : 0) * words_per_row;
+      const int n = (tile / p.m_tiles) * kBN + dt;
+      const bool n_ok = n < p.N;
+      const uint32_t* row = p.packed + (size_t)(n_ok ? n : 0) * words_per_row;
+      const uint32_t* szp = p.sz + (n_ok ? n : 0);
       // software pipeline: the words of k-block kb+1 are in flight while kb is expanded
-      uint4 qa[2], qb[2];
-      auto fetch = [&](int kb, uint4 (&a)[2], uint4 (&b)[2]) {
-        const int w0 = kb * (kBK / 8);
-        const bool k_ok = (kb + 1) * kBK <= p.K;
-        a[0] = (ok_a && k_ok) ? ldg_stream_v4(row_a + w0) : make_uint4(0, 0, 0, 0);
-        a[1] = (ok_a && k_ok) ? ldg_stream_v4(row_a + w0 + 4) : make_uint4(0, 0, 0, 0);
-        b[0] = (ok_b && k_ok) ? ldg_stream_v4(row_b + w0) : make_uint4(0, 0, 0, 0);
-        b[1] = (ok_b && k_ok) ? ldg_stream_v4(row_b + w0 + 4) : make_uint4(0, 0, 0, 0);
+      uint4 q0, q1;
+      auto fetch = [&](int kb) {
+        const uint32_t* src = row + kb * (kBK / 8);
+        q0 = n_ok ? ldg_stream_v4(src) : make_uint4(0, 0, 0, 0);
+        q1 = n_ok ? ldg_stream_v4(src + 4) : make_uint4(0, 0, 0, 0);
       };
-      fetch(0, qa, qb);
+      fetch(0);
+      uint32_t szw = n_ok ? __ldg(szp) : 0u;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        uint4 ca[2] = {qa[0], qa[1]}, cb[2] = {qb[0], qb[1]};
-        if (kb + 1 < p.k_blocks) fetch(kb + 1, qa, qb);
-        const int grp = (kb * kBK) / p.group;
-        const uint32_t sza = ok_a ? __ldg(p.sz + (size_t)grp * p.N + n_a) : 0u;
-        const uint32_t szb = ok_b ? __ldg(p.sz + (size_t)grp * p.N + n_b) : 0u;
-        const __half2 ha = *reinterpret_cast<const __half2*>(&sza), hb = *reinterpret_cast<const __half2*>(&szb);
-        const ScaleZero spa = make_scale_zero(__low2half(ha), __high2half(ha));
-        const ScaleZero spb = make_scale_zero(__low2half(hb), __high2half(hb));
+        const uint4 c0 = q0, c1 = q1;
+        const uint32_t szc = szw;
+        if (kb + 1 < p.k_blocks) {
+          fetch(kb + 1);
+          const int grp_next = ((kb + 1) * kBK) / p.group;
+          szw = n_ok ? __ldg(szp + (size_t)grp_next * p.N) : 0u;
+        }
+        const __half2 hz = *reinterpret_cast<const __half2*>(&szc);
+        const ScaleZero sp = make_scale_zero(__low2half(hz), __high2half(hz));
         if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag))) { ok = false; break; }
-        unsigned char* tile_b = sB + stage * kBBytes;
+        unsigned char* row_base = sB + stage * kBBytes + row_off;
 #pragma unroll
-        for (int half_sel = 0; half_sel < 2; ++half_sel) {
-          const int r = dt + half_sel * 128;                        // row inside the weight tile
-          unsigned char* row_base = tile_b + (r >> 3) * 1024 + (r & 7) * 128;
-          const ScaleZero& sp = half_sel ? spb : spa;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {                             // 16-byte chunk j = columns 8j..8j+7
-            const uint4& src = half_sel ? cb[j >> 2] : ca[j >> 2];
-            const uint32_t word = (j & 3) == 0 ? src.x : (j & 3) == 1 ? src.y : (j & 3) == 2 ? src.z : src.w;
-            __half2 v[4];
-            dequant8(word, sp, v);
-            const uint32_t a = h2_as_u32(v[0]), b = h2_as_u32(v[1]), c = h2_as_u32(v[2]), d = h2_as_u32(v[3]);
-            uint4 o;                                                // natural column order for the MMA
-            o.x = prmt(a, b, 0x5410);
-            o.y = prmt(c, d, 0x5410);
-            o.z = prmt(a, b, 0x7632);
-            o.w = prmt(c, d, 0x7632);
-            *reinterpret_cast<uint4*>(row_base + ((j ^ (r & 7)) << 4)) = o;   // 128-byte swizzle
-          }
+        for (int j = 0; j < 8; ++j) {                             // 16-byte chunk j = columns 8j..8j+7
+          const uint4& src = j < 4 ? c0 : c1;
+          const uint32_t word = (j & 3) == 0 ? src.x : (j & 3) == 1 ? src.y : (j & 3) == 2 ? src.z : src.w;
+          __half2 v[4];
+          dequant8(word, sp, v);
+          const uint32_t a = h2_as_u32(v[0]), b = h2_as_u32(v[1]), c = h2_as_u32(v[2]), d = h2_as_u32(v[3]);
+          uint4 o;                                                // natural column order for the MMA
+          o.x = prmt(a, b, 0x5410);
+          o.y = prmt(c, d, 0x5410);
+          o.z = prmt(a, b, 0x7632);
+          o.w = prmt(c, d, 0x7632);
+          *reinterpret_cast<uint4*>(row_base + ((j ^ sw) << 4)) = o;   // 128-byte swizzle
         }
         fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();

@@ -56,7 +56,8 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kBarBytes = 256;
-  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes;
+  static constexpr int kScaleBytes = 4 * 256 * 4;   // per epilogue warp: the tile's 256 channel scales
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes + kScaleBytes;
 };
 
 template <int BN, int EPI>
@@ -72,6 +73,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * Cfg::kBBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_scales = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + Cfg::kBarBytes);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -160,17 +162,36 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     const int quarter = warp & 3;               // TMEM lanes [32*quarter, +32) belong to this warp
+    float* my_scales = s_scales + quarter * 256; // this warp's copy of the tile's channel scales
     int buf = 0;
     uint32_t buf_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
+      // channel scales of this tile -> shared memory (each warp keeps its own copy: no cross-warp barrier)
+      if (EPI != EPI_I32) {
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = lane + 32 * i;             // column of the accumulator tile
+          int n, src;
+          if (EPI == EPI_SWIGLU) {
+            n = n_tile * 128 + (c & 127);
+            src = e_row0 + (c >= 128 ? p.up_row_offset : 0) + n;
+          } else {
+            n = n_tile * BN + c;
+            src = e_row0 + n;
+          }
+          my_scales[c] = (c < BN && n < p.N) ? __ldg(p.b_scale + src) : 0.0f;
+        }
+        __syncwarp();
+      }
       // the whole warp takes the same way out: the TMEM loads below are warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
       const int row = m_tile * kBM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const float sa = (EPI != EPI_I32 && row_ok) ? p.a_scale[row] : 0.0f;
-      const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       if (EPI == EPI_SWIGLU) {
         const int n0 = n_tile * 128;
@@ -182,29 +203,37 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_ld_32x32(taddr + c0, rg);
           tmem_ld_32x32(taddr + 128 + c0, ru);
           tmem_ld_wait();
-          __align__(16) __half hv[32];
+          uint32_t hp[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = n0 + c0 + j;
-            const bool n_ok = n < p.N;
-            const float sg = n_ok ? __ldg(p.b_scale + e_row0 + n) : 0.0f;
-            const float su = n_ok ? __ldg(p.b_scale + e_row0 + p.up_row_offset + n) : 0.0f;
-            // the reference rounds gate/up (F.linear output), silu(gate) and the product to fp16
-            const __half g16 = f2h(static_cast<float>(static_cast<int>(rg[j])) * sa * sg);
-            const __half u16 = f2h(static_cast<float>(static_cast<int>(ru[j])) * sa * su);
-            const float gf = h2f(g16);
-            const __half s16 = f2h(gf / (1.0f + expf(-gf)));
-            const __half h16 = hmul_t(s16, u16);
-            hv[j] = h16;
-            hmax = fmaxf(hmax, fabsf(h2f(h16)));
+          for (int j = 0; j < 32; j += 2) {
+            __half h2v[2];
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+              const float sg = my_scales[c0 + j + jj], su = my_scales[128 + c0 + j + jj];
+              // the reference rounds gate/up (F.linear output), silu(gate) and the product to fp16
+              const __half g16 = f2h(static_cast<float>(static_cast<int>(rg[j + jj])) * sa * sg);
+              const __half u16 = f2h(static_cast<float>(static_cast<int>(ru[j + jj])) * sa * su);
+              const float gf = h2f(g16);
+              const __half s16 = f2h(gf / (1.0f + expf(-gf)));
+              const __half h16 = hmul_t(s16, u16);
+              h2v[jj] = h16;
+              hmax = fmaxf(hmax, fabsf(h2f(h16)));
+            }
+            hp[j >> 1] = h2_as_u32(__halves2half2(h2v[0], h2v[1]));
           }
           if (row_ok) {
             __half* dst = out + (size_t)row * p.N + n0 + c0;
             if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<uint4*>(hv)[v];
+              for (int v = 0; v < 4; ++v)
+                reinterpret_cast<uint4*>(dst)[v] = make_uint4(hp[4 * v], hp[4 * v + 1], hp[4 * v + 2], hp[4 * v + 3]);
             } else {
-              for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = hv[j];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {                   // static indices keep hp in registers
+                const uint32_t w = hp[j >> 1];
+                if (n0 + c0 + j < p.N)
+                  dst[j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+              }
             }
           }
         }
@@ -224,27 +253,36 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 for (int v = 0; v < 8; ++v)
                   reinterpret_cast<uint4*>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
               } else {
-                for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = static_cast<int>(r[j]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + c0 + j < p.N) dst[j] = static_cast<int>(r[j]);
               }
             }
           } else {
-            __align__(16) __half hv[32];
+            uint32_t hp[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + c0 + j;
-              const bool n_ok = n < p.N;
-              const float sb = n_ok ? __ldg(p.b_scale + e_row0 + n) : 0.0f;
-              float v = static_cast<float>(static_cast<int>(r[j])) * sa * sb;
-              if (p.bias && n_ok) v += h2f(p.bias[n]);
-              hv[j] = f2h(v);
+            for (int j = 0; j < 32; j += 2) {
+              float v0 = static_cast<float>(static_cast<int>(r[j])) * sa * my_scales[c0 + j];
+              float v1 = static_cast<float>(static_cast<int>(r[j + 1])) * sa * my_scales[c0 + j + 1];
+              if (p.bias) {
+                if (n0 + c0 + j < p.N) v0 += h2f(p.bias[n0 + c0 + j]);
+                if (n0 + c0 + j + 1 < p.N) v1 += h2f(p.bias[n0 + c0 + j + 1]);
+              }
+              hp[j >> 1] = h2_as_u32(__floats2half2_rn(v0, v1));
             }
             if (row_ok) {
               __half* dst = static_cast<__half*>(p.out) + (size_t)row * p.N + n0 + c0;
               if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
-                for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<uint4*>(hv)[v];
+                for (int v = 0; v < 4; ++v)
+                  reinterpret_cast<uint4*>(dst)[v] = make_uint4(hp[4 * v], hp[4 * v + 1], hp[4 * v + 2], hp[4 * v + 3]);
               } else {
-                for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) dst[j] = hv[j];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {                 // static indices keep hp in registers
+                  const uint32_t w = hp[j >> 1];
+                  if (n0 + c0 + j < p.N)
+                    dst[j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+                }
               }
             }
           }
