@@ -44,9 +44,26 @@ def w4a16_bytes(n, k, m, g=GROUP):
     return n * k // 2 + 2 * n * k // g + n * k // (2 * g) + 2 * m * k + 2 * m * n
 
 
-def layer_shapes():
+FUSE = True   # q/k/v and gate/up stored as one row-concatenated weight each (how serving runtimes hold them)
+
+
+def base_shapes():
     from mindpipe_b200 import synth
     return list(synth.LLAMA2_7B_LINEARS.items())
+
+
+def layer_shapes():
+    """The linears one step launches: (name, (N, K)).  With FUSE the q/k/v weights are concatenated
+    along the output rows into qkv_proj and gate/up into gate_up_proj (group quantisation is per row,
+    so concatenation changes no code, scale or zero point)."""
+    base = dict(base_shapes())
+    if not FUSE:
+        return list(base.items())
+    return [("qkv_proj", (3 * base["q_proj"][0], base["q_proj"][1])), ("o_proj", base["o_proj"]),
+            ("gate_up_proj", (2 * base["gate_proj"][0], base["gate_proj"][1])), ("down_proj", base["down_proj"])]
+
+
+FUSED_PARTS = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
 
 
 def step_bytes(m):
@@ -138,12 +155,12 @@ def build_cpu_sets(n_sets, m):
     sets, xs = [], {}
     for s in range(n_sets):
         layer = {}
-        for i, (name, (n, k)) in enumerate(layer_shapes()):
+        for i, (name, (n, k)) in enumerate(base_shapes()):
             w = synth.normal_weight(n, k, seed=s, index=i).numpy()
             wdq, _, _, _ = O.w4_group_asym_quantize(w, GROUP)
             layer[name] = torch.from_numpy(wdq)
         sets.append(layer)
-    for i, (name, (n, k)) in enumerate(layer_shapes()):
+    for i, (name, (n, k)) in enumerate(base_shapes()):
         xs[name] = synth.normal_activation(m, k, seed=0, index=100 + i)
     return sets, xs
 
@@ -231,6 +248,7 @@ def measure_moe(world, rank, dev, dist, iters=5):
 def workload_config():
     return {"workload": "llama2-7b decoder-layer linear set (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008), "
                         f"W4A16 asymmetric int4 g{GROUP}, decode M={M_DECODE}",
+            "launches_per_step": [f"{name} {n}x{k}" for name, (n, k) in layer_shapes()],
             "weight_pool": f"{POOL_SETS} layer sets cycled, {POOL_SETS * step_bytes(M_DECODE) / 1e6:.0f} MB > 126 MB L2 "
                            "(inputs larger than L2; no explicit flush)",
             "parallelism": "replicas only (this config does not shard)"}
@@ -254,16 +272,24 @@ def run_ours(args, rank, world, local_rank):
     from mindpipe_b200 import _lib
     # ---- build the pool: quantise seeded weights on the GPU with the product's own kernel ----
     pool = []
+    base_index = {name: i for i, (name, _) in enumerate(base_shapes())}
     for s in range(POOL_SETS):
+        parts = {}
+        for name, (n, k) in base_shapes():
+            w = synth.normal_weight(n, k, seed=s, index=base_index[name]).to(dev)
+            parts[name] = ops.w4a16_quantize(w, GROUP)[:3]
+            del w
         layer = []
-        for i, (name, (n, k)) in enumerate(layer_shapes()):
-            w = synth.normal_weight(n, k, seed=s, index=i).to(dev)
-            packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+        for name, (n, k) in layer_shapes():
+            members = FUSED_PARTS.get(name, [name]) if FUSE else [name]
+            packed = torch.cat([parts[m_][0] for m_ in members]).contiguous()
+            scale = torch.cat([parts[m_][1] for m_ in members]).contiguous()
+            zero = torch.cat([parts[m_][2] for m_ in members]).contiguous()
             mod = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k,
                                        out_features=n, zero_point=zero)
             mod.process_weights_after_loading()
             layer.append((name, mod))
-            del w
+        del parts
         pool.append(layer)
     x_host = {name: synth.normal_activation(M_DECODE, k, seed=0, index=100 + i).pin_memory()
               for i, (name, (n, k)) in enumerate(layer_shapes())}
@@ -299,6 +325,10 @@ def run_ours(args, rank, world, local_rank):
             for s_ in side[:len(names) - 1]:
                 main.wait_stream(s_)
 
+        if FUSE:
+            for n in ("qkv_proj", "o_proj", "gate_up_proj", "down_proj"):
+                launch(n, mods[n])
+            return
         parallel(["q_proj", "k_proj", "v_proj"])
         launch("o_proj", mods["o_proj"])
         parallel(["gate_proj", "up_proj"])
@@ -443,7 +473,10 @@ def run_suite(args, local_rank):
 
     want = set(args.suite.split(","))
     if "decode" in want or "all" in want:
-        for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008), (8192, 8192), (28672, 8192), (8192, 28672)]:
+        shapes = [(4096, 4096), (11008, 4096), (4096, 11008), (8192, 8192), (28672, 8192), (8192, 28672)]
+        if args.decode_shapes:
+            shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.decode_shapes.split(",")]
+        for (n, k) in shapes:
             copies = max(2, int(300e6 // (n * k // 2)) + 1)           # rotate > 2x L2 of packed weights
             mods = []
             for c in range(copies):
@@ -522,7 +555,7 @@ def run_suite(args, local_rank):
 
 
 def main():
-    global POOL_SETS
+    global POOL_SETS, FUSE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -532,14 +565,18 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--pool-sets", type=int, default=POOL_SETS, help="layer sets in the weight pool")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch for the decode linears")
+    ap.add_argument("--fuse", type=int, default=1,
+                    help="hold q/k/v and gate/up as row-concatenated weights (4 launches per step instead of 7)")
     ap.add_argument("--concurrent", type=int, default=1,
                     help="run q/k/v and gate/up of a layer on parallel streams inside the captured step")
     ap.add_argument("--moe", type=int, default=1, help="also measure the expert-parallel MoE layer (extra key)")
     ap.add_argument("--suite", default="", help="comma list of extra per-kernel lines: decode,prefill,w8a8,moe,all")
     ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
+    ap.add_argument("--decode-shapes", default="", help="restrict the decode suite, e.g. 8192x28672,4096x4096 (NxK)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     POOL_SETS = max(2, args.pool_sets)
+    FUSE = bool(args.fuse)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -146,6 +146,13 @@ int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, con
  */
 int mp_set_programmatic_launch(int enabled);
 
+/*
+ * Synchronously reads (and clears) the flag a decode kernel sets when one of
+ * its bounded device-side waits gave up; *value == 0 means none did.  A
+ * debugging aid: it synchronises with the device.
+ */
+int mp_read_decode_error(int* value);
+
 /* ------------------------------------------------------------------- W8A8 */
 
 /*

@@ -34,6 +34,7 @@ SIGNATURES = {
     "mp_w4a16_linear_decode_static_max_bytes": (_Z, []),
     "mp_w4a16_linear_decode_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_set_programmatic_launch": (_I, [_I]),
+    "mp_read_decode_error": (_I, [_P]),
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_w8a8_gemm_i32": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),

@@ -199,6 +199,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 // cuTensorMapEncodeTiled, fetched from the driver at run time so that the
 // library has no link-time dependency on libcuda.
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
-                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                         bool swizzle_128b = true);
 
 }  // namespace mp

@@ -28,6 +28,12 @@
 
 namespace mp {
 
+// TMA-fed kernel for M <= 16 (w4a16_decode_tma.cu)
+int launch_decode_tma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
+                      int group, cudaStream_t st);
+void set_decode_programmatic_launch(bool on);
+int read_and_clear_decode_error(int* value);
+
 constexpr int kWarpsK = 4;        // warps along K inside a block
 constexpr int kRowGroups = 4;     // 8-row groups per warp -> 32 rows per warp
 constexpr int kChunk = 128;       // columns one warp step covers
@@ -507,6 +513,9 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   p.chunks = K / kChunk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M <= 16 && k_split <= 0) {
+    // preferred: the TMA-fed ring kernel; shapes it does not take fall through to the register-streaming one
+    const int rc_tma = launch_decode_tma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, st);
+    if (rc_tma != MP_ERR_UNSUPPORTED) return rc_tma;
     // cluster split-K: the smallest power of two (<= 8, the portable limit) that puts about two
     // 16-warp blocks on every SM, as long as every block keeps at least one chunk per K-warp
     const int row_blocks_ = (N + kClusterRows - 1) / kClusterRows;
@@ -545,6 +554,7 @@ extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32,
 extern "C" int mp_set_programmatic_launch(int enabled) {
   const int prev = g_programmatic_launch ? 1 : 0;
   g_programmatic_launch = enabled != 0;
+  set_decode_programmatic_launch(g_programmatic_launch);
   return prev;
 }
 
@@ -616,4 +626,9 @@ extern "C" int mp_w4a16_linear_decode_static(const void* x_f16, const void* pack
   if (pl.mb == 1) return launch_decode<1, false, 2, 8>(p, pl, st);
   if (pl.mb == 2) return launch_decode<2, false, 2, 4>(p, pl, st);
   return launch_decode<4, false, 2, 4>(p, pl, st);
+}
+
+extern "C" int mp_read_decode_error(int* value) {
+  if (!value) return MP_ERR_INVALID_ARG;
+  return read_and_clear_decode_error(value);
 }

@@ -22,17 +22,27 @@ namespace mp {
 using namespace tc;
 
 namespace w4 {
-constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;            // fp16 elements of K per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
-constexpr int kABytes = kBM * kBK * 2;   // 16 KB
-constexpr int kBBytes = kBN * kBK * 2;   // 32 KB
-constexpr int kTmemCols = 2 * kBN;
-constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + 256;
-constexpr int kThreads = 448;
+constexpr int kSubBytes = 128 * kBK * 2;   // one 128-row activation sub-tile: 16 KB
+constexpr int kBBytes = kBN * kBK * 2;     // 32 KB
+constexpr int kTmemCols = 2 * kBN;         // all 512 columns
 constexpr int kDequantWarps = 8;
+// MT = 128-row activation sub-tiles per block tile.  MT = 1: 128 x 256 tile, two accumulator
+// buffers (the epilogue of a tile overlaps the next main loop).  MT = 2: 256 x 256 tile whose two
+// accumulators share one dequantised weight tile -- half the dequant work per flop, one buffer.
+template <int MT>
+struct Cfg {
+  static constexpr int kBM = 128 * MT;
+  static constexpr int kStages = MT == 1 ? 4 : 3;
+  static constexpr int kABytes = MT * kSubBytes;
+  static constexpr int kBufs = MT == 1 ? 2 : 1;
+  static constexpr int kEpiWarps = 4 * MT;
+  static constexpr int kFirstDequantWarp = 2 + kEpiWarps;
+  static constexpr int kThreads = 32 * (2 + kEpiWarps + kDequantWarps);
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + 256;
+};
 }  // namespace w4
 
 struct W4GemmParams {
@@ -45,9 +55,14 @@ struct W4GemmParams {
   int* error_word;
 };
 
-__global__ void __launch_bounds__(w4::kThreads, 1)
+template <int MT>
+__global__ void __launch_bounds__(w4::Cfg<MT>::kThreads, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams p) {
   using namespace w4;
+  using C = Cfg<MT>;
+  constexpr int kStages = C::kStages;
+  constexpr int kABytes = C::kABytes;
+  constexpr int kBM = C::kBM;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = smem;
@@ -66,7 +81,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 4);
+      mbar_init(tempty0 + 8 * b, C::kEpiWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -93,14 +108,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t full = full0 + 8 * stage;
           mbar_arrive_expect_tx(full, kABytes);
-          tma_load_2d(smem_u32(sA + stage * kABytes), &tmap_x, full, kb * kBK, m0);
+#pragma unroll
+          for (int sub = 0; sub < MT; ++sub)
+            tma_load_2d(smem_u32(sA + stage * kABytes + sub * kSubBytes), &tmap_x, full, kb * kBK, m0 + sub * 128);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, kBM, kBN);
+      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, 128, kBN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -109,35 +126,39 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
         if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * kBN;
+        const uint32_t d_tmem = tmem_base + buf * kBN;        // MT == 2: the accumulators sit at columns 0 and 256
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * kABytes));
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * kBBytes));
 #pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-            umma_f16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);   // +32 bytes of K per step
+          for (int sub = 0; sub < MT; ++sub) {
+            const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * kABytes + sub * kSubBytes));
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk)   // +32 bytes of K per step
+              umma_f16(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+          }
           umma_commit(empty0 + 8 * stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(tfull0 + 8 * buf);
-        if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+        if (++buf == C::kBufs) { buf = 0; buf_phase ^= 1; }
       }
     }
-  } else if (warp < 6) {
-    const int quarter = warp & 3;
+  } else if (warp < C::kFirstDequantWarp) {
+    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32) belong to this warp
+    const int sub = (warp - 2) >> 2;              // which 128-row accumulator (MT == 2)
     int buf = 0;
     uint32_t buf_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
-      const int row = m_tile * kBM + quarter * 32 + lane;
+      const int row = m_tile * kBM + sub * 128 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const int n0 = n_tile * kBN;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (buf + sub) * kBN;
 #pragma unroll 1
       for (int c0 = 0; c0 < kBN; c0 += 32) {
         uint32_t r[32];
@@ -174,11 +195,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
-      if (++buf == 2) { buf = 0; buf_phase ^= 1; }
+      if (++buf == C::kBufs) { buf = 0; buf_phase ^= 1; }
     }
   } else {
     // ---- dequant producers: thread dt owns row dt of the weight tile ----
-    const int dt = threadIdx.x - 6 * 32;            // 0..255
+    const int dt = threadIdx.x - C::kFirstDequantWarp * 32;            // 0..255
     const int words_per_row = p.K >> 3;
     int stage = 0;
     uint32_t phase = 0;
@@ -246,6 +267,25 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   }
 }
 
+template <int MT>
+static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st) {
+  using C = w4::Cfg<MT>;
+  p.m_tiles = (p.M + C::kBM - 1) / C::kBM;
+  auto kern = w4a16_gemm_kernel<MT>;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  if (configured_device != device) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmem));
+    configured_device = device;
+  }
+  const long long total = (long long)p.m_tiles * p.n_tiles;
+  const int grid = (int)(total < kSmCount ? total : kSmCount);
+  kern<<<grid, C::kThreads, C::kSmem, st>>>(tx, p);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
 }  // namespace mp
 
 using namespace mp;
@@ -258,7 +298,7 @@ extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32
   if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 16)) return MP_ERR_ALIGNMENT;
   CUtensorMap tx;
   int rc = encode_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)K, (uint64_t)M,
-                                (uint64_t)K * 2, w4::kBK, w4::kBM);
+                                (uint64_t)K * 2, w4::kBK, 128);
   if (rc != MP_OK) return rc;
   W4GemmParams p{};
   p.packed = static_cast<const uint32_t*>(packed_i32);
@@ -266,20 +306,10 @@ extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32
   p.bias = static_cast<const __half*>(bias_f16);
   p.y = static_cast<__half*>(y_f16);
   p.M = M; p.N = N; p.K = K; p.group = group;
-  p.m_tiles = (M + w4::kBM - 1) / w4::kBM;
   p.n_tiles = (N + w4::kBN - 1) / w4::kBN;
   p.k_blocks = K / w4::kBK;
   p.error_word = error_word;
-  static thread_local int configured_device = -1;
-  int device = 0;
-  MP_CUDA_TRY(cudaGetDevice(&device));
-  if (configured_device != device) {
-    MP_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w4::kSmem));
-    configured_device = device;
-  }
-  const long long total = (long long)p.m_tiles * p.n_tiles;
-  const int grid = (int)(total < kSmCount ? total : kSmCount);
-  w4a16_gemm_kernel<<<grid, w4::kThreads, w4::kSmem, static_cast<cudaStream_t>(stream)>>>(tx, p);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M > 128) return launch_w4_gemm<2>(tx, p, st);
+  return launch_w4_gemm<1>(tx, p, st);
 }

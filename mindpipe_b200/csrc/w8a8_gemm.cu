@@ -214,7 +214,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               const __half g16 = f2h(static_cast<float>(static_cast<int>(rg[j + jj])) * sa * sg);
               const __half u16 = f2h(static_cast<float>(static_cast<int>(ru[j + jj])) * sa * su);
               const float gf = h2f(g16);
-              const __half s16 = f2h(gf / (1.0f + expf(-gf)));
+              // silu in fp32 with the hardware exp2 / reciprocal: the result is rounded to fp16 right
+              // away (as the reference does), which hides their ~2 ulp fp32 error
+              const __half s16 = f2h(__fdividef(gf, 1.0f + __expf(-gf)));
               const __half h16 = hmul_t(s16, u16);
               h2v[jj] = h16;
               hmax = fmaxf(hmax, fabsf(h2f(h16)));
@@ -329,7 +331,8 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
-                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                         bool swizzle_128b) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return MP_ERR_CUDA;
   cuuint64_t dims[2] = {inner, outer};
@@ -337,7 +340,8 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = 100000 + static_cast<int>(r);
     return MP_ERR_CUDA;

@@ -251,6 +251,11 @@ def _error_word(device: torch.device) -> torch.Tensor:
 def check_device_errors(device=None) -> None:
     """Synchronise and raise if any kernel reported a device-side wait that gave up."""
     torch.cuda.synchronize(device)
+    import ctypes
+    flag = ctypes.c_int(0)
+    _lib.check(_lib.load().mp_read_decode_error(ctypes.byref(flag)), "read_decode_error")
+    if flag.value != 0:
+        raise _lib.MindPipeKernelError("a bounded wait inside a decode kernel timed out")
     for idx, w in _err_words.items():
         if int(w.item()) != 0:
             w.zero_()
