@@ -173,6 +173,19 @@ int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i8, void* sc
                            void* fake_f16, mp_stream_t stream);
 
 /*
+ * Residual add + RMSNorm + per-token int8 quantisation in one pass:
+ *   residual <- f16(x + residual);  y = f16(f16(residual * rsqrt(mean(residual^2) + eps)) * gamma);
+ *   (q, scale) = per-token absmax int8 of y (arithmetic of mp_act_quant_per_token).
+ * Stands in for torch_npu.npu_add_rms_norm_dynamic_quant, whose (codes, scale)
+ * pair the W8A8 linear takes as a tuple input
+ * (acceleration/runtime_patches/vllm_ascend.patch:754-770, 3945-3962).  The
+ * reference has no CPU statement of this fused op; the RMSNorm arithmetic is
+ * that of the Hugging Face Llama RMSNorm the models use.  H % 8 == 0, H <= 16384.
+ */
+int mp_add_rmsnorm_quant(const void* x_f16, void* residual_f16, const void* gamma_f16, float eps, int M,
+                         int H, void* q_i8, void* scale_f32, mp_stream_t stream);
+
+/*
  * y[M,N] = f16( (qx[M,K] . w[N,K]^T as int32) * x_scale[m] * w_scale[n] (+ bias[n]) )
  * on the int8 tensor cores (tcgen05 kind::i8, int32 accumulators in TMEM).
  * Stands in for torch_npu.npu_quant_matmul as called by

@@ -36,6 +36,7 @@ SIGNATURES = {
     "mp_set_programmatic_launch": (_I, [_I]),
     "mp_read_decode_error": (_I, [_P]),
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
+    "mp_add_rmsnorm_quant": (_I, [_P, _P, _P, ctypes.c_float, _I, _I, _P, _P, _P]),
     "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_w8a8_gemm_i32": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_moe_router_topk": (_I, [_P, _I, _I, _I, _P, _P, _P]),

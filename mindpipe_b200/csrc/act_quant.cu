@@ -100,9 +100,128 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   }
 }
 
+// Residual add + RMSNorm + per-token int8 quant in one pass over the row: the
+// torch_npu.npu_add_rms_norm_dynamic_quant call that feeds the (codes, scale) tuple to
+// the W8A8 linear (acceleration/runtime_patches/vllm_ascend.patch:754-770).
+//   r   = f16(x + residual)                      (written back as the new residual)
+//   y   = f16( f16(r * rsqrt(mean(r^2) + eps)) * gamma )   (RMSNorm as HF Llama computes it)
+//   q,s = per-token absmax int8 of y             (same arithmetic as act_quant_kernel)
+template <int THREADS, int NV>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_quant_kernel(const __half* __restrict__ x, __half* __restrict__ residual,
+                         const __half* __restrict__ gamma, float eps, int H, int8_t* __restrict__ q,
+                         float* __restrict__ scale) {
+  __shared__ float s_red[THREADS / 32];
+  __shared__ float s_bcast;
+  const int row = blockIdx.x;
+  const int chunks = H >> 3;
+  const __half* xr = x + (size_t)row * H;
+  __half* rr = residual + (size_t)row * H;
+  auto block_reduce = [&](float v, bool is_max) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, other) : v + other;
+    }
+    __syncthreads();                               // s_red may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float w = threadIdx.x < THREADS / 32 ? s_red[threadIdx.x] : 0.0f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, w, o);
+        w = is_max ? fmaxf(w, other) : w + other;
+      }
+      if (threadIdx.x == 0) s_bcast = w;
+    }
+    __syncthreads();
+    return s_bcast;
+  };
+  uint4 held[NV];
+  float sumsq = 0.0f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * THREADS;
+    held[v] = make_uint4(0, 0, 0, 0);
+    if (c < chunks) {
+      const uint4 a = *reinterpret_cast<const uint4*>(xr + c * 8);
+      const uint4 b = *reinterpret_cast<const uint4*>(rr + c * 8);
+      const __half* ha = reinterpret_cast<const __half*>(&a);
+      const __half* hb = reinterpret_cast<const __half*>(&b);
+      __align__(16) __half hs[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        hs[j] = hadd_t(ha[j], hb[j]);
+        const float f = h2f(hs[j]);
+        sumsq += f * f;
+      }
+      held[v] = *reinterpret_cast<uint4*>(hs);
+      *reinterpret_cast<uint4*>(rr + c * 8) = held[v];           // new residual
+    }
+  }
+  const float inv = rsqrtf(block_reduce(sumsq, false) / static_cast<float>(H) + eps);
+  float amax = 0.0f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * THREADS;
+    if (c < chunks) {
+      const uint4 gw = *reinterpret_cast<const uint4*>(gamma + c * 8);
+      const __half* hg = reinterpret_cast<const __half*>(&gw);
+      __half* hs = reinterpret_cast<__half*>(&held[v]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        hs[j] = hmul_t(f2h(h2f(hs[j]) * inv), hg[j]);
+        amax = fmaxf(amax, fabsf(h2f(hs[j])));
+      }
+    }
+  }
+  const float eps_q = h2f(f2h(1e-5f));
+  const float sf = h2f(f2h(__fdiv_rn(fmaxf(block_reduce(amax, true), eps_q), 127.0f)));
+  if (threadIdx.x == 0) scale[row] = sf;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * THREADS;
+    if (c < chunks) {
+      const __half* hs = reinterpret_cast<const __half*>(&held[v]);
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hs[j]), sf)))))) & 0xFFu) << (8 * j);
+        w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hs[j + 4]), sf)))))) & 0xFFu) << (8 * j);
+      }
+      *reinterpret_cast<uint2*>(q + (size_t)row * H + c * 8) = make_uint2(w0, w1);
+    }
+  }
+}
+
 }  // namespace mp
 
 using namespace mp;
+
+extern "C" int mp_add_rmsnorm_quant(const void* x_f16, void* residual_f16, const void* gamma_f16, float eps, int M,
+                                    int H, void* q_i8, void* scale_f32, mp_stream_t stream) {
+  if (!x_f16 || !residual_f16 || !gamma_f16 || !q_i8 || !scale_f32 || M <= 0 || H <= 0) return MP_ERR_INVALID_ARG;
+  if (H % 8 != 0 || H > 16384) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || !aligned(residual_f16, 16) || !aligned(gamma_f16, 16) || !aligned(q_i8, 8)) return MP_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half* x = static_cast<const __half*>(x_f16);
+  __half* r = static_cast<__half*>(residual_f16);
+  const __half* g = static_cast<const __half*>(gamma_f16);
+  int8_t* q = static_cast<int8_t*>(q_i8);
+  float* sc = static_cast<float*>(scale_f32);
+  if (H <= 2048) {
+    add_rmsnorm_quant_kernel<256, 1><<<M, 256, 0, st>>>(x, r, g, eps, H, q, sc);
+  } else if (H <= 4096) {
+    add_rmsnorm_quant_kernel<256, 2><<<M, 256, 0, st>>>(x, r, g, eps, H, q, sc);
+  } else if (H <= 8192) {
+    add_rmsnorm_quant_kernel<512, 2><<<M, 512, 0, st>>>(x, r, g, eps, H, q, sc);
+  } else {
+    add_rmsnorm_quant_kernel<512, 4><<<M, 512, 0, st>>>(x, r, g, eps, H, q, sc);
+  }
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
 
 extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i8, void* scale_f32,
                                       void* fake_f16, mp_stream_t stream) {

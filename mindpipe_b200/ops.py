@@ -406,3 +406,25 @@ def gather_rows(src, row_map, out=None):
         st = _lib.load().mp_gather_rows(src.data_ptr(), m.data_ptr(), m.numel(), row_bytes, dst.data_ptr(), _stream())
         _lib.check(st, "gather_rows", rows=m.numel(), row_bytes=row_bytes)
     return dst
+
+
+def add_rmsnorm_quant(x, residual, gamma, eps: float = 1e-5):
+    """``residual += x`` (fp16), RMSNorm with ``gamma``, per-token int8 quant.
+
+    Returns ``(codes int8[...,H], scale f32[...])`` -- the tuple input of the W8A8
+    linear -- and updates ``residual`` in place.
+    """
+    xt = _req(x, "x", torch.float16)
+    rt = _req(residual, "residual", torch.float16)
+    g = _req(gamma, "gamma", torch.float16, 1)
+    h = xt.shape[-1]
+    if rt.shape != xt.shape or g.numel() != h:
+        raise ValueError("x, residual and gamma shapes disagree")
+    m = xt.numel() // h
+    q = torch.empty(xt.shape, dtype=torch.int8, device=xt.device)
+    s = torch.empty(xt.shape[:-1], dtype=torch.float32, device=xt.device)
+    if m:
+        st = _lib.load().mp_add_rmsnorm_quant(xt.data_ptr(), rt.data_ptr(), g.data_ptr(), float(eps), m, h, q.data_ptr(),
+                                              s.data_ptr(), _stream())
+        _lib.check(st, "add_rmsnorm_quant", M=m, H=h)
+    return q, s

@@ -53,3 +53,28 @@ def test_act_quant_3d_and_empty():
     assert q.shape == (2, 3, 256) and s.shape == (2, 3)
     q, s, _ = ops.act_quant_per_token(torch.zeros(0, 64, dtype=torch.float16, device="cuda"))
     assert q.shape == (0, 64) and s.shape == (0,)
+
+
+@pytest.mark.parametrize("m,h", [(5, 256), (33, 4096), (4, 8192), (2, 14336)])
+def test_add_rmsnorm_quant_vs_composed_oracle(m, h):
+    """Fused residual add + RMSNorm + quant.  The new residual is bit-exact; codes may differ by one
+    step where the fp32 reduction order moves rsqrt by an ulp (the reference has no CPU statement
+    of this fused op, so the oracle is a composition of its pieces)."""
+    from mindpipe_b200 import ops
+    x = synth.normal_activation(m, h, seed=1, index=1).numpy()
+    res = synth.outlier_activation(m, h, seed=1, index=2).numpy()
+    gamma = (1.0 + 0.1 * synth.normal_activation(1, h, seed=1, index=3).numpy()[0]).astype(np.float16)
+    res_d = dev(res.copy())
+    q, s = ops.add_rmsnorm_quant(dev(x), res_d, dev(gamma), 1e-5)
+    r_ref, codes, sc = O.add_rmsnorm_quant(x, res, gamma, 1e-5)
+    assert np.array_equal(bits(res_d.cpu().numpy()), bits(r_ref))
+    diff = np.abs(q.cpu().numpy().astype(np.int32) - codes.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-3
+    assert np.allclose(s.cpu().numpy(), sc.astype(np.float32).reshape(-1), rtol=2e-3)
+    # the pair feeds the W8A8 linear directly
+    from mindpipe_b200.modules import SmoothQuantLinear
+    lin = torch.nn.Linear(h, 64, bias=False).half().cuda()
+    mod = SmoothQuantLinear.from_float(lin)
+    y = mod((q, s))
+    assert y.shape == (m, 64)
+    ops.check_device_errors()
