@@ -217,9 +217,15 @@ def measure_moe(world, rank, dev, dist, iters=5):
     hs = synth.normal_activation(shape.tokens, shape.hidden, seed=0)[rank * t_loc:(rank + 1) * t_loc].to(dev)
     logits = synth.router_logits(shape.tokens, shape.num_experts, seed=0)[rank * t_loc:(rank + 1) * t_loc].to(dev)
     idx, wts = ops.moe_router_topk(logits, shape.top_k)
+    exchange = "none"
     if world > 1:
-        from mindpipe_b200.expert_parallel import ExpertParallelMoE
-        layer = ExpertParallelMoE(mod, shape.num_experts)
+        from mindpipe_b200.expert_parallel import ExpertParallelMoE, SymmetricExpertParallelMoE
+        try:
+            layer = SymmetricExpertParallelMoE(mod, shape.num_experts, max_tokens_per_rank=t_loc, top_k=shape.top_k)
+            exchange = "peer-memory pull/push kernels (symmetric memory, no host sync)"
+        except Exception as err:      # no peer mapping available: NCCL all-to-all with host-side split sizes
+            layer = ExpertParallelMoE(mod, shape.num_experts)
+            exchange = f"nccl all_to_all_single ({type(err).__name__})"
     else:
         layer = mod
     for _ in range(2):
@@ -242,7 +248,7 @@ def measure_moe(world, rank, dev, dist, iters=5):
         2 * (shape.top_k * shape.tokens) * shape.ffn * shape.hidden
     return {"config": "mixtral-8x7b-shaped layer, 8192 tokens, top-2, experts sharded over the ranks (all-to-all)",
             "ms_per_layer": ms, "tokens_per_s": shape.tokens / (ms * 1e-3), "int8_tops": int8_ops / (ms * 1e-3) / 1e12,
-            "n_gpus": world}
+            "n_gpus": world, "exchange": exchange}
 
 
 def workload_config():

@@ -272,6 +272,42 @@ int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk
                    const void* topk_weights_f16, int T, int H, int k, void* out_f16, mp_stream_t stream);
 
 /*
+ * Expert-parallel exchange over peer-mapped (symmetric) memory, without a host
+ * round trip -- the device-driven form of the runtime's all-to-all token
+ * dispatcher / combiner (TokenDispatcherWithAll2AllV,
+ * acceleration/runtime_patches/vllm_ascend.patch:3228-3236).  Every *_ptrs
+ * argument is a host array of `world` device pointers, entry s being rank s's
+ * buffer as mapped into this process (entry `rank` is the local buffer).
+ *
+ * mp_peer_barrier   cross-rank barrier on the stream: stores `epoch` (must grow by
+ *                   one per call, same sequence on every rank) into slot `rank`
+ *                   of every peer's flag array (uint32[world], zero at start) and
+ *                   waits, for at most 2 s, until all local slots reached it; a
+ *                   timeout sets *error_word = 4 and returns.
+ * mp_moe_ep_plan    reads every peer's routing plan (as written by
+ *                   mp_moe_route_gather_quant over all `num_experts` experts)
+ *                   and lays out this rank's expert-sorted buffer: xplan_i32
+ *                   (mp_moe_ep_plan_ints ints) starts with the plan
+ *                   mp_moe_expert_stage takes.
+ * mp_moe_ep_pull    copies the rows this rank's experts own out of the peers'
+ *                   routed buffers (int8 rows + fp32 scales) into sorted order.
+ * mp_moe_ep_push    stores each result row into its source rank's result buffer
+ *                   at the row's original position.
+ * capacity_rows: rows of the expert-sorted buffers (multiple of 128; an upper
+ * bound, e.g. mp_moe_padded_rows(local experts, world * tokens * k)).
+ */
+int mp_peer_barrier(const void* const* peer_flag_ptrs, int world, int rank, unsigned int epoch,
+                    int* error_word, mp_stream_t stream);
+size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
+int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
+                   int capacity_rows, void* xplan_i32, mp_stream_t stream);
+int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,
+                   int world, int num_local_experts, int capacity_rows, int H, void* q_sorted_i8,
+                   void* scale_sorted_f32, mp_stream_t stream);
+int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                   int capacity_rows, int H, const void* const* peer_back_ptrs, mp_stream_t stream);
+
+/*
  * dst row i = src row row_map[i] (rows of row_bytes bytes; 4, or a multiple of
  * 16); a negative map entry gives a zero row.  The row permutation an
  * expert-parallel rank applies to what its peers sent (source-major) to get

@@ -47,6 +47,11 @@ SIGNATURES = {
     "mp_moe_expert_stage": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
     "mp_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_gather_rows": (_I, [_P, _P, _I, _I, _P, _P]),
+    "mp_peer_barrier": (_I, [_P, _I, _I, ctypes.c_uint, _P, _P]),
+    "mp_moe_ep_plan_ints": (_Z, [_I, _I, _I]),
+    "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
+    "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "mp_moe_ep_push": (_I, [_P, _P, _I, _I, _I, _I, _P, _P]),
 }
 
 

@@ -1,0 +1,219 @@
+// Expert-parallel MoE exchange over NVLink peer memory, driven from the device.
+//
+// Every rank keeps its routed int8 rows, their scales, its routing plan and a
+// result buffer in symmetric memory (mapped by every peer).  The dispatch is a
+// PULL: after a cross-rank barrier, each rank reads its peers' per-expert row
+// counts, lays out its expert-sorted buffer, and copies the rows it owns
+// straight out of the peers' routed buffers with plain peer loads.  The return
+// is a PUSH: after the expert stage each result row is stored straight into
+// the source rank's result buffer at the row's original position, so the
+// weighted combine at home needs no re-ordering.  Row counts never visit the
+// host, so a layer is a fixed sequence of launches with no synchronisation.
+//
+// Role in the reference: the all-to-all token dispatcher / combiner of the
+// runtime (TokenDispatcherWithAll2AllV, acceleration/runtime_patches/
+// vllm_ascend.patch:3228-3236; int8 payload as at :1668-1682).
+//
+// The barrier is a bounded wait: each rank stores the call's epoch into a flag
+// slot on every peer and polls its own slots; if a peer does not show up within
+// the limit the kernel records an error word and returns (no trap, no endless
+// spin).  One process per GPU: the waiting kernels of different ranks run on
+// different devices.  Only plain peer loads / stores are used.
+#include "common.cuh"
+
+namespace mp {
+
+constexpr int kMaxRanks = 16;
+constexpr int kEpTile = 128;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+__device__ __forceinline__ uint64_t ep_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// flags[r] on rank p is written by rank r.  Thread r < world: publish, then wait for peer r.
+__global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int epoch, int* error_word) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();                                           // everything this GPU wrote so far is visible
+  unsigned int* remote = static_cast<unsigned int*>(peer_flags.p[r]) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const unsigned int* mine = static_cast<const unsigned int*>(peer_flags.p[rank]) + r;
+  const uint64_t t0 = ep_timer_ns();
+  for (unsigned int it = 0;; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int>(v - epoch) >= 0) break;                    // peer r reached this epoch (wrap-safe)
+    if ((it & 0xFF) == 0xFF && ep_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, report, return
+      if (error_word) atomicExch(error_word, 4);
+      break;
+    }
+  }
+  __threadfence_system();
+}
+
+// Extended plan of the receiving rank (ints):
+//   [0, plan_std)                       the standard plan the expert stage reads
+//                                       (counts[El] | cursors[El] | seg[El+1] | num_tiles | tile_expert[...])
+//   ext + e*(W+1) + s                   cum[e][s]: rows of local expert e that come from ranks < s
+//   ext + El*(W+1) + e*W + s            src_seg[e][s]: first row of that segment in rank s's routed buffer
+__global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_total, int e_loc, int max_tiles,
+                               int ext, int* __restrict__ xplan) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int* counts = xplan;
+  int* cursors = xplan + e_loc;
+  int* seg = xplan + 2 * e_loc;
+  int* num_tiles = xplan + 3 * e_loc + 1;
+  int* tile_expert = xplan + 3 * e_loc + 2;
+  int* cum = xplan + ext;
+  int* src_seg = xplan + ext + e_loc * (world + 1);
+  int off = 0, tiles = 0;
+  for (int e = 0; e < e_loc; ++e) {
+    const int ge = rank * e_loc + e;
+    int total = 0;
+    for (int s = 0; s < world; ++s) {
+      const int* pp = static_cast<const int*>(peer_plans.p[s]);     // rank s's plan over all e_total experts
+      cum[e * (world + 1) + s] = total;
+      total += pp[ge];                                               // counts[ge]
+      src_seg[e * world + s] = pp[2 * e_total + ge];                 // seg_offsets[ge]
+    }
+    cum[e * (world + 1) + world] = total;
+    counts[e] = total;
+    cursors[e] = 0;
+    seg[e] = off;
+    const int nt = (total + kEpTile - 1) / kEpTile;
+    for (int i = 0; i < nt && tiles < max_tiles; ++i) tile_expert[tiles++] = e;
+    off += nt * kEpTile;
+  }
+  seg[e_loc] = off;
+  *num_tiles = tiles;
+}
+
+// Which (expert, source rank, row inside the source segment) does sorted row i hold?  -1 = padding.
+__device__ __forceinline__ bool ep_locate(const int* xplan, int world, int e_loc, int ext, int i, int& s_out,
+                                          int& src_row) {
+  const int* seg = xplan + 2 * e_loc;
+  const int* cum = xplan + ext;
+  const int* src_seg = xplan + ext + e_loc * (world + 1);
+  int e = 0;
+  while (e + 1 < e_loc && i >= seg[e + 1]) ++e;
+  const int j = i - seg[e];
+  if (j >= cum[e * (world + 1) + world]) return false;
+  int s = 0;
+  while (s + 1 < world && j >= cum[e * (world + 1) + s + 1]) ++s;
+  s_out = s;
+  src_row = src_seg[e * world + s] + (j - cum[e * (world + 1) + s]);
+  return true;
+}
+
+// Sorted row i <- peer row (int8 codes and fp32 scale).  Blocks stride over the rows in use.
+__global__ void __launch_bounds__(256)
+ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xplan, int world, int e_loc, int ext,
+               int vec_per_row, uint4* __restrict__ q_sorted, float* __restrict__ s_sorted) {
+  const int rows = xplan[2 * e_loc + e_loc];                        // seg[e_loc]: padded rows in use
+  for (int i = blockIdx.x; i < rows; i += gridDim.x) {
+    int s, src;
+    const bool real = ep_locate(xplan, world, e_loc, ext, i, s, src);
+    if (!real) {
+      if (threadIdx.x == 0) s_sorted[i] = 0.0f;                     // padding row: neutralised by a zero scale
+      continue;
+    }
+    const uint4* from = static_cast<const uint4*>(peer_q.p[s]) + (size_t)src * vec_per_row;
+    for (int v = threadIdx.x; v < vec_per_row; v += 256) q_sorted[(size_t)i * vec_per_row + v] = from[v];
+    if (threadIdx.x == 0) s_sorted[i] = static_cast<const float*>(peer_scale.p[s])[src];
+  }
+}
+
+// Result row i -> the source rank's result buffer, at the row's original position.
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const uint4* __restrict__ d_sorted, const int* __restrict__ xplan, int world, int e_loc, int ext,
+               int vec_per_row, PeerPtrs peer_back) {
+  const int rows = xplan[2 * e_loc + e_loc];
+  for (int i = blockIdx.x; i < rows; i += gridDim.x) {
+    int s, src;
+    if (!ep_locate(xplan, world, e_loc, ext, i, s, src)) continue;
+    uint4* to = static_cast<uint4*>(peer_back.p[s]) + (size_t)src * vec_per_row;
+    for (int v = threadIdx.x; v < vec_per_row; v += 256) to[v] = d_sorted[(size_t)i * vec_per_row + v];
+  }
+}
+
+static int fill_peers(PeerPtrs& dst, const void* const* src, int world) {
+  if (!src || world <= 0 || world > kMaxRanks) return MP_ERR_INVALID_ARG;
+  for (int i = 0; i < kMaxRanks; ++i) dst.p[i] = i < world ? const_cast<void*>(src[i]) : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (!dst.p[i]) return MP_ERR_INVALID_ARG;
+  return MP_OK;
+}
+
+}  // namespace mp
+
+using namespace mp;
+
+extern "C" int mp_peer_barrier(const void* const* peer_flag_ptrs, int world, int rank, unsigned int epoch,
+                               int* error_word, mp_stream_t stream) {
+  PeerPtrs pf;
+  int rc = fill_peers(pf, peer_flag_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, world, rank, epoch, error_word);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows) {
+  const int max_tiles = capacity_rows / kEpTile;
+  const size_t std_ints = (size_t)3 * num_local_experts + 2 + max_tiles;
+  return std_ints + (size_t)num_local_experts * (world + 1) + (size_t)num_local_experts * world;
+}
+
+extern "C" int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
+                              int capacity_rows, void* xplan_i32, mp_stream_t stream) {
+  PeerPtrs pp;
+  int rc = fill_peers(pp, peer_plan_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (!xplan_i32 || num_experts <= 0 || num_experts % world != 0 || capacity_rows <= 0 || capacity_rows % kEpTile != 0)
+    return MP_ERR_INVALID_ARG;
+  const int e_loc = num_experts / world;
+  const int max_tiles = capacity_rows / kEpTile;
+  const int ext = 3 * e_loc + 2 + max_tiles;
+  ep_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, rank, num_experts, e_loc, max_tiles, ext,
+                                                                  static_cast<int*>(xplan_i32));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,
+                              int world, int num_local_experts, int capacity_rows, int H, void* q_sorted_i8,
+                              void* scale_sorted_f32, mp_stream_t stream) {
+  PeerPtrs pq, ps;
+  int rc = fill_peers(pq, peer_q_ptrs, world);
+  if (rc != MP_OK) return rc;
+  rc = fill_peers(ps, peer_scale_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (!xplan_i32 || !q_sorted_i8 || !scale_sorted_f32 || H <= 0 || H % 16 != 0) return MP_ERR_INVALID_ARG;
+  const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
+  ep_pull_kernel<<<4 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pq, ps, static_cast<const int*>(xplan_i32), world, num_local_experts, ext, H / 16,
+      static_cast<uint4*>(q_sorted_i8), static_cast<float*>(scale_sorted_f32));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                              int capacity_rows, int H, const void* const* peer_back_ptrs, mp_stream_t stream) {
+  PeerPtrs pb;
+  int rc = fill_peers(pb, peer_back_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (!d_sorted_f16 || !xplan_i32 || H <= 0 || H % 8 != 0) return MP_ERR_INVALID_ARG;
+  const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
+  ep_push_kernel<<<4 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(d_sorted_f16), static_cast<const int*>(xplan_i32), world, num_local_experts, ext,
+      H / 8, pb);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}

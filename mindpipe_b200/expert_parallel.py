@@ -170,3 +170,109 @@ class ExpertParallelMoE(torch.nn.Module):
         dist.all_to_all_single(back[:n_send], d_recv, plan.send_splits, plan.recv_splits, group=self.group)
         out = ops.moe_combine(back, routing.dest_row, ids, w, t)
         return out.reshape(shape)
+
+
+class SymmetricExpertParallelMoE(torch.nn.Module):
+    """Expert-parallel W8A8 MoE whose dispatch and return run over NVLink peer memory, driven
+    entirely from the device: no row count ever visits the host, so a forward is a fixed sequence
+    of stream-ordered launches (route -> barrier -> plan -> pull -> expert stage -> push ->
+    barrier -> combine).
+
+    Each rank keeps its routing plan, routed int8 rows, their scales and a result buffer in one
+    symmetric allocation that every peer maps (``torch.distributed._symmetric_memory``).  Peers
+    *pull* the rows their experts own and *push* the results back to the row's original position.
+    ``max_tokens_per_rank`` fixes the buffer sizes; the expert-sorted buffers are sized for the
+    worst case (every token of every rank routed to this rank).
+    """
+
+    def __init__(self, experts, num_experts: int, max_tokens_per_rank: int, top_k: int = 2, group=None):
+        super().__init__()
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self.experts = experts
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.num_experts = int(num_experts)
+        self.e_loc = self.num_experts // self.world
+        self.top_k = int(top_k)
+        if tuple(experts.expert_range) != expert_partition(self.num_experts, self.world)[self.rank]:
+            raise ValueError("experts.expert_range does not match this rank's partition")
+        lib = _lib.load()
+        dev = experts.gate_up_proj.device
+        self.hidden = experts.hidden_dim
+        self.inter = experts.intermediate_dim
+        self.max_tokens = int(max_tokens_per_rank)
+        entries = self.max_tokens * self.top_k
+        self.r_cap = lib.mp_moe_padded_rows(self.num_experts, entries)            # rows of this rank's routed buffers
+        self.sorted_cap = lib.mp_moe_padded_rows(self.e_loc, self.world * entries)  # rows of the expert-sorted buffers
+        plan_ints = lib.mp_moe_plan_ints(self.num_experts, entries)
+        al = lambda n: (n + 255) // 256 * 256
+        self.off_flags = 0
+        self.off_plan = 256
+        self.off_scale = self.off_plan + al(plan_ints * 4)
+        self.off_q = self.off_scale + al(self.r_cap * 4)
+        self.off_back = self.off_q + al(self.r_cap * self.hidden)
+        total = self.off_back + al(self.r_cap * self.hidden * 2)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize(dev)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        dist.barrier(self.group)                                                   # every rank zeroed its flags
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+
+        def ptrs(off):
+            import ctypes
+            return (ctypes.c_void_p * self.world)(*[b + off for b in bases])
+
+        self.p_flags, self.p_plan = ptrs(self.off_flags), ptrs(self.off_plan)
+        self.p_scale, self.p_q, self.p_back = ptrs(self.off_scale), ptrs(self.off_q), ptrs(self.off_back)
+        v = self.buf
+        self.plan = v[self.off_plan:self.off_plan + plan_ints * 4].view(torch.int32)
+        self.routed_scale = v[self.off_scale:self.off_scale + self.r_cap * 4].view(torch.float32)
+        self.routed_q = v[self.off_q:self.off_q + self.r_cap * self.hidden].view(torch.int8).view(self.r_cap, self.hidden)
+        self.back = v[self.off_back:self.off_back + self.r_cap * self.hidden * 2].view(torch.float16).view(
+            self.r_cap, self.hidden)
+        self.xplan = torch.zeros(lib.mp_moe_ep_plan_ints(self.world, self.e_loc, self.sorted_cap), dtype=torch.int32,
+                                 device=dev)
+        self.q_sorted = torch.empty((self.sorted_cap, self.hidden), dtype=torch.int8, device=dev)
+        self.s_sorted = torch.empty(self.sorted_cap, dtype=torch.float32, device=dev)
+        self.epoch = 0
+
+    def _barrier(self):
+        from . import _lib, ops
+        self.epoch += 1
+        st = _lib.load().mp_peer_barrier(self.p_flags, self.world, self.rank, self.epoch,
+                                         ops._error_word(self.buf.device).data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+        _lib.check(st, "peer_barrier", world=self.world, rank=self.rank)
+
+    @torch.no_grad()
+    def forward(self, hidden_states, top_k_index, top_k_weights):
+        from . import _lib, ops
+        lib = _lib.load()
+        shape = hidden_states.shape
+        hs = hidden_states.reshape(-1, shape[-1]).contiguous()
+        t, h = hs.shape
+        if t > self.max_tokens or h != self.hidden:
+            raise ValueError(f"{t} tokens x {h} exceed the buffers sized at construction "
+                             f"({self.max_tokens} x {self.hidden})")
+        ids = top_k_index.reshape(t, -1).to(torch.int32).contiguous()
+        w = top_k_weights.reshape(t, -1).to(torch.float16).contiguous()
+        stream = torch.cuda.current_stream().cuda_stream
+        routing = ops.moe_route_gather_quant(hs, ids, 0, self.num_experts,
+                                             out=(self.plan, self.routed_q, self.routed_scale))
+        self._barrier()                                    # every rank's routed rows and plan are in place
+        _lib.check(lib.mp_moe_ep_plan(self.p_plan, self.world, self.rank, self.num_experts, self.sorted_cap,
+                                      self.xplan.data_ptr(), stream), "moe_ep_plan")
+        _lib.check(lib.mp_moe_ep_pull(self.p_q, self.p_scale, self.xplan.data_ptr(), self.world, self.e_loc,
+                                      self.sorted_cap, h, self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), stream),
+                   "moe_ep_pull")
+        ex = self.experts
+        d_sorted = ops.moe_expert_stage(self.q_sorted, self.s_sorted, self.xplan, self.e_loc, ex.gate_up_proj,
+                                        ex.gate_up_proj_scale, ex.down_proj, ex.down_proj_scale)
+        _lib.check(lib.mp_moe_ep_push(d_sorted.data_ptr(), self.xplan.data_ptr(), self.world, self.e_loc,
+                                      self.sorted_cap, h, self.p_back, stream), "moe_ep_push")
+        self._barrier()                                    # every result row has landed at home
+        out = ops.moe_combine(self.back, routing.dest_row, ids, w, t)
+        return out.reshape(shape)

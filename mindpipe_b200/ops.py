@@ -331,8 +331,10 @@ class MoeRouting:
         return self.plan[2 * e: 3 * e + 1]
 
 
-def moe_route_gather_quant(hidden, top_k_index, expert_lo: int, expert_hi: int) -> MoeRouting:
-    """Sort the routed rows of experts ``[expert_lo, expert_hi)`` by expert and quantise them per token."""
+def moe_route_gather_quant(hidden, top_k_index, expert_lo: int, expert_hi: int, out=None) -> MoeRouting:
+    """Sort the routed rows of experts ``[expert_lo, expert_hi)`` by expert and quantise them per token.
+
+    ``out = (plan, routed_q, routed_scale)`` writes into caller buffers (e.g. symmetric memory)."""
     hs = _req(hidden, "hidden_states", torch.float16, 2)
     ids = _req(top_k_index, "top_k_index", torch.int32, 2)
     t, h = hs.shape
@@ -342,10 +344,15 @@ def moe_route_gather_quant(hidden, top_k_index, expert_lo: int, expert_hi: int) 
     e = expert_hi - expert_lo
     lib = _lib.load()
     padded = lib.mp_moe_padded_rows(e, t * k)
-    plan = torch.empty(lib.mp_moe_plan_ints(e, t * k), dtype=torch.int32, device=hs.device)
     dest = torch.empty(t * k, dtype=torch.int32, device=hs.device)
-    rq = torch.empty((padded, h), dtype=torch.int8, device=hs.device)
-    rs = torch.empty(padded, dtype=torch.float32, device=hs.device)
+    if out is None:
+        plan = torch.empty(lib.mp_moe_plan_ints(e, t * k), dtype=torch.int32, device=hs.device)
+        rq = torch.empty((padded, h), dtype=torch.int8, device=hs.device)
+        rs = torch.empty(padded, dtype=torch.float32, device=hs.device)
+    else:
+        plan, rq, rs = out
+        if plan.numel() < lib.mp_moe_plan_ints(e, t * k) or rq.shape[0] < padded or rs.numel() < padded:
+            raise ValueError("routing buffers are too small for this many tokens")
     st = lib.mp_moe_route_gather_quant(hs.data_ptr(), ids.data_ptr(), t, h, k, expert_lo, expert_hi, plan.data_ptr(),
                                        dest.data_ptr(), rq.data_ptr(), rs.data_ptr(), _stream())
     _lib.check(st, "moe_route_gather_quant", T=t, H=h, k=k, experts=(expert_lo, expert_hi))
@@ -369,7 +376,7 @@ def moe_expert_stage(routed_q, routed_scale, plan, num_local_experts: int, w13_q
         raise ValueError("expert weight / routed buffer shapes are inconsistent")
     lib = _lib.load()
     nbytes = lib.mp_moe_expert_stage_workspace_bytes(padded, i)
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=rq.device)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=rq.device)      # served by torch's caching allocator
     d = torch.empty((padded, h), dtype=torch.float16, device=rq.device)
     st = lib.mp_moe_expert_stage(rq.data_ptr(), rs.data_ptr(), pl.data_ptr(), padded, h, i, e, w13.data_ptr(),
                                  s13.data_ptr(), w2.data_ptr(), s2.data_ptr(), d.data_ptr(), ws.data_ptr(), nbytes,
