@@ -209,6 +209,31 @@ int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const void* w_i8, c
 int mp_w8a8_gemm_i32(const void* qx_i8, const void* w_i8, void* acc_i32, int M, int N, int K,
                      int* error_word, mp_stream_t stream);
 
+/*
+ * OmniQuant-style W8A8: dynamic ASYMMETRIC 8-bit quantisation of each row (per token for
+ * activations, per output channel for weights) to unsigned codes,
+ *   s = clamp(f16(f16(max - min) / 255), 1e-5, 1e4), zp = rint(clamp(f16(-min / s), +-1e4)),
+ *   u = clamp(f16(rint(f16(x / s)) + zp), 0, 255),
+ * the arithmetic of UniformAffineQuantizer.per_token_dynamic_calibration + fake_quant
+ * (algorithm/quantization/ptq/omniquant/source/omniquant/quantizer.py:124-150, 89-111).
+ * Outputs: q_u8 [M,K], scale_f32 [M], zero_f32 [M] (integer valued), rowsum_i32 [M] = sum of the
+ * row's codes; fake_f16 (optional) = f16(f16(u - zp) * s).  K % 8 == 0.
+ */
+int mp_affine_quant_per_row(const void* x_f16, int M, int K, void* q_u8, void* scale_f32, void* zero_f32,
+                            void* rowsum_i32, void* fake_f16, mp_stream_t stream);
+
+/*
+ * y = f16( sum_k (qx - zx)(qw - zw) * sx[m] * sw[n] (+bias) ) with the sum evaluated exactly as
+ * acc - zw*sum(qx) - zx*sum(qw) + K*zx*zw from a u8 x u8 -> int32 tensor-core product
+ * (tcgen05 kind::i8, unsigned operands).  The real-int twin of QuantLinear.forward
+ * (algorithm/quantization/ptq/omniquant/source/omniquant/int_linear.py:42-55).
+ * K * 255 * 255 must fit int32 (K <= 33025).
+ */
+int mp_w8a8_affine_gemm(const void* qx_u8, const void* x_scale_f32, const void* x_zero_f32,
+                        const void* x_rowsum_i32, const void* w_u8, const void* w_scale_f32,
+                        const void* w_zero_f32, const void* w_rowsum_i32, const void* bias_f16,
+                        void* y_f16, int M, int N, int K, int* error_word, mp_stream_t stream);
+
 /* -------------------------------------------------------------------- MoE */
 
 /*

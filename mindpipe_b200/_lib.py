@@ -39,6 +39,8 @@ SIGNATURES = {
     "mp_add_rmsnorm_quant": (_I, [_P, _P, _P, ctypes.c_float, _I, _I, _P, _P, _P]),
     "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_w8a8_gemm_i32": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_affine_quant_per_row": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "mp_w8a8_affine_gemm": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_moe_router_topk": (_I, [_P, _I, _I, _I, _P, _P, _P]),
     "mp_moe_plan_ints": (_Z, [_I, _I]),
     "mp_moe_padded_rows": (_I, [_I, _I]),

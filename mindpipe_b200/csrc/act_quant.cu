@@ -100,6 +100,87 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   }
 }
 
+// OmniQuant-style dynamic asymmetric quantisation of each row to unsigned 8-bit codes:
+// UniformAffineQuantizer.per_token_dynamic_calibration + fake_quant
+// (algorithm/quantization/ptq/omniquant/source/omniquant/quantizer.py:124-150, 89-111;
+// symmetric=False, no group, no learned clipping), every op rounded to fp16 as torch does:
+//   s  = clamp(f16(f16(max - min) / 255), 1e-5, 1e4)
+//   zp = rint(clamp(f16(-min / s), -1e4, 1e4))
+//   u  = clamp(f16(rint(f16(x / s)) + zp), 0, 255);   fake = f16(f16(u - zp) * s)
+// Also emits the row sum of the codes, which the integer GEMM's zero-point correction needs.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+affine_quant_kernel(const __half* __restrict__ x, int K, uint8_t* __restrict__ q, float* __restrict__ scale,
+                    float* __restrict__ zero, int* __restrict__ rowsum, __half* __restrict__ fake) {
+  __shared__ float s_max[THREADS / 32], s_min[THREADS / 32];
+  __shared__ int s_sum[THREADS / 32];
+  __shared__ float s_scale, s_zp;
+  const int row = blockIdx.x;
+  const __half* xr = x + (size_t)row * K;
+  const int chunks = K >> 3;
+  float vmax = -INFINITY, vmin = INFINITY;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = h2f(h[j]);
+      vmax = fmaxf(vmax, f);
+      vmin = fminf(vmin, f);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+  }
+  if ((threadIdx.x & 31) == 0) { s_max[threadIdx.x >> 5] = vmax; s_min[threadIdx.x >> 5] = vmin; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < THREADS / 32; ++i) { vmax = fmaxf(vmax, s_max[i]); vmin = fminf(vmin, s_min[i]); }
+    const __half hmax = f2h(vmax), hmin = f2h(vmin);
+    __half s = hdiv_t(hsub_t(hmax, hmin), f2h(255.0f));
+    const float lo = h2f(f2h(1e-5f)), hi = h2f(f2h(1e4f));
+    s = f2h(fminf(fmaxf(h2f(s), lo), hi));
+    float zp = h2f(hdiv_t(__hneg(hmin), s));
+    zp = rintf(fminf(fmaxf(zp, -hi), hi));
+    s_scale = h2f(s);
+    s_zp = zp;
+    scale[row] = s_scale;
+    zero[row] = zp;
+  }
+  __syncthreads();
+  const float sf = s_scale, zp = s_zp;
+  int local_sum = 0;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+    const __half* h = reinterpret_cast<const __half*>(&raw);
+    uint32_t w0 = 0, w1 = 0;
+    __align__(16) __half out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float u = rintf(h2f(f2h(__fdiv_rn(h2f(h[j]), sf))));
+      u = h2f(f2h(u + zp));
+      u = fminf(fmaxf(u, 0.0f), 255.0f);
+      const uint32_t code = static_cast<uint32_t>(u);
+      local_sum += static_cast<int>(code);
+      if (j < 4) w0 |= code << (8 * j); else w1 |= code << (8 * (j - 4));
+      out[j] = hmul_t(f2h(u - zp), f2h(sf));
+    }
+    if (q) *reinterpret_cast<uint2*>(q + (size_t)row * K + c * 8) = make_uint2(w0, w1);
+    if (fake) *reinterpret_cast<uint4*>(fake + (size_t)row * K + c * 8) = *reinterpret_cast<uint4*>(out);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local_sum += __shfl_xor_sync(0xffffffffu, local_sum, o);
+  if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = local_sum;
+  __syncthreads();
+  if (threadIdx.x == 0 && rowsum) {
+    int tot = 0;
+    for (int i = 0; i < THREADS / 32; ++i) tot += s_sum[i];
+    rowsum[row] = tot;
+  }
+}
+
 // Residual add + RMSNorm + per-token int8 quant in one pass over the row: the
 // torch_npu.npu_add_rms_norm_dynamic_quant call that feeds the (codes, scale) tuple to
 // the W8A8 linear (acceleration/runtime_patches/vllm_ascend.patch:754-770).
@@ -246,6 +327,18 @@ extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i
   } else {
     act_quant_kernel<512, 0><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
   }
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_affine_quant_per_row(const void* x_f16, int M, int K, void* q_u8, void* scale_f32, void* zero_f32,
+                                       void* rowsum_i32, void* fake_f16, mp_stream_t stream) {
+  if (!x_f16 || !scale_f32 || !zero_f32 || M <= 0 || K <= 0 || (!q_u8 && !fake_f16)) return MP_ERR_INVALID_ARG;
+  if (K % 8 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(x_f16, 16) || (q_u8 && !aligned(q_u8, 8)) || (fake_f16 && !aligned(fake_f16, 16))) return MP_ERR_ALIGNMENT;
+  affine_quant_kernel<256><<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(x_f16), K, static_cast<uint8_t*>(q_u8), static_cast<float*>(scale_f32),
+      static_cast<float*>(zero_f32), static_cast<int*>(rowsum_i32), static_cast<__half*>(fake_f16));
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

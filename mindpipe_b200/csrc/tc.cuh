@@ -163,6 +163,7 @@ constexpr uint32_t kIdescDFormatF32 = 1u << 4;
 constexpr uint32_t kIdescDFormatS32 = 2u << 4;
 constexpr uint32_t kIdescABFormatF16 = (0u << 7) | (0u << 10);
 constexpr uint32_t kIdescABFormatS8 = (1u << 7) | (1u << 10);
+constexpr uint32_t kIdescABFormatU8 = (0u << 7) | (0u << 10);
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t formats, int m, int n) {
   return formats | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }

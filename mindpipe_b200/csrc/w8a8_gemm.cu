@@ -32,7 +32,7 @@ constexpr int kBM = 128;
 constexpr int kBK = 128;      // int8 elements (= bytes) of K per stage
 constexpr int kUmmaK = 32;    // K of one kind::i8 instruction
 
-enum : int { EPI_F16 = 0, EPI_I32 = 1, EPI_SWIGLU = 2 };
+enum : int { EPI_F16 = 0, EPI_I32 = 1, EPI_SWIGLU = 2, EPI_AFFINE = 3 };   // AFFINE: unsigned codes with zero points
 
 struct GemmParams {
   int M, N, K;
@@ -46,6 +46,10 @@ struct GemmParams {
   const __half* bias;          // [N] or null
   void* out;                   // f16 [M,N] or int32 [M,N]
   unsigned int* row_absmax;    // SwiGLU: per-row max |h| as float bits (atomicMax target)
+  const float* a_zero;         // AFFINE: per-token zero points (integer valued) and code row sums
+  const int* a_rowsum;
+  const float* b_zero;         // AFFINE: per-channel zero points and code row sums
+  const int* b_rowsum;
   int* error_word;
 };
 
@@ -56,7 +60,7 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kBarBytes = 256;
-  static constexpr int kScaleBytes = 4 * 256 * 4;   // per epilogue warp: the tile's 256 channel scales
+  static constexpr int kScaleBytes = 3 * 4 * 256 * 4;   // per epilogue warp: 256 channel scales (+ zero points, row sums)
   static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes + kScaleBytes;
 };
 
@@ -132,7 +136,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(kIdescDFormatS32 | kIdescABFormatS8, kBM, BN);
+      constexpr uint32_t idesc =
+          umma_idesc(kIdescDFormatS32 | (EPI == EPI_AFFINE ? kIdescABFormatU8 : kIdescABFormatS8), kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -162,7 +167,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     const int quarter = warp & 3;               // TMEM lanes [32*quarter, +32) belong to this warp
-    float* my_scales = s_scales + quarter * 256; // this warp's copy of the tile's channel scales
+    float* my_scales = s_scales + quarter * 768; // this warp's copy of the tile's channel scales
+    float* my_zero = my_scales + 256;             // AFFINE: channel zero points ...
+    int* my_wsum = reinterpret_cast<int*>(my_scales + 512);   // ... and channel code sums
     int buf = 0;
     uint32_t buf_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
@@ -183,6 +190,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             src = e_row0 + n;
           }
           my_scales[c] = (c < BN && n < p.N) ? __ldg(p.b_scale + src) : 0.0f;
+          if (EPI == EPI_AFFINE) {
+            my_zero[c] = (c < BN && n < p.N) ? __ldg(p.b_zero + src) : 0.0f;
+            my_wsum[c] = (c < BN && n < p.N) ? __ldg(p.b_rowsum + src) : 0;
+          }
         }
         __syncwarp();
       }
@@ -262,10 +273,25 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           } else {
             uint32_t hp[16];
+            long long zx = 0, xs = 0;
+            if (EPI == EPI_AFFINE && row_ok) {
+              zx = static_cast<long long>(p.a_zero[row]);
+              xs = p.a_rowsum[row];
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
-              float v0 = static_cast<float>(static_cast<int>(r[j])) * sa * my_scales[c0 + j];
-              float v1 = static_cast<float>(static_cast<int>(r[j + 1])) * sa * my_scales[c0 + j + 1];
+              float v0, v1;
+              if (EPI == EPI_AFFINE) {
+                // sum (qx - zx)(qw - zw) = acc - zw * sum(qx) - zx * sum(qw) + K * zx * zw, exactly, in int64
+                const long long zw0 = static_cast<long long>(my_zero[c0 + j]), zw1 = static_cast<long long>(my_zero[c0 + j + 1]);
+                const long long t0 = static_cast<long long>(r[j]) - zw0 * xs - zx * my_wsum[c0 + j] + (long long)p.K * zx * zw0;
+                const long long t1 = static_cast<long long>(r[j + 1]) - zw1 * xs - zx * my_wsum[c0 + j + 1] + (long long)p.K * zx * zw1;
+                v0 = static_cast<float>(t0) * sa * my_scales[c0 + j];
+                v1 = static_cast<float>(t1) * sa * my_scales[c0 + j + 1];
+              } else {
+                v0 = static_cast<float>(static_cast<int>(r[j])) * sa * my_scales[c0 + j];
+                v1 = static_cast<float>(static_cast<int>(r[j + 1])) * sa * my_scales[c0 + j + 1];
+              }
               if (p.bias) {
                 if (n0 + c0 + j < p.N) v0 += h2f(p.bias[n0 + c0 + j]);
                 if (n0 + c0 + j + 1 < p.N) v1 += h2f(p.bias[n0 + c0 + j + 1]);
@@ -350,6 +376,7 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void
 }
 
 struct GemmCall {
+  const float* a_zero = nullptr; const int* a_rowsum = nullptr; const float* b_zero = nullptr; const int* b_rowsum = nullptr;
   const void* a; const void* b;
   int M, N, K;
   int a_rows;                 // rows of the activation buffer (>= M; padded in grouped mode)
@@ -380,6 +407,7 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.b_rows_per_expert = c.b_rows_per_expert; p.up_row_offset = c.up_row_offset;
   p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
   p.row_absmax = c.row_absmax; p.error_word = c.error_word;
+  p.a_zero = c.a_zero; p.a_rowsum = c.a_rowsum; p.b_zero = c.b_zero; p.b_rowsum = c.b_rowsum;
   auto kern = w8a8_gemm_kernel<BN, EPI>;
   static thread_local int configured_device = -1;
   int device = 0;
@@ -458,4 +486,24 @@ extern "C" int mp_w8a8_gemm_i32(const void* qx_i8, const void* w_i8, void* acc_i
   const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_I32>(c, st);
   return launch_gemm<256, EPI_I32>(c, st);
+}
+
+extern "C" int mp_w8a8_affine_gemm(const void* qx_u8, const void* x_scale_f32, const void* x_zero_f32,
+                                   const void* x_rowsum_i32, const void* w_u8, const void* w_scale_f32,
+                                   const void* w_zero_f32, const void* w_rowsum_i32, const void* bias_f16,
+                                   void* y_f16, int M, int N, int K, int* error_word, mp_stream_t stream) {
+  int rc = check_gemm_args(qx_u8, w_u8, y_f16, M, N, K);
+  if (rc != MP_OK) return rc;
+  if (!x_scale_f32 || !x_zero_f32 || !x_rowsum_i32 || !w_scale_f32 || !w_zero_f32 || !w_rowsum_i32) return MP_ERR_INVALID_ARG;
+  if ((long long)K * 255 * 255 > 2147483647LL) return MP_ERR_UNSUPPORTED;   // the unsigned sums must fit int32
+  GemmCall c{};
+  c.a = qx_u8; c.b = w_u8; c.M = M; c.N = N; c.K = K; c.a_rows = M; c.b_rows_total = N;
+  c.a_scale = static_cast<const float*>(x_scale_f32); c.b_scale = static_cast<const float*>(w_scale_f32);
+  c.a_zero = static_cast<const float*>(x_zero_f32); c.a_rowsum = static_cast<const int*>(x_rowsum_i32);
+  c.b_zero = static_cast<const float*>(w_zero_f32); c.b_rowsum = static_cast<const int*>(w_rowsum_i32);
+  c.bias = static_cast<const __half*>(bias_f16); c.out = y_f16; c.error_word = error_word;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_AFFINE>(c, st);
+  return launch_gemm<256, EPI_AFFINE>(c, st);
 }

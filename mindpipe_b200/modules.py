@@ -203,6 +203,63 @@ class SmoothQuantLinear(nn.Module):
                 f"output_quant={self.output_quant_name}, int8=True)")
 
 
+class QuantLinear(nn.Module):
+    """Real-int twin of OmniQuant's ``QuantLinear``
+    (algorithm/quantization/ptq/omniquant/source/omniquant/int_linear.py:10-59) for the W8A8 recipe:
+    per-output-channel asymmetric 8-bit weights and per-token dynamic asymmetric 8-bit activations
+    (``UniformAffineQuantizer`` with ``symmetric=False``, quantizer.py:124-150).  Same constructor
+    shape (``org_module, weight_quant_params, act_quant_params, disable_input_quant``) and
+    ``set_quant_state``; the forward runs on unsigned 8-bit codes with the zero-point correction
+    folded into the tensor-core GEMM's epilogue.
+    """
+
+    def __init__(self, org_module: nn.Linear, weight_quant_params: dict | None = None,
+                 act_quant_params: dict | None = None, disable_input_quant: bool = False):
+        super().__init__()
+        wq, aq = dict(weight_quant_params or {}), dict(act_quant_params or {})
+        for name, prm in (("weight", wq), ("activation", aq)):
+            if int(prm.get("n_bits", 8)) != 8 or prm.get("symmetric", False) or prm.get("group_size") or \
+                    prm.get("lwc", False) or prm.get("disable_zero_point", False):
+                raise ValueError(f"{name} quantiser: the integer kernels implement 8-bit, asymmetric, "
+                                 "ungrouped quantisation without learned clipping")
+        if disable_input_quant:
+            raise ValueError("disable_input_quant=True (fp16 activations) is not an integer path")
+        w = org_module.weight.detach()
+        if w.dtype != torch.float16:
+            raise TypeError(f"expected an fp16 weight, got {w.dtype}")
+        self.in_features = org_module.in_features
+        self.out_features = org_module.out_features
+        q, s, z, rs, _ = ops.affine_quant_per_row(w.contiguous())
+        self.register_buffer("weight", q)                      # uint8 codes [N, K]
+        self.register_buffer("scales", s)                      # names of register_scales_and_zeros (quantizer.py:152-155)
+        self.register_buffer("zeros", z)
+        self.register_buffer("weight_rowsum", rs)
+        if org_module.bias is not None:
+            self.register_buffer("bias", org_module.bias.detach().clone())
+        else:
+            self.bias = None
+        self.use_weight_quant = True
+        self.use_act_quant = True
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False) -> None:
+        if not (weight_quant and act_quant):
+            raise ValueError("this module only holds the quantised weight; both quantisers stay on")
+        self.use_weight_quant, self.use_act_quant = True, True
+
+    def dequantize(self) -> torch.Tensor:
+        """The reference's fake-quantised weight ``f16(f16(u - zp) * s)``."""
+        return ((self.weight.to(torch.float16) - self.zeros.to(torch.float16)[:, None])
+                * self.scales.to(torch.float16)[:, None]).to(torch.float16)
+
+    @torch.no_grad()
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        lead = input.shape[:-1]
+        x2 = input.reshape(-1, input.shape[-1]).contiguous()
+        q, s, z, rs, _ = ops.affine_quant_per_row(x2)
+        y = ops.w8a8_affine_gemm(q, s, z, rs, self.weight, self.scales, self.zeros, self.weight_rowsum, self.bias)
+        return y.reshape(*lead, self.out_features)
+
+
 class W8A8DynamicLinearMethod:
     """Linear-method style entry, mirroring ``AscendW8A8DynamicLinearMethod``
     (acceleration/runtime_patches/vllm_ascend.patch:3933-4033): ``apply(layer, x, bias, tp_rank)``

@@ -435,3 +435,45 @@ def add_rmsnorm_quant(x, residual, gamma, eps: float = 1e-5):
                                               s.data_ptr(), _stream())
         _lib.check(st, "add_rmsnorm_quant", M=m, H=h)
     return q, s
+
+
+def affine_quant_per_row(x, *, want_fake: bool = False):
+    """OmniQuant-style dynamic asymmetric 8-bit quantisation of each row of ``x[..., K]`` (fp16).
+
+    Returns ``(codes uint8, scale f32, zero_point f32, rowsum int32, fake f16 | None)``.
+    """
+    xt = _req(x, "x", torch.float16)
+    k = xt.shape[-1]
+    m = xt.numel() // k
+    q = torch.empty(xt.shape, dtype=torch.uint8, device=xt.device)
+    s = torch.empty(xt.shape[:-1], dtype=torch.float32, device=xt.device)
+    z = torch.empty(xt.shape[:-1], dtype=torch.float32, device=xt.device)
+    rs = torch.empty(xt.shape[:-1], dtype=torch.int32, device=xt.device)
+    f = torch.empty_like(xt) if want_fake else None
+    if m:
+        st = _lib.load().mp_affine_quant_per_row(xt.data_ptr(), m, k, q.data_ptr(), s.data_ptr(), z.data_ptr(),
+                                                 rs.data_ptr(), _ptr(f), _stream())
+        _lib.check(st, "affine_quant_per_row", M=m, K=k)
+    return q, s, z, rs, f
+
+
+def w8a8_affine_gemm(qx, x_scale, x_zero, x_rowsum, weight_u8, weight_scale, weight_zero, weight_rowsum, bias=None):
+    """``f16(sum_k (qx - zx)(qw - zw) * sx * sw (+bias))`` from unsigned 8-bit codes."""
+    a = _req(qx, "qx", torch.uint8, 2)
+    b = _req(weight_u8, "weight", torch.uint8, 2)
+    args = [_req(x_scale, "x_scale", torch.float32, 1), _req(x_zero, "x_zero", torch.float32, 1),
+            _req(x_rowsum, "x_rowsum", torch.int32, 1), _req(weight_scale, "weight_scale", torch.float32, 1),
+            _req(weight_zero, "weight_zero", torch.float32, 1), _req(weight_rowsum, "weight_rowsum", torch.int32, 1)]
+    bi = None if bias is None else _req(bias, "bias", torch.float16, 1)
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k or any(t.numel() != m for t in args[:3]) or any(t.numel() != n for t in args[3:]):
+        raise ValueError("shape mismatch between codes and their per-row parameters")
+    y = torch.empty((m, n), dtype=torch.float16, device=a.device)
+    if m == 0:
+        return y
+    st = _lib.load().mp_w8a8_affine_gemm(a.data_ptr(), args[0].data_ptr(), args[1].data_ptr(), args[2].data_ptr(),
+                                         b.data_ptr(), args[3].data_ptr(), args[4].data_ptr(), args[5].data_ptr(),
+                                         _ptr(bi), y.data_ptr(), m, n, k, _error_word(a.device).data_ptr(), _stream())
+    _lib.check(st, "w8a8_affine_gemm", M=m, N=n, K=k)
+    return y

@@ -23,6 +23,7 @@ REF = Path(os.environ.get("MINDPIPE_REFERENCE", "/root/reference"))
 OUT = Path(__file__).resolve().parent
 sys.dont_write_bytecode = True
 for sub in ("", "algorithm/quantization/ptq/awq/source", "algorithm/quantization/ptq/smoothquant/source",
+            "algorithm/quantization/ptq/omniquant/source",
             "algorithm/quantization/ptq/gptq/source", "algorithm/quantization/qat/flatquant/source",
             "scripts/repro"):
     sys.path.insert(0, str(REF / sub))
@@ -107,6 +108,29 @@ def main():
     np.savez_compressed(OUT / "w8a8_small.npz", x=np16(xa), x_fake=np16(xq), w=np16(w8), w_fake=np16(w8q),
                         exp_q=np16(e_q), exp_scale=np16(e_s), exp_offset=np16(e_o), bias=np16(lin8.bias),
                         y=np16(m_plain(xa)), y_outq=np16(m_oq(xa)))
+
+    # ---- OmniQuant-style asymmetric per-token activations / per-channel weights ----
+    oq = importlib.import_module("omniquant.int_linear")
+    lin_o = torch.nn.Linear(256, 16, bias=True).half()
+    with torch.no_grad():
+        lin_o.weight.copy_(w8)
+        lin_o.bias.copy_(lin8.bias)
+    act_p = {"n_bits": 8, "per_channel_axes": [], "symmetric": False, "dynamic_method": "per_token"}
+    w_p = {"n_bits": 8, "per_channel_axes": [0], "symmetric": False, "dynamic_method": "per_channel",
+           "group_size": None, "lwc": False, "disable_zero_point": False}
+    ql = oq.QuantLinear(lin_o, weight_quant_params=w_p, act_quant_params=act_p)
+    ql.set_quant_state(weight_quant=True, act_quant=True)
+    with torch.no_grad():
+        xo = xa.clone()
+        xo[5] = xa[4] + 0.25                                # no all-zero row: keep the ranges ordinary
+        y_o = ql(xo)
+        x_fake_o = ql.act_quantizer(xo.clone())
+        x_scale_o, x_zp_o = ql.act_quantizer.scale.clone(), ql.act_quantizer.round_zero_point.clone()
+        w_fake_o = ql.weight_quantizer(w8.clone())
+        w_scale_o, w_zp_o = ql.weight_quantizer.scale.clone(), ql.weight_quantizer.round_zero_point.clone()
+    np.savez_compressed(OUT / "omniquant_small.npz", x=np16(xo), w=np16(w8), bias=np16(lin8.bias), y=np16(y_o),
+                        x_fake=np16(x_fake_o), x_scale=np16(x_scale_o), x_zp=np16(x_zp_o),
+                        w_fake=np16(w_fake_o), w_scale=np16(w_scale_o), w_zp=np16(w_zp_o))
 
     # ---- MoE ----
     E, H, I, T, K = 4, 128, 192, 40, 2

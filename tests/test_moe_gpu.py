@@ -110,3 +110,33 @@ def test_moe_expert_ranges_sum_to_full_output():
     for q in quarters:                                               # each token has two non-zero addends
         acc += q.astype(np.float32)
     assert np.array_equal(acc.astype(np.float16), full)
+
+
+def test_peer_barrier_wait_is_bounded_and_reports():
+    """A peer that never shows up: the barrier's wait runs out (2 s), the kernel records an error
+    word and returns, and the context stays usable.  The 'peer' is a second flag array on the same
+    GPU that nothing ever signals."""
+    import ctypes
+    import time
+    from mindpipe_b200 import _lib, ops
+    lib = _lib.load()
+    mine = torch.zeros(16, dtype=torch.int32, device="cuda")
+    absent_peer = torch.zeros(16, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), absent_peer.data_ptr())
+    t0 = time.time()
+    st = lib.mp_peer_barrier(ptrs, 2, 0, 1, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert err.item() == 4                          # "a peer did not arrive"
+    assert 1.5 < waited < 10.0
+    assert absent_peer[0].item() == 1               # our own arrival was published to the peer
+    # a barrier whose peer has arrived passes at once, and ordinary work still runs afterwards
+    err.zero_()
+    mine[1] = 2
+    st = lib.mp_peer_barrier(ptrs, 2, 0, 2, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert st == 0 and err.item() == 0
+    q, s, _ = ops.act_quant_per_token(torch.ones(2, 64, dtype=torch.float16, device="cuda"))
+    assert q.abs().max().item() == 127

@@ -116,3 +116,15 @@ def test_moe_experts_forward(golden):
     assert np.array_equal(bits(dnf), bits(g["down_fake"]))
     out = O.moe_experts_forward(g["hidden"], g["top_k_index"], g["top_k_weights"], guf, dnf)
     assert O.rel_frobenius(out, g["out"]) < 2e-3
+
+
+def test_omniquant_affine_quantizer_bitwise(golden):
+    g = golden("omniquant_small.npz")
+    for key in ("x", "w"):
+        fake, codes, s, zp = O.affine_quant_last_dim(g[key])
+        assert np.array_equal(bits(fake), bits(g[key + "_fake"]))
+        assert np.array_equal(bits(s), bits(g[key + "_scale"]))
+        assert np.array_equal(bits(zp), bits(g[key + "_zp"]))
+        assert codes.min() >= 0 and codes.max() <= 255
+    y = O.omniquant_linear_forward(g["x"], g["w"], g["bias"])
+    assert O.rel_frobenius(y, g["y"]) < 1e-3

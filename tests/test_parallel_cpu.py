@@ -140,3 +140,21 @@ def test_expert_parallel_exchange_world2_gloo():
     ret = mgr.dict()
     mp.spawn(_ep_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_expert_parallel_constructor_rejects_wrong_partition():
+    """Host-side failure injection: a rank holding the wrong experts is refused before any launch."""
+    import types
+    from mindpipe_b200 import expert_parallel as ep
+
+    class FakeExperts:
+        expert_range = (0, 3)
+
+    fake_dist = types.SimpleNamespace(get_world_size=lambda g=None: 2, get_rank=lambda g=None: 1)
+    real = ep.dist
+    ep.dist = fake_dist
+    try:
+        with pytest.raises(ValueError, match="must hold experts"):
+            ep.ExpertParallelMoE(FakeExperts(), 8)
+    finally:
+        ep.dist = real

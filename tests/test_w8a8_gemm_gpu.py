@@ -138,3 +138,56 @@ def test_smoothquant_linear_module_matches_reference_golden(golden):
     layer._ascend_quant_config = {"output_dtype": torch.int32}
     acc = method.apply(layer, (q, s))
     assert np.array_equal(acc.cpu().numpy(), O.int32_accumulate(q.cpu().numpy(), m.weight.cpu().numpy()))
+
+
+def test_omniquant_affine_quant_bit_exact(golden):
+    """Asymmetric per-row quantiser vs the reference's UniformAffineQuantizer (golden) and the oracle."""
+    from mindpipe_b200 import ops
+    g = golden("omniquant_small.npz")
+    for key in ("x", "w"):
+        q, s, z, rs, f = ops.affine_quant_per_row(dev(g[key]), want_fake=True)
+        fake, codes, sc, zp = O.affine_quant_last_dim(g[key])
+        assert np.array_equal(q.cpu().numpy(), codes)
+        assert np.array_equal(s.cpu().numpy(), sc.astype(np.float32).reshape(-1))
+        assert np.array_equal(z.cpu().numpy(), zp.astype(np.float32).reshape(-1))
+        assert np.array_equal(rs.cpu().numpy(), codes.astype(np.int64).sum(axis=1).astype(np.int32))
+        assert np.array_equal(f.cpu().numpy(), g[key + "_fake"])
+    x = synth.outlier_activation(300, 4096, seed=3).numpy()
+    q, s, z, rs, _ = ops.affine_quant_per_row(dev(x))
+    _, codes, sc, zp = O.affine_quant_last_dim(x)
+    assert np.array_equal(q.cpu().numpy(), codes) and np.array_equal(z.cpu().numpy(), zp.astype(np.float32).reshape(-1))
+
+
+@pytest.mark.parametrize("m,n,k", [(7, 16, 256), (300, 520, 1024), (1024, 1024, 4096)])
+def test_omniquant_quantlinear_twin(golden, m, n, k):
+    from mindpipe_b200 import ops
+    from mindpipe_b200.modules import QuantLinear
+    if (m, n, k) == (7, 16, 256):
+        g = golden("omniquant_small.npz")
+        x, w, b, ref = g["x"], g["w"], g["bias"], g["y"]               # outputs of the reference module itself
+    else:
+        x = synth.outlier_activation(m, k, seed=m).numpy()
+        w = synth.normal_weight(n, k, seed=m, index=0).numpy()
+        b = None
+        ref = O.omniquant_linear_forward(x, w)
+    lin = torch.nn.Linear(k, n, bias=b is not None).half().cuda()
+    with torch.no_grad():
+        lin.weight.copy_(dev(w))
+        if b is not None:
+            lin.bias.copy_(dev(b))
+    mod = QuantLinear(lin, weight_quant_params={"n_bits": 8, "symmetric": False, "dynamic_method": "per_channel"},
+                      act_quant_params={"n_bits": 8, "symmetric": False, "dynamic_method": "per_token"})
+    assert np.array_equal(mod.dequantize().cpu().numpy(), O.affine_quant_last_dim(w)[0])
+    y = mod(dev(x))
+    ops.check_device_errors()
+    assert O.rel_frobenius(y.cpu().numpy(), ref) <= TOL
+    # exact integer identity of the zero-point correction, checked through a unit-scale call
+    q, s, z, rs, _ = ops.affine_quant_per_row(dev(x))
+    ones_m = torch.ones_like(s)
+    ones_n = torch.ones_like(mod.scales)
+    yi = ops.w8a8_affine_gemm(q[:4].contiguous(), ones_m[:4].contiguous(), z[:4].contiguous(), rs[:4].contiguous(),
+                              mod.weight[:8].contiguous(), ones_n[:8].contiguous(), mod.zeros[:8].contiguous(),
+                              mod.weight_rowsum[:8].contiguous())
+    exact = (q[:4].cpu().numpy().astype(np.int64) - z[:4].cpu().numpy().astype(np.int64)[:, None]) @ \
+            (mod.weight[:8].cpu().numpy().astype(np.int64) - mod.zeros[:8].cpu().numpy().astype(np.int64)[:, None]).T
+    assert np.allclose(yi.float().cpu().numpy(), exact.astype(np.float16).astype(np.float32), rtol=2e-3, atol=1.0)
