@@ -425,7 +425,7 @@ def run_ours(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_src, "kernel": "w4a16_decode_kernel",
+                         "traffic": traffic, "peak_source": peak_src, "kernel": "w4a16_decode_tma_kernel",
                          "launch_bytes_avg": bytes_step / launches_per_step,
                          "launch_us_avg": ms * 1e3 / (args.steps * launches_per_step)},
             "e2e": {"value": e2e_val, "unit": "GB/s",

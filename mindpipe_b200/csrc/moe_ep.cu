@@ -64,7 +64,18 @@ __global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, un
 //   ext + El*(W+1) + e*W + s            src_seg[e][s]: first row of that segment in rank s's routed buffer
 __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_total, int e_loc, int max_tiles,
                                int ext, int* __restrict__ xplan) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // one thread per (local expert, source rank) fetches that peer's count and segment offset over NVLink
+  __shared__ int s_cnt[256], s_seg[256];
+  const int pairs = e_loc * world;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = i / world, s = i - e * world;
+    const int ge = rank * e_loc + e;
+    const int* pp = static_cast<const int*>(peer_plans.p[s]);       // rank s's plan over all e_total experts
+    s_cnt[i] = pp[ge];                                               // counts[ge]
+    s_seg[i] = pp[2 * e_total + ge];                                 // seg_offsets[ge]
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
   int* counts = xplan;
   int* cursors = xplan + e_loc;
   int* seg = xplan + 2 * e_loc;
@@ -74,13 +85,11 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
   int* src_seg = xplan + ext + e_loc * (world + 1);
   int off = 0, tiles = 0;
   for (int e = 0; e < e_loc; ++e) {
-    const int ge = rank * e_loc + e;
     int total = 0;
     for (int s = 0; s < world; ++s) {
-      const int* pp = static_cast<const int*>(peer_plans.p[s]);     // rank s's plan over all e_total experts
       cum[e * (world + 1) + s] = total;
-      total += pp[ge];                                               // counts[ge]
-      src_seg[e * world + s] = pp[2 * e_total + ge];                 // seg_offsets[ge]
+      total += s_cnt[e * world + s];
+      src_seg[e * world + s] = s_seg[e * world + s];
     }
     cum[e * (world + 1) + world] = total;
     counts[e] = total;
@@ -178,10 +187,11 @@ extern "C" int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int 
   if (rc != MP_OK) return rc;
   if (!xplan_i32 || num_experts <= 0 || num_experts % world != 0 || capacity_rows <= 0 || capacity_rows % kEpTile != 0)
     return MP_ERR_INVALID_ARG;
+  if (num_experts > 256) return MP_ERR_UNSUPPORTED;   // (local expert, source) pairs are staged in shared memory
   const int e_loc = num_experts / world;
   const int max_tiles = capacity_rows / kEpTile;
   const int ext = 3 * e_loc + 2 + max_tiles;
-  ep_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, rank, num_experts, e_loc, max_tiles, ext,
+  ep_plan_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, rank, num_experts, e_loc, max_tiles, ext,
                                                                   static_cast<int*>(xplan_i32));
   MP_LAUNCH_CHECK();
   return MP_OK;
