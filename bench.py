@@ -474,6 +474,29 @@ def run_suite(args, local_rank):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters * 1e-3
 
+    def timed_graph(fns, rounds=4, warm=2):
+        """Kernels shorter than the host's launch path: capture the callables (rotated, so that inputs
+        larger than L2 are streamed from HBM) in one CUDA graph and time its replay."""
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(warm):
+                for fn in fns:
+                    fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(rounds):
+                    for fn in fns:
+                        fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (rounds * len(fns)) * 1e-3
+
     def emit(**kw):
         print(json.dumps(kw), flush=True)
 
@@ -522,7 +545,9 @@ def run_suite(args, local_rank):
             qw, sw, _ = ops.act_quant_per_token(w)
             x = synth.outlier_activation(m, k, seed=0).to(dev)
             qx, sx, _ = ops.act_quant_per_token(x)
-            t_q = timed(lambda: ops.act_quant_per_token(x), 20)
+            xs = [x] + [synth.outlier_activation(m, k, seed=0, index=i).to(dev)
+                        for i in range(1, max(2, int(300e6 // (2 * m * k)) + 1))]       # rotate > 2x L2
+            t_q = timed_graph([(lambda xi=xi: ops.act_quant_per_token(xi)) for xi in xs])
             t_g = timed(lambda: ops.w8a8_gemm(qx, sx, qw, sw), 20)
             op = 2 * m * n * k
             lib_tops = None

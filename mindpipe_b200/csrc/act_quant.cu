@@ -14,6 +14,56 @@
 
 namespace mp {
 
+// Quantise eight values held in one 128-bit register group and store the codes and / or the
+// fake-quantised values f16(code * s).
+__device__ __forceinline__ void emit_codes(const uint4& raw, const RowQuant& rq, int8_t* q8, __half* fake8) {
+  if (fake8) {
+    uint4 fk;
+    const uint2 codes = quant8_pack_fake(raw, rq, fk);
+    if (q8) *reinterpret_cast<uint2*>(q8) = codes;
+    *reinterpret_cast<uint4*>(fake8) = fk;
+  } else if (q8) {
+    *reinterpret_cast<uint2*>(q8) = quant8_pack(raw, rq);
+  }
+}
+
+// One warp per row (rows of up to 32 * 8 * NV columns): the row is read once with NV independent
+// 128-bit loads per lane, reduced with shuffles only, and quantised from registers -- no block-level
+// synchronisation at all.
+template <int NV>
+__global__ void __launch_bounds__(128)
+act_quant_warp_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
+                      float* __restrict__ scale, __half* __restrict__ fake) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const __half* xr = x + (size_t)row * K;
+  const int chunks = K >> 3;
+  uint4 held[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = lane + v * 32;
+    held[v] = c < chunks ? *reinterpret_cast<const uint4*>(xr + c * 8) : make_uint4(0, 0, 0, 0);
+  }
+  __half2 m2 = __float2half2_rn(0.0f);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) m2 = absmax8(m2, held[v]);
+  float amax = absmax_to_float(m2);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float eps = h2f(f2h(1e-5f));                                   // clamp_(min=1e-5) on an fp16 tensor
+  const float sf = h2f(f2h(__fdiv_rn(fmaxf(amax, eps), 127.0f)));      // div_(q_max), rounded to fp16
+  const RowQuant rq = make_row_quant(sf);
+  if (lane == 0 && scale) scale[row] = sf;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = lane + v * 32;
+    if (c >= chunks) continue;
+    emit_codes(held[v], rq, q ? q + (size_t)row * K + c * 8 : nullptr,
+               fake ? fake + (size_t)row * K + c * 8 : nullptr);
+  }
+}
+
 // NV = 128-bit vectors per thread.  NV > 0: the row (K <= THREADS * 8 * NV) is held in
 // registers between the abs-max and the rounding step, so global memory is read once;
 // NV == 0: any K, second pass re-reads the row (an L1/L2 hit).
@@ -28,15 +78,8 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   const int chunks = K >> 3;
   constexpr int NREG = NV > 0 ? NV : 1;
   uint4 held[NREG];
-  float amax = 0.0f;
-  auto absmax_of = [&](const uint4& raw) {
-    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 f = __half22float2(__habs2(h2[j]));
-      amax = fmaxf(amax, fmaxf(f.x, f.y));
-    }
-  };
+  __half2 m2 = __float2half2_rn(0.0f);
+  auto absmax_of = [&](const uint4& raw) { m2 = absmax8(m2, raw); };
   if (NV > 0) {
 #pragma unroll
     for (int v = 0; v < NREG; ++v) {
@@ -48,6 +91,7 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
   } else {
     for (int c = threadIdx.x; c < chunks; c += THREADS) absmax_of(*reinterpret_cast<const uint4*>(xr + c * 8));
   }
+  float amax = absmax_to_float(m2);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
@@ -64,30 +108,10 @@ act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict_
     }
   }
   __syncthreads();
-  const float sf = s_scale;
+  const RowQuant rq = make_row_quant(s_scale);
   auto emit = [&](int c, const uint4& raw) {
-    const __half* h = reinterpret_cast<const __half*>(&raw);
-    float code[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) code[j] = rintf(h2f(f2h(__fdiv_rn(h2f(h[j]), sf))));
-    if (q) {
-      uint2 o;
-      o.x = (static_cast<uint32_t>(static_cast<int>(code[0])) & 0xFFu) |
-            ((static_cast<uint32_t>(static_cast<int>(code[1])) & 0xFFu) << 8) |
-            ((static_cast<uint32_t>(static_cast<int>(code[2])) & 0xFFu) << 16) |
-            ((static_cast<uint32_t>(static_cast<int>(code[3])) & 0xFFu) << 24);
-      o.y = (static_cast<uint32_t>(static_cast<int>(code[4])) & 0xFFu) |
-            ((static_cast<uint32_t>(static_cast<int>(code[5])) & 0xFFu) << 8) |
-            ((static_cast<uint32_t>(static_cast<int>(code[6])) & 0xFFu) << 16) |
-            ((static_cast<uint32_t>(static_cast<int>(code[7])) & 0xFFu) << 24);
-      *reinterpret_cast<uint2*>(q + (size_t)row * K + c * 8) = o;
-    }
-    if (fake) {
-      __align__(16) __half out[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) out[j] = f2h(__fmul_rn(code[j], sf));
-      *reinterpret_cast<uint4*>(fake + (size_t)row * K + c * 8) = *reinterpret_cast<uint4*>(out);
-    }
+    emit_codes(raw, rq, q ? q + (size_t)row * K + c * 8 : nullptr,
+               fake ? fake + (size_t)row * K + c * 8 : nullptr);
   };
   if (NV > 0) {
 #pragma unroll
@@ -259,19 +283,13 @@ add_rmsnorm_quant_kernel(const __half* __restrict__ x, __half* __restrict__ resi
   }
   const float eps_q = h2f(f2h(1e-5f));
   const float sf = h2f(f2h(__fdiv_rn(fmaxf(block_reduce(amax, true), eps_q), 127.0f)));
+  const RowQuant rq = make_row_quant(sf);
   if (threadIdx.x == 0) scale[row] = sf;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int c = threadIdx.x + v * THREADS;
     if (c < chunks) {
-      const __half* hs = reinterpret_cast<const __half*>(&held[v]);
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hs[j]), sf)))))) & 0xFFu) << (8 * j);
-        w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hs[j + 4]), sf)))))) & 0xFFu) << (8 * j);
-      }
-      *reinterpret_cast<uint2*>(q + (size_t)row * H + c * 8) = make_uint2(w0, w1);
+      *reinterpret_cast<uint2*>(q + (size_t)row * H + c * 8) = quant8_pack(held[v], rq);
     }
   }
 }
@@ -314,12 +332,13 @@ extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i
   int8_t* q = static_cast<int8_t*>(q_i8);
   float* sc = static_cast<float*>(scale_f32);
   __half* fk = static_cast<__half*>(fake_f16);
+  const unsigned warp_blocks = static_cast<unsigned>((M + 3) / 4);
   if (K <= 1024) {
-    act_quant_kernel<128, 1><<<M, 128, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_warp_kernel<4><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 2048) {
-    act_quant_kernel<256, 1><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_warp_kernel<8><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 4096) {
-    act_quant_kernel<256, 2><<<M, 256, 0, st>>>(x, M, K, q, sc, fk);
+    act_quant_warp_kernel<16><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 8192) {
     act_quant_kernel<512, 2><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 16384) {

@@ -41,6 +41,133 @@ __device__ __forceinline__ __half hsub_t(__half a, __half b) { return f2h(__fsub
 __device__ __forceinline__ __half hadd_t(__half a, __half b) { return f2h(__fadd_rn(h2f(a), h2f(b))); }
 __device__ __forceinline__ __half hmul_t(__half a, __half b) { return f2h(__fmul_rn(h2f(a), h2f(b))); }
 
+// ---- per-row int8 codes of fp16 values: code = rint(f16(x / s)), as torch computes
+// x.div_(scale).round_() on an fp16 tensor (fp32 division, rounded to fp16, rounded to an integer).
+// For fp16 x and s the fp32 rounding in the middle never changes the result (x / s cannot come within
+// 2^-23 relative of an fp16 rounding midpoint without hitting it), so the task is the correctly
+// rounded fp16 quotient.  Two routes produce it:
+//
+//  * packed route (scales >= 2^-14, i.e. every row whose abs-max is above 0.0078): all in f16x2
+//    arithmetic, two values per instruction.  With s' = s * 2^-e in [1, 2), x' = x * 2^-e and
+//    r = f16(1 / s'):  q = x' * r;  rem = fma(-q, s', x');  q' = fma(rem, r, q).  q' equals the
+//    correctly rounded x' / s' for every pair of 11-bit significands with 0.25 <= |x'/s'| <= 128 (checked
+//    exhaustively on the CPU; smaller quotients give code 0 on any route).  rint is the addition of
+//    1536 = 1.5 * 2^10, after which the code is the low byte of each half.
+//  * fp32 route (tiny scales, where 2^-e is not an fp16 number): x * (1/s) in fp32 is within 3 ulps
+//    of the correctly rounded quotient and rounds to the same fp16 value unless it lies within 8 fp32
+//    ulps of an fp16 rounding midpoint; only then is the IEEE division carried out.
+constexpr float kRoundMagic = 12582912.0f;   // 1.5 * 2^23: (v + magic) holds rint(v) in its low mantissa bits
+
+struct RowQuant {
+  float s, inv;                 // scale and its fp32 reciprocal (fp32 route)
+  __half2 pow2, rcp, neg_sp;    // 2^-e, f16(1 / s'), -s' (packed route)
+  __half2 s2;                   // scale, both halves
+  bool packed;
+};
+
+__device__ __forceinline__ RowQuant make_row_quant(float s) {   // s > 0, an fp16 value held in fp32
+  RowQuant rq;
+  rq.s = s;
+  rq.inv = __frcp_rn(s);
+  const int e = static_cast<int>(__float_as_uint(s) >> 23) - 127;
+  rq.packed = e >= -14;
+  const float p = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e
+  const float sp = s * p;                                                    // exact, in [1, 2)
+  rq.pow2 = __float2half2_rn(p);
+  rq.rcp = __float2half2_rn(__frcp_rn(sp));
+  rq.neg_sp = __float2half2_rn(-sp);
+  rq.s2 = __float2half2_rn(s);
+  return rq;
+}
+
+// Packed route: two values -> f16x2 holding 1536 + code in each half.
+__device__ __forceinline__ __half2 quant_pair_packed(__half2 x, const RowQuant& rq) {
+  const __half2 xp = __hmul2_rn(x, rq.pow2);
+  const __half2 q = __hmul2_rn(xp, rq.rcp);
+  const __half2 rem = __hfma2(q, rq.neg_sp, xp);
+  const __half2 q2 = __hfma2(rem, rq.rcp, q);
+  return __hadd2_rn(q2, __float2half2_rn(1536.0f));
+}
+
+__device__ __forceinline__ float quotient_for_f16(float x, float s, float inv_s) {
+  float c = x * inv_s;
+  const uint32_t low = __float_as_uint(c) & 0x1FFFu;        // the 13 mantissa bits fp16 drops
+  if ((low - 0x0FF8u) <= 0x10u) {                           // within 8 ulps of the midpoint 0x1000
+    if (fabsf(c) >= 0.25f) c = __fdiv_rn(x, s);
+  }
+  return c;
+}
+
+// fp32 route: two values -> (code + kRoundMagic) each; the code is the low byte of each bit pattern.
+__device__ __forceinline__ float2 quant_pair_biased(__half2 h, float s, float inv_s) {
+  const float2 x = __half22float2(h);
+  const float c0 = quotient_for_f16(x.x, s, inv_s);
+  const float c1 = quotient_for_f16(x.y, s, inv_s);
+  const float2 r = __half22float2(__floats2half2_rn(c0, c1));
+  return make_float2(__fadd_rn(r.x, kRoundMagic), __fadd_rn(r.y, kRoundMagic));
+}
+
+__device__ __forceinline__ uint32_t pack_biased_codes(float2 a, float2 b) {
+  const uint32_t lo = __byte_perm(__float_as_uint(a.x), __float_as_uint(a.y), 0x0040);
+  const uint32_t hi = __byte_perm(__float_as_uint(b.x), __float_as_uint(b.y), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+// Eight fp16 values (one 128-bit load) -> eight packed int8 codes.
+__device__ __forceinline__ uint2 quant8_pack(const uint4& raw, const RowQuant& rq) {
+  const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+  if (rq.packed) {
+    const uint32_t a = h2_bits(quant_pair_packed(h2[0], rq)), b = h2_bits(quant_pair_packed(h2[1], rq));
+    const uint32_t c = h2_bits(quant_pair_packed(h2[2], rq)), d = h2_bits(quant_pair_packed(h2[3], rq));
+    return make_uint2(__byte_perm(a, b, 0x6420), __byte_perm(c, d, 0x6420));
+  }
+  const float2 a = quant_pair_biased(h2[0], rq.s, rq.inv), b = quant_pair_biased(h2[1], rq.s, rq.inv);
+  const float2 c = quant_pair_biased(h2[2], rq.s, rq.inv), d = quant_pair_biased(h2[3], rq.s, rq.inv);
+  return make_uint2(pack_biased_codes(a, b), pack_biased_codes(c, d));
+}
+
+// Same, also producing the fake-quantised values f16(code * s).  Their sign is the input's (s > 0),
+// which restores the -0 that round_() keeps for small negative quotients and the biased addition loses.
+__device__ __forceinline__ uint2 quant8_pack_fake(const uint4& raw, const RowQuant& rq, uint4& fake) {
+  const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+  const uint32_t* xin = reinterpret_cast<const uint32_t*>(&raw);
+  uint32_t* fo = reinterpret_cast<uint32_t*>(&fake);
+  if (rq.packed) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 b = quant_pair_packed(h2[j], rq);
+      w[j] = h2_bits(b);
+      const __half2 f = __hmul2_rn(__hsub2_rn(b, __float2half2_rn(1536.0f)), rq.s2);
+      fo[j] = (h2_bits(f) & 0x7FFF7FFFu) | (xin[j] & 0x80008000u);
+    }
+    return make_uint2(__byte_perm(w[0], w[1], 0x6420), __byte_perm(w[2], w[3], 0x6420));
+  }
+  float2 b[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b[j] = quant_pair_biased(h2[j], rq.s, rq.inv);
+    const __half2 f = __floats2half2_rn(__fmul_rn(__fsub_rn(b[j].x, kRoundMagic), rq.s),
+                                        __fmul_rn(__fsub_rn(b[j].y, kRoundMagic), rq.s));
+    fo[j] = (h2_bits(f) & 0x7FFF7FFFu) | (xin[j] & 0x80008000u);
+  }
+  return make_uint2(pack_biased_codes(b[0], b[1]), pack_biased_codes(b[2], b[3]));
+}
+
+// max |x| over eight fp16 values, folded into a running half2 maximum.
+__device__ __forceinline__ __half2 absmax8(__half2 running, const uint4& raw) {
+  const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) running = __hmax2(running, __habs2(h2[j]));
+  return running;
+}
+__device__ __forceinline__ float absmax_to_float(__half2 m) {
+  const float2 f = __half22float2(m);
+  return fmaxf(f.x, f.y);
+}
+
 // ---- int4 -> fp16 dequantisation ------------------------------------------
 // One packed word holds the codes of columns 8c..8c+7, low nibble first.
 // dequant8 returns them as four half2 in the order

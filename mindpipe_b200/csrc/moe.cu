@@ -134,17 +134,11 @@ moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict
   }
   __syncthreads();
   const float sf = s_scale;
+  const RowQuant rq = make_row_quant(sf);
   int8_t* qr = routed_q + (size_t)s_dest * H;
   for (int c = threadIdx.x; c < chunks; c += 256) {
     uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
-    const __half* h = reinterpret_cast<const __half*>(&raw);
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(h[j]), sf)))))) & 0xFFu) << (8 * j);
-      w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(h[j + 4]), sf)))))) & 0xFFu) << (8 * j);
-    }
-    *reinterpret_cast<uint2*>(qr + c * 8) = make_uint2(w0, w1);
+    *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
   }
 }
 
@@ -157,19 +151,13 @@ moe_requant_kernel(const __half* __restrict__ h, const unsigned int* __restrict_
   if (row >= *num_tiles * kTileRows) return;
   const float eps = h2f(f2h(1e-5f));
   const float sf = h2f(f2h(__fdiv_rn(fmaxf(__uint_as_float(absmax_bits[row]), eps), 127.0f)));
+  const RowQuant rq = make_row_quant(sf);
   if (threadIdx.x == 0) scale[row] = sf;
   const __half* hr = h + (size_t)row * I;
   int8_t* qr = q + (size_t)row * I;
   for (int c = threadIdx.x; c < (I >> 3); c += 256) {
     uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
-    const __half* hh = reinterpret_cast<const __half*>(&raw);
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      w0 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hh[j]), sf)))))) & 0xFFu) << (8 * j);
-      w1 |= (static_cast<uint32_t>(static_cast<int>(rintf(h2f(f2h(__fdiv_rn(h2f(hh[j + 4]), sf)))))) & 0xFFu) << (8 * j);
-    }
-    *reinterpret_cast<uint2*>(qr + c * 8) = make_uint2(w0, w1);
+    *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
   }
 }
 

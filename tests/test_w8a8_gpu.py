@@ -46,6 +46,25 @@ def test_act_quant_cfg3_full_size():
     _check_quant(synth.outlier_activation(4096, 4096, seed=0, index=100).numpy())
 
 
+@pytest.mark.parametrize("k", [4096, 8192])
+@pytest.mark.parametrize("amax", [1e-6, 1e-4, 0.004, 0.00775, 0.0079, 0.0371, 1.0, 1.9995, 3.1416, 77.25, 1000.0, 65504.0])
+def test_act_quant_every_fp16_value(amax, k):
+    """Every finite fp16 value of magnitude <= amax, quantised against the scale amax pins: the kernel's
+    division-free routes (packed f16x2 for ordinary scales, fp32 for tiny ones) must give the code the IEEE
+    division gives, for all of them."""
+    allv = np.arange(65536, dtype=np.uint32).astype(np.uint16).view(np.float16)
+    a16 = np.float16(amax)
+    vals = allv[np.isfinite(allv) & (np.abs(allv.astype(np.float32)) <= np.float32(a16))]
+    per_row = k - 1
+    rows = -(-vals.size // per_row)
+    x = np.zeros((rows, k), np.float16)
+    x[:, 0] = a16
+    flat = np.zeros(rows * per_row, np.float16)
+    flat[:vals.size] = vals
+    x[:, 1:] = flat.reshape(rows, per_row)
+    _check_quant(x)
+
+
 def test_act_quant_3d_and_empty():
     from mindpipe_b200 import ops
     x = synth.normal_activation(6, 256, seed=1).reshape(2, 3, 256).cuda()
