@@ -128,7 +128,7 @@ def test_decode_repeat_calls_identical_and_workspace_rearmed():
 
 
 def test_decode_linearity_property_full_size():
-    """Size-independent check at a 70B shape: f(x1 + x2) ~ f(x1) + f(x2), f(2x) = 2 f(x) exactly."""
+    """Size-independent check at a 70B shape: f(2x) = 2 f(x) to within one fp16 rounding of the output."""
     from mindpipe_b200 import ops
     n, k = 8192, 8192
     w = synth.normal_weight(n, k, seed=5, index=1).cuda()
@@ -137,9 +137,14 @@ def test_decode_linearity_property_full_size():
     x = synth.normal_activation(8, k, seed=5, index=2).cuda()
     y = ops.w4a16_linear_decode(x, packed, sz)
     y2 = ops.w4a16_linear_decode(x * 2, packed, sz)
-    # scaling by a power of two is exact end to end, except where an output falls in the
-    # fp16 subnormal range (spacing 2^-24), whose rounding is not scale invariant
-    assert (y2.float() - 2 * y.float()).abs().max().item() <= 2.0 ** -23
+    # scaling by a power of two is exact end to end except for two roundings that are not scale
+    # invariant: outputs in the fp16 subnormal range (spacing 2^-24), and, in the folded kernel, the
+    # few activations below 2^-10, whose 1/16 multiple is subnormal (an absolute error of a few 1e-7
+    # in an output of magnitude ~1).  Either moves an output by at most one fp16 unit in the last
+    # place, or by 2^-19 absolutely where the output itself is a near-cancellation.
+    gap = (y2.float() - 2 * y.float()).abs()
+    assert bool((gap <= 2.0 ** -10 * (2 * y.float()).abs() + 2.0 ** -19).all())
+    assert (gap > 0).float().mean().item() < 0.01
     ref = (x.float() @ ops.w4a16_dequant(packed, scale, zero, n, k).float().T)
     err = (y.float() - ref).norm() / ref.norm()
     assert err.item() <= TOL
