@@ -14,8 +14,8 @@ region cycles through a pool of layer sets whose packed weights exceed the
 Reported metric: algorithmic HBM bytes per second of the W4A16 decode linears
 (packed codes + scales + packed zero points + X + Y, per linear, per step).
 ``value`` is measured with inputs resident in HBM and the step replayed from a
-CUDA graph; ``e2e`` goes through ``VllmPackedInt4Linear.forward`` with host
-buffers (pinned H2D of X and D2H of Y inside the timed region).  With N>1
+CUDA graph; ``e2e`` goes through ``VllmPackedInt4Linear.forward_host`` (the host-buffer
+C-ABI entry: pinned H2D of X, kernel and D2H of Y inside the timed region).  With N>1
 every rank runs an independent replica (this config does not shard) and the
 values add up ("weak").  ``--impl reference`` times the reference's CPU path
 for the same linears, ``F.linear(x, Wdq)`` on the host cores.
@@ -377,9 +377,7 @@ def run_ours(args, rank, world, local_rank):
     # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
     def e2e_step(layer):
         for name, mod in layer:
-            xd = x_host[name].to(dev, non_blocking=True)
-            y = mod(xd)
-            y_host[name].copy_(y, non_blocking=True)
+            mod.forward_host(x_host[name], y_host[name])      # H2D of X, kernel, D2H of Y on one stream
         torch.cuda.synchronize()
 
     e2e_s = float("nan")

@@ -102,6 +102,19 @@ int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const v
                               mp_stream_t stream);
 
 /*
+ * Host-buffer form of the decode linear for M <= 16, for a host that keeps its
+ * activations in (preferably pinned) host memory, as the reference's CPU
+ * forward does (quantizer.py:109-130 runs nn.Linear on host tensors): copies
+ * x_host into x_stage, runs the linear into y_stage and copies the result to
+ * y_host, all enqueued on `stream` without blocking; y_host is valid once the
+ * stream has been synchronised.  x_stage [M,K] and y_stage [M,N] are device
+ * buffers of the caller (nothing is allocated here).
+ */
+int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
+                                const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
+                                void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream);
+
+/*
  * Prefill variant (any M; meant for M > 64): the same linear on the fp16 tensor
  * cores (tcgen05 kind::f16, fp32 accumulators in TMEM), activations fed by TMA,
  * int4 unpack + group dequant fused in as a producer stage that writes the

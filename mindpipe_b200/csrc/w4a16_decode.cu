@@ -544,6 +544,20 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   return launch_decode<4, false, 2, 4>(p, pl, st);
 }
 
+extern "C" int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
+                                           const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
+                                           void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream) {
+  if (!x_host_f16 || !x_stage_f16 || !y_stage_f16 || !y_host_f16) return MP_ERR_INVALID_ARG;
+  if (M > 16) return MP_ERR_UNSUPPORTED;          // the scratch-free kernels only
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MP_CUDA_TRY(cudaMemcpyAsync(x_stage_f16, x_host_f16, (size_t)M * K * sizeof(__half), cudaMemcpyHostToDevice, st));
+  const int rc = mp_w4a16_linear_decode_ex(x_stage_f16, packed_i32, sz_f16x2, bias_f16, y_stage_f16, M, N, K, group,
+                                           nullptr, 0, 0, stream);
+  if (rc != MP_OK) return rc;
+  MP_CUDA_TRY(cudaMemcpyAsync(y_host_f16, y_stage_f16, (size_t)M * N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  return MP_OK;
+}
+
 extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                                       const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                                       void* workspace, size_t workspace_bytes, mp_stream_t stream) {

@@ -55,6 +55,7 @@ class VllmPackedInt4Linear(nn.Module):
             raise ValueError(f"scale shape {tuple(self.weight_scale.shape)} does not divide in_features")
         self.group_size = self.in_features // int(self.weight_scale.shape[1])
         self._scale_zero = None   # kernel-side layout, built on first use
+        self._host_stage = {}     # row count -> (x, y) device staging buffers of forward_host
 
     # -- construction -------------------------------------------------------
     @staticmethod
@@ -99,6 +100,22 @@ class VllmPackedInt4Linear(nn.Module):
             x2 = x2.contiguous()
         y = ops.w4a16_linear(x2, self.weight_packed, self._scale_zero, self.bias)
         return y.reshape(*shape[:-1], self.out_features)
+
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None) -> torch.Tensor:
+        """Decode (<= 16 rows) on a CPU fp16 tensor, as the reference's CPU forward takes it: the H2D
+        copy, the kernel and the D2H copy are enqueued on the current stream and the call returns at
+        once; read ``y_host`` after synchronising.  Staging buffers are kept per row count."""
+        if self._scale_zero is None:
+            self.process_weights_after_loading()
+        m = x_host.shape[0]
+        stage = self._host_stage.get(m)
+        if stage is None:
+            dev = self.weight_packed.device
+            stage = (torch.empty((m, self.in_features), dtype=torch.float16, device=dev),
+                     torch.empty((m, self.out_features), dtype=torch.float16, device=dev))
+            self._host_stage[m] = stage
+        return ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias, y_host=y_host,
+                                            x_stage=stage[0], y_stage=stage[1])
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "

@@ -152,6 +152,37 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
     return y
 
 
+def w4a16_linear_decode_host(x_host, weight_packed, scale_zero, bias=None, *, y_host=None, x_stage=None, y_stage=None):
+    """Decode linear (M <= 16) on HOST activations: H2D copy, kernel and D2H copy are enqueued on the
+    current stream and the call returns without waiting; ``y_host`` is valid after the stream (or
+    device) has been synchronised.  ``x_host`` / ``y_host`` are CPU fp16 tensors (pinned memory makes
+    the copies asynchronous); ``x_stage`` / ``y_stage`` are optional device staging buffers to reuse.
+    """
+    if x_host.device.type != "cpu" or x_host.dtype != torch.float16 or x_host.dim() != 2 or not x_host.is_contiguous():
+        raise ValueError("x_host must be a contiguous 2-D fp16 CPU tensor")
+    p = _req(weight_packed, "weight_packed", torch.int32, 2)
+    sz = _req(scale_zero, "scale_zero", torch.float16, 3)
+    b = None if bias is None else _req(bias, "bias", torch.float16, 1)
+    m, k = x_host.shape
+    n = p.shape[0]
+    groups = sz.shape[0]
+    if p.shape[1] * 8 != k or sz.shape[1] != n or k % groups:
+        raise ValueError(f"shape mismatch: x{tuple(x_host.shape)} packed{tuple(p.shape)} sz{tuple(sz.shape)}")
+    if y_host is None:
+        y_host = torch.empty((m, n), dtype=torch.float16).pin_memory()
+    if y_host.device.type != "cpu" or y_host.dtype != torch.float16 or tuple(y_host.shape) != (m, n) \
+            or not y_host.is_contiguous():
+        raise ValueError(f"y_host must be a contiguous fp16 CPU tensor [{m}, {n}]")
+    xs = torch.empty((m, k), dtype=torch.float16, device=p.device) if x_stage is None else _req(x_stage, "x_stage", torch.float16, 2)
+    ys = torch.empty((m, n), dtype=torch.float16, device=p.device) if y_stage is None else _req(y_stage, "y_stage", torch.float16, 2)
+    if tuple(xs.shape) != (m, k) or tuple(ys.shape) != (m, n):
+        raise ValueError("staging buffers must be [M, K] and [M, N]")
+    st = _lib.load().mp_w4a16_linear_decode_host(x_host.data_ptr(), xs.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b),
+                                                 ys.data_ptr(), y_host.data_ptr(), m, n, k, k // groups, _stream())
+    _lib.check(st, "w4a16_linear_decode_host", M=m, N=n, K=k, group=k // groups)
+    return y_host
+
+
 def w4a16_linear_decode_static(x, weight_packed, scale_zero, bias=None, out=None):
     """Decode linear that takes no scratch from the caller and allocates none.
 

@@ -167,6 +167,27 @@ def test_module_forward_matches_reference_forward(golden):
     assert O.rel_frobenius(big.cpu().numpy()[:5], g["y"]) <= TOL
 
 
+@pytest.mark.parametrize("m", [1, 16])
+def test_host_buffer_entry_matches_device_entry(m):
+    """The host-buffer form (H2D copy, kernel, D2H copy on one stream) gives the device entry's bits."""
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    n, k = 512, 1024
+    lin = torch.nn.Linear(k, n, bias=True).half().cuda()
+    mod = VllmPackedInt4Linear.from_float(lin)
+    x_host = synth.normal_activation(m, k, seed=3, index=m).pin_memory()
+    y_host = torch.empty((m, n), dtype=torch.float16).pin_memory()
+    for _ in range(2):                                   # second call reuses the staging buffers
+        y_host.zero_()
+        out = mod.forward_host(x_host, y_host)
+        torch.cuda.synchronize()
+        assert out is y_host
+        assert torch.equal(y_host, mod(x_host.cuda()).cpu())
+    with pytest.raises(ValueError):
+        mod.forward_host(x_host.cuda(), y_host)
+    with pytest.raises(RuntimeError):
+        mod.forward_host(synth.normal_activation(17, k, seed=3).pin_memory())
+
+
 def test_errors_are_loud():
     from mindpipe_b200 import _lib, ops
     x = torch.zeros(1, 64, dtype=torch.float16, device="cuda")             # K = 64 is not a multiple of 128
