@@ -30,7 +30,10 @@ __device__ __forceinline__ void emit_codes(const uint4& raw, const RowQuant& rq,
 // One warp per row (rows of up to 32 * 8 * NV columns): the row is read once with NV independent
 // 128-bit loads per lane, reduced with shuffles only, and quantised from registers -- no block-level
 // synchronisation at all.
-template <int NV>
+// CODES / FAKE select the outputs at compile time and the rare tiny-scale rows take a rolled loop that
+// re-reads the row, so the unrolled body holds one route only (the kernel stays small enough for the
+// instruction cache).
+template <int NV, bool CODES, bool FAKE>
 __global__ void __launch_bounds__(128)
 act_quant_warp_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
                       float* __restrict__ scale, __half* __restrict__ fake) {
@@ -53,14 +56,35 @@ act_quant_warp_kernel(const __half* __restrict__ x, int M, int K, int8_t* __rest
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   const float eps = h2f(f2h(1e-5f));                                   // clamp_(min=1e-5) on an fp16 tensor
   const float sf = h2f(f2h(__fdiv_rn(fmaxf(amax, eps), 127.0f)));      // div_(q_max), rounded to fp16
-  const RowQuant rq = make_row_quant(sf);
+  RowQuant rq = make_row_quant(sf);
   if (lane == 0 && scale) scale[row] = sf;
+  int8_t* qr = CODES ? q + (size_t)row * K : nullptr;
+  __half* fr = FAKE ? fake + (size_t)row * K : nullptr;
+  if (!rq.packed) {                                   // scale below 2^-14: fp32 route, rolled
+#pragma unroll 1
+    for (int c = lane; c < chunks; c += 32)
+      emit_codes(*reinterpret_cast<const uint4*>(xr + c * 8), rq, CODES ? qr + c * 8 : nullptr,
+                 FAKE ? fr + c * 8 : nullptr);
+    return;
+  }
+  rq.packed = true;                                   // lets the compiler drop the other route below
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int c = lane + v * 32;
     if (c >= chunks) continue;
-    emit_codes(held[v], rq, q ? q + (size_t)row * K + c * 8 : nullptr,
-               fake ? fake + (size_t)row * K + c * 8 : nullptr);
+    emit_codes(held[v], rq, CODES ? qr + c * 8 : nullptr, FAKE ? fr + c * 8 : nullptr);
+  }
+}
+
+template <int NV>
+static void launch_act_quant_warp(const __half* x, int M, int K, int8_t* q, float* sc, __half* fk, cudaStream_t st) {
+  const unsigned blocks = static_cast<unsigned>((M + 3) / 4);
+  if (q && fk) {
+    act_quant_warp_kernel<NV, true, true><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+  } else if (q) {
+    act_quant_warp_kernel<NV, true, false><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+  } else {
+    act_quant_warp_kernel<NV, false, true><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
   }
 }
 
@@ -332,13 +356,12 @@ extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i
   int8_t* q = static_cast<int8_t*>(q_i8);
   float* sc = static_cast<float*>(scale_f32);
   __half* fk = static_cast<__half*>(fake_f16);
-  const unsigned warp_blocks = static_cast<unsigned>((M + 3) / 4);
   if (K <= 1024) {
-    act_quant_warp_kernel<4><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    launch_act_quant_warp<4>(x, M, K, q, sc, fk, st);
   } else if (K <= 2048) {
-    act_quant_warp_kernel<8><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    launch_act_quant_warp<8>(x, M, K, q, sc, fk, st);
   } else if (K <= 4096) {
-    act_quant_warp_kernel<16><<<warp_blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    launch_act_quant_warp<16>(x, M, K, q, sc, fk, st);
   } else if (K <= 8192) {
     act_quant_kernel<512, 2><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
   } else if (K <= 16384) {

@@ -1,11 +1,11 @@
 // W4A16 prefill GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T on the fp16 tensor
 // cores, with the int4 unpack + group dequant fused in as a producer stage.
 //
-// One persistent CTA per SM, 14 warps:
-//   warp 0      TMA producer for the activation tile x[128 x 64] (128-byte swizzle)
+// One persistent CTA per SM, 14 warps (128-row tile, MT = 1) or 18 warps (256-row tile, MT = 2):
+//   warp 0      TMA producer for the activation tile x[128 MT x 64] (128-byte swizzle)
 //   warp 1      MMA issuer: tcgen05.mma kind::f16, M=128, N=256, K=16, fp32 in TMEM
-//   warps 2-5   epilogue: tcgen05.ld -> (+bias) -> fp16 -> global (TMEM double buffered)
-//   warps 6-13  dequant producers: stream the packed int4 words of the weight tile
+//   next 4 MT   epilogue warps: tcgen05.ld -> (+bias) -> fp16 -> global
+//   last 8      dequant producers: stream the packed int4 words of the weight tile
 //               [256 rows x 64 columns] from global memory with 128-bit loads, expand
 //               them with dequant8 (exactly f16((u - z) * s), the reference's Wdq) and
 //               store them into shared memory in the canonical K-major 128-byte-swizzle
@@ -211,23 +211,26 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       const bool n_ok = n < p.N;
       const uint32_t* row = p.packed + (size_t)(n_ok ? n : 0) * words_per_row;
       const uint32_t* szp = p.sz + (n_ok ? n : 0);
-      // software pipeline: the words of k-block kb+1 are in flight while kb is expanded
-      uint4 q0, q1;
-      auto fetch = [&](int kb) {
+      // software pipeline: the words of the next kPrefetch k-blocks are in flight while one is
+      // expanded (a k-block lasts about 1000 tensor cycles, a global load under load about as long)
+      constexpr int kPrefetch = 3;
+      uint4 q0[kPrefetch], q1[kPrefetch];
+      uint32_t szq[kPrefetch];
+      auto fetch = [&](int kb, uint4& a, uint4& b, uint32_t& z) {
+        const bool live = n_ok && kb < p.k_blocks;
         const uint32_t* src = row + kb * (kBK / 8);
-        q0 = n_ok ? ldg_stream_v4(src) : make_uint4(0, 0, 0, 0);
-        q1 = n_ok ? ldg_stream_v4(src + 4) : make_uint4(0, 0, 0, 0);
+        a = live ? ldg_stream_v4(src) : make_uint4(0, 0, 0, 0);
+        b = live ? ldg_stream_v4(src + 4) : make_uint4(0, 0, 0, 0);
+        z = live ? __ldg(szp + (size_t)((kb * kBK) / p.group) * p.N) : 0u;
       };
-      fetch(0);
-      uint32_t szw = n_ok ? __ldg(szp) : 0u;
+#pragma unroll
+      for (int d = 0; d < kPrefetch; ++d) fetch(d, q0[d], q1[d], szq[d]);
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        const uint4 c0 = q0, c1 = q1;
-        const uint32_t szc = szw;
-        if (kb + 1 < p.k_blocks) {
-          fetch(kb + 1);
-          const int grp_next = ((kb + 1) * kBK) / p.group;
-          szw = n_ok ? __ldg(szp + (size_t)grp_next * p.N) : 0u;
-        }
+        const uint4 c0 = q0[0], c1 = q1[0];
+        const uint32_t szc = szq[0];
+#pragma unroll
+        for (int d = 0; d + 1 < kPrefetch; ++d) { q0[d] = q0[d + 1]; q1[d] = q1[d + 1]; szq[d] = szq[d + 1]; }
+        fetch(kb + kPrefetch, q0[kPrefetch - 1], q1[kPrefetch - 1], szq[kPrefetch - 1]);
         const __half2 hz = *reinterpret_cast<const __half2*>(&szc);
         const ScaleZero sp = make_scale_zero(__low2half(hz), __high2half(hz));
         if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag))) { ok = false; break; }

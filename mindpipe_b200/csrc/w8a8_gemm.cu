@@ -53,22 +53,27 @@ struct GemmParams {
   int* error_word;
 };
 
-template <int BN>
+// PAIR: two CTAs (a cluster of 2) share each MMA -- a 256 x BN tile, 128 rows of A and of the
+// accumulator per CTA, and each CTA stages only its half of the BN weight rows.  Per CTA and k-block
+// the shared memory then carries 16 KB (A) + BN/2 x 128 B (B) in and the same out, instead of
+// 16 KB + BN x 128 B: at BN = 256 that is 64 KB rather than 96 KB per 512 tensor cycles, which takes
+// the kernel off the 128 B/clk shared-memory limit that held the single-CTA form at ~70 % tensor use.
+template <int BN, bool PAIR = false>
 struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kABytes = kBM * kBK;
-  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * kBK;
+  static constexpr int kStages = PAIR ? (BN == 256 ? 6 : 8) : (BN == 256 ? 4 : 6);
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kBarBytes = 256;
   static constexpr int kScaleBytes = 3 * 4 * 256 * 4;   // per epilogue warp: 256 channel scales (+ zero points, row sums)
   static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes + kScaleBytes;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(192, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   constexpr int STAGES = Cfg::kStages;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -82,6 +87,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // PAIR: rank 0 of the cluster leads (issues the MMAs, owns the "full" and "accumulator free"
+  // barriers); both CTAs own a "stage empty" and an "accumulator full" barrier that the leader's
+  // commits arrive on.  Every WAIT in the kernel is on a barrier of the waiting CTA.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -89,22 +99,36 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 4);     // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * b, PAIR ? 8 : 4);     // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) {            // the peer's barriers exist before anything signals them
+    cluster_arrive();
+    cluster_wait();
+  }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int m_tiles = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
+  // tiles are 128 (PAIR: 256) rows of the activations; the grouped plan counts 128-row units
+  const int m_units = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
+  const int m_tiles = PAIR ? (m_units + 1) / 2 : m_units;
   const int total = m_tiles * p.n_tiles;
+  const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+  const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
+  constexpr int kRowsPerTile = PAIR ? 2 * kBM : kBM;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -113,37 +137,50 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
         const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-        const int m0 = m_tile * kBM;
-        const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
+        const int m0 = m_tile * kRowsPerTile + static_cast<int>(rank) * kBM;
+        const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
-          const uint32_t full = full0 + 8 * stage;
-          mbar_arrive_expect_tx(full, Cfg::kABytes + Cfg::kBBytes);
-          tma_load_2d(smem_u32(sA + stage * Cfg::kABytes), &tmap_a, full, kb * kBK, m0);
-          if (EPI == EPI_SWIGLU) {
-            // gate rows then the matching up rows: the tile's columns [0,128) and [128,256)
-            const uint32_t dst = smem_u32(sB + stage * Cfg::kBBytes);
-            tma_load_2d(dst, &tmap_b, full, kb * kBK, e_row0 + n_tile * 128);
-            tma_load_2d(dst + 128 * kBK, &tmap_b, full, kb * kBK, e_row0 + p.up_row_offset + n_tile * 128);
+          if (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier
+            const uint32_t full = map_to_cta(full0 + 8 * stage, 0);
+            if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * (Cfg::kABytes + Cfg::kBBytes));
+            tma_load_2d_pair(smem_u32(sA + stage * Cfg::kABytes), &tmap_a, full, kb * kBK, m0);
+            // this CTA's half of the tile's weight rows; with SwiGLU the halves are the gate rows
+            // (accumulator columns [0,128)) and the matching up rows (columns [128,256))
+            const int b_row = EPI == EPI_SWIGLU
+                                  ? e_row0 + (rank ? p.up_row_offset : 0) + n_tile * 128
+                                  : e_row0 + n_tile * BN + static_cast<int>(rank) * (BN / 2);
+            tma_load_2d_pair(smem_u32(sB + stage * Cfg::kBBytes), &tmap_b, full, kb * kBK, b_row);
           } else {
-            tma_load_2d(smem_u32(sB + stage * Cfg::kBBytes), &tmap_b, full, kb * kBK, e_row0 + n_tile * BN);
+            const uint32_t full = full0 + 8 * stage;
+            mbar_arrive_expect_tx(full, Cfg::kABytes + Cfg::kBBytes);
+            tma_load_2d(smem_u32(sA + stage * Cfg::kABytes), &tmap_a, full, kb * kBK, m0);
+            if (EPI == EPI_SWIGLU) {
+              // gate rows then the matching up rows: the tile's columns [0,128) and [128,256)
+              const uint32_t dst = smem_u32(sB + stage * Cfg::kBBytes);
+              tma_load_2d(dst, &tmap_b, full, kb * kBK, e_row0 + n_tile * 128);
+              tma_load_2d(dst + 128 * kBK, &tmap_b, full, kb * kBK, e_row0 + p.up_row_offset + n_tile * 128);
+            } else {
+              tma_load_2d(smem_u32(sB + stage * Cfg::kBBytes), &tmap_b, full, kb * kBK, e_row0 + n_tile * BN);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    if (elect_one()) {
+    if (leader && elect_one()) {
       constexpr uint32_t idesc =
-          umma_idesc(kIdescDFormatS32 | (EPI == EPI_AFFINE ? kIdescABFormatU8 : kIdescABFormatS8), kBM, BN);
+          umma_idesc(kIdescDFormatS32 | (EPI == EPI_AFFINE ? kIdescABFormatU8 : kIdescABFormatS8), kRowsPerTile, BN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
         if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
@@ -155,13 +192,27 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
             // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in 16-byte address units
-            umma_i8(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+            if (PAIR) {
+              umma_i8_pair(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+            } else {
+              umma_i8(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+            }
           }
-          umma_commit(empty0 + 8 * stage);
+          if (PAIR) {                      // release the stage in both CTAs
+            umma_commit_pair(empty0 + 8 * stage);
+            umma_commit_pair(map_to_cta(empty0 + 8 * stage, 1));
+          } else {
+            umma_commit(empty0 + 8 * stage);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull0 + 8 * buf);
+        if (PAIR) {                        // publish the accumulator halves to both CTAs' epilogues
+          umma_commit_pair(tfull0 + 8 * buf);
+          umma_commit_pair(map_to_cta(tfull0 + 8 * buf, 1));
+        } else {
+          umma_commit(tfull0 + 8 * buf);
+        }
         if (++buf == 2) { buf = 0; buf_phase ^= 1; }
       }
     }
@@ -172,9 +223,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int* my_wsum = reinterpret_cast<int*>(my_scales + 512);   // ... and channel code sums
     int buf = 0;
     uint32_t buf_phase = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty0, 0) : tempty0;
+    for (int tile = first_tile; tile < total; tile += tile_step) {
       const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-      const int e_row0 = p.tile_expert ? p.tile_expert[m_tile] * p.b_rows_per_expert : 0;
+      const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
       // channel scales of this tile -> shared memory (each warp keeps its own copy: no cross-warp barrier)
       if (EPI != EPI_I32) {
         __syncwarp();
@@ -200,7 +252,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // the whole warp takes the same way out: the TMEM loads below are warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
-      const int row = m_tile * kBM + quarter * 32 + lane;
+      const int row = m_tile * kRowsPerTile + static_cast<int>(rank) * kBM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const float sa = (EPI != EPI_I32 && row_ok) ? p.a_scale[row] : 0.0f;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
@@ -318,12 +370,25 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+      if (lane == 0) {
+        if (PAIR) {
+          mbar_arrive_cluster(tempty_leader0 + 8 * buf);
+        } else {
+          mbar_arrive(tempty0 + 8 * buf);
+        }
+      }
       if (++buf == 2) { buf = 0; buf_phase ^= 1; }
     }
   }
 
   __syncthreads();
+  if (PAIR) {
+    // a CTA that gave up tells its peer (whose waits poll the flag) before both meet at the cluster
+    // barrier; the peer cannot have left yet, so its shared memory is still there
+    if (*abort_flag && threadIdx.x == 0) st_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u), 1u);
+    cluster_arrive();       // the leader's MMAs read the peer's shared memory: nobody leaves early
+    cluster_wait();
+  }
   if (*abort_flag) {
     if (threadIdx.x == 0 && p.error_word) atomicExch(p.error_word, 1);
     // give copies still in flight time to land before the shared memory goes away
@@ -333,7 +398,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) {
+      tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    } else {
+      tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
   }
 }
 
@@ -388,15 +457,15 @@ struct GemmCall {
   int* error_word;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 static int launch_gemm(const GemmCall& c, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   CUtensorMap ta, tb;
   int rc = encode_tensor_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, (uint64_t)c.K, (uint64_t)c.a_rows,
                                 (uint64_t)c.K, kBK, kBM);
   if (rc != MP_OK) return rc;
   rc = encode_tensor_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, (uint64_t)c.K, (uint64_t)c.b_rows_total,
-                            (uint64_t)c.K, kBK, EPI == EPI_SWIGLU ? 128 : BN);
+                            (uint64_t)c.K, kBK, PAIR ? BN / 2 : (EPI == EPI_SWIGLU ? 128 : BN));
   if (rc != MP_OK) return rc;
   GemmParams p{};
   p.M = c.M; p.N = c.N; p.K = c.K;
@@ -408,7 +477,7 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
   p.row_absmax = c.row_absmax; p.error_word = c.error_word;
   p.a_zero = c.a_zero; p.a_rowsum = c.a_rowsum; p.b_zero = c.b_zero; p.b_rowsum = c.b_rowsum;
-  auto kern = w8a8_gemm_kernel<BN, EPI>;
+  auto kern = w8a8_gemm_kernel<BN, EPI, PAIR>;
   static thread_local int configured_device = -1;
   int device = 0;
   MP_CUDA_TRY(cudaGetDevice(&device));
@@ -416,11 +485,35 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmem));
     configured_device = device;
   }
+  if (PAIR) {
+    // one cluster of two CTAs per 256-row tile in flight: 74 pairs fill the 148 SMs
+    const long long total = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
+    const int pairs = (int)(total < kSmCount / 2 ? total : kSmCount / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    return MP_OK;
+  }
   const long long total = (long long)p.m_tiles * p.n_tiles;
   const int grid = (int)(total < kSmCount ? total : kSmCount);
   kern<<<grid, 192, Cfg::kSmem, st>>>(ta, tb, p);
   MP_LAUNCH_CHECK();
   return MP_OK;
+}
+
+// The CTA-pair form pays once there are enough 256-row tiles to occupy the 74 pairs.
+static bool use_pair(int M, int N) {
+  return (long long)((M + 255) / 256) * ((N + 255) / 256) >= kSmCount / 2 && N > 128;
 }
 
 static int check_gemm_args(const void* a, const void* b, void* out, int M, int N, int K) {
@@ -470,6 +563,7 @@ extern "C" int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const vo
   c.a_scale = static_cast<const float*>(x_scale_f32); c.b_scale = static_cast<const float*>(w_scale_f32);
   c.bias = static_cast<const __half*>(bias_f16); c.out = y_f16; c.error_word = error_word;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, N)) return launch_gemm<256, EPI_F16, true>(c, st);
   const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_F16>(c, st);
   return launch_gemm<256, EPI_F16>(c, st);
@@ -483,6 +577,7 @@ extern "C" int mp_w8a8_gemm_i32(const void* qx_i8, const void* w_i8, void* acc_i
   c.a = qx_i8; c.b = w_i8; c.M = M; c.N = N; c.K = K; c.a_rows = M; c.b_rows_total = N;
   c.out = acc_i32; c.error_word = error_word;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, N)) return launch_gemm<256, EPI_I32, true>(c, st);
   const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_I32>(c, st);
   return launch_gemm<256, EPI_I32>(c, st);

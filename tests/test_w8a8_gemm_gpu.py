@@ -57,6 +57,20 @@ def test_int32_many_tiles_per_cta_and_both_tmem_buffers():
     assert np.array_equal(acc.cpu().numpy().astype(np.int64), exact_acc(qx, qw))
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (2304, 2304, 128),     # 9 x 9 pair tiles on 74 CTA pairs: one k-block, some pairs take two tiles
+    (2100, 2500, 384),     # ragged M and N: the second CTA of the last pair row is partly / fully out of range
+    (4096, 4096, 1024),    # 256 pair tiles, ring of 6 stages reused across tiles, both accumulator buffers
+])
+def test_int32_cta_pair_form_bit_exact(m, n, k):
+    """Shapes with >= 74 tiles of 256 x 256 run the two-CTA (cta_group::2) kernel."""
+    from mindpipe_b200 import ops
+    qx, qw = rand_i8((m, k), 5), rand_i8((n, k), 6)
+    acc = ops.w8a8_gemm_i32(dev(qx), dev(qw))
+    ops.check_device_errors()
+    assert np.array_equal(acc.cpu().numpy().astype(np.int64), exact_acc(qx, qw))
+
+
 def _w8a8_case(m, n, k, seed, bias=False):
     from mindpipe_b200 import ops
     x = synth.outlier_activation(m, k, seed=seed, index=100).numpy()
