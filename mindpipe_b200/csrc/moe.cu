@@ -16,7 +16,7 @@
 
 namespace mp {
 
-constexpr int kTileRows = 128;
+constexpr int kTileRows = kMoeTileRows;
 constexpr int kMaxExperts = 256;
 
 // softmax(fp32) -> top-k -> renormalise -> fp16, one thread per token
@@ -66,7 +66,7 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_entries, int
     if (s_counts[i]) atomicAdd(&counts[i], s_counts[i]);
 }
 
-// Padded segment offsets, the expert of every 128-row tile and the tile count.
+// Padded segment offsets (multiples of 256 rows), the expert of every 128-row tile and the tile count.
 // plan layout (ints): [0,E) counts | [E,2E) cursors | [2E,3E+1) seg_offsets | 3E+1 num_tiles | 3E+2.. tile_expert
 __global__ void moe_plan_kernel(int* __restrict__ plan, int E, int max_tiles) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -79,7 +79,7 @@ __global__ void moe_plan_kernel(int* __restrict__ plan, int E, int max_tiles) {
   for (int e = 0; e < E; ++e) {
     seg[e] = off;
     cursors[e] = 0;
-    const int nt = (counts[e] + kTileRows - 1) / kTileRows;
+    const int nt = moe_segment_tiles(counts[e]);
     for (int i = 0; i < nt && tiles < max_tiles; ++i) tile_expert[tiles++] = e;
     off += nt * kTileRows;
   }
@@ -242,12 +242,12 @@ extern "C" int mp_moe_router_topk(const void* logits_f32, int T, int E, int k, v
 }
 
 extern "C" size_t mp_moe_plan_ints(int num_local_experts, int max_rows) {
-  const int max_tiles = max_rows / kTileRows + num_local_experts;
+  const int max_tiles = mp_moe_padded_rows(num_local_experts, max_rows) / kTileRows;
   return (size_t)3 * num_local_experts + 2 + max_tiles;
 }
 
 extern "C" int mp_moe_padded_rows(int num_local_experts, int max_rows) {
-  return (max_rows / kTileRows + num_local_experts) * kTileRows;
+  return (max_rows / kMoeSegmentAlign + num_local_experts) * kMoeSegmentAlign;
 }
 
 extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* topk_ids_i32, int T, int H, int k,
@@ -297,7 +297,7 @@ extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_s
   if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || !w2_q_i8 || !w2_scale_f32 ||
       !d_out_f16 || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
     return MP_ERR_INVALID_ARG;
-  if (padded_rows % kTileRows != 0 || H % 16 != 0 || I % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
+  if (padded_rows % kMoeSegmentAlign != 0 || H % 16 != 0 || I % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
   if (!workspace || workspace_bytes < mp_moe_expert_stage_workspace_bytes(padded_rows, I)) return MP_ERR_WORKSPACE;
   if (!aligned(workspace, 256) || !aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16) || !aligned(w2_q_i8, 16) ||
       !aligned(d_out_f16, 16))

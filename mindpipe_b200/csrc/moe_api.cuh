@@ -5,6 +5,15 @@
 
 namespace mp {
 
+// Layout of expert-sorted rows: the plan counts tiles in units of 128 rows, and every expert's
+// segment starts at a multiple of 256 rows (an even number of units), so that both the 128-row
+// single-CTA tiles and the 256-row CTA-pair tiles of the grouped GEMMs stay inside one expert.
+constexpr int kMoeTileRows = 128;
+constexpr int kMoeSegmentAlign = 256;
+__host__ __device__ constexpr int moe_segment_tiles(int rows) {
+  return (rows + kMoeSegmentAlign - 1) / kMoeSegmentAlign * (kMoeSegmentAlign / kMoeTileRows);
+}
+
 // h[r, n] = f16(silu(f16(gate)) * f16(up)) for the expert-sorted int8 rows, plus per-row max |h|.
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,

@@ -20,11 +20,12 @@
 // spin).  One process per GPU: the waiting kernels of different ranks run on
 // different devices.  Only plain peer loads / stores are used.
 #include "common.cuh"
+#include "moe_api.cuh"
 
 namespace mp {
 
 constexpr int kMaxRanks = 16;
-constexpr int kEpTile = 128;
+constexpr int kEpTile = kMoeTileRows;
 
 struct PeerPtrs {
   void* p[kMaxRanks];
@@ -95,7 +96,7 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
     counts[e] = total;
     cursors[e] = 0;
     seg[e] = off;
-    const int nt = (total + kEpTile - 1) / kEpTile;
+    const int nt = moe_segment_tiles(total);
     for (int i = 0; i < nt && tiles < max_tiles; ++i) tile_expert[tiles++] = e;
     off += nt * kEpTile;
   }
@@ -185,7 +186,7 @@ extern "C" int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int 
   PeerPtrs pp;
   int rc = fill_peers(pp, peer_plan_ptrs, world);
   if (rc != MP_OK) return rc;
-  if (!xplan_i32 || num_experts <= 0 || num_experts % world != 0 || capacity_rows <= 0 || capacity_rows % kEpTile != 0)
+  if (!xplan_i32 || num_experts <= 0 || num_experts % world != 0 || capacity_rows <= 0 || capacity_rows % kMoeSegmentAlign != 0)
     return MP_ERR_INVALID_ARG;
   if (num_experts > 256) return MP_ERR_UNSUPPORTED;   // (local expert, source) pairs are staged in shared memory
   const int e_loc = num_experts / world;

@@ -17,7 +17,8 @@
 // acceleration/runtime_patches/vllm.patch:756-760), and the MoE gate/up GEMM
 // with the SwiGLU epilogue.  In grouped (MoE) mode every 128-row tile of the
 // expert-sorted activations belongs to one expert, whose weight rows start at
-// expert * rows_per_expert.
+// expert * rows_per_expert (segments are 256-row aligned, so a CTA pair's 256-row
+// tile belongs to one expert as well).
 //
 // Every mbarrier wait is bounded; on a timeout the block records an error
 // word, lets its copies land, frees its TMEM and returns.
@@ -37,6 +38,7 @@ enum : int { EPI_F16 = 0, EPI_I32 = 1, EPI_SWIGLU = 2, EPI_AFFINE = 3 };   // AF
 struct GemmParams {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
+  int group_m;                 // tile order: groups of this many M tiles are swept across all of N before the next group
   const int* m_tiles_dev;      // grouped: number of 128-row tiles in use (device side)
   const int* tile_expert;      // grouped: expert of each 128-row tile
   int b_rows_per_expert;       // grouped: weight rows per expert (2I for gate/up, H for down)
@@ -68,6 +70,22 @@ struct GemmCfg {
   static constexpr int kScaleBytes = 3 * 4 * 256 * 4;   // per epilogue warp: 256 channel scales (+ zero points, row sums)
   static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes + kScaleBytes;
 };
+
+// Tile order.  Concurrent CTAs work on consecutive tile numbers; a group of `group_m` M tiles is swept
+// over all N tiles before the next group starts (M fastest inside the group).  The activation rows of
+// one group (a few MB) and the weight tiles of a handful of N tiles are then the whole working set
+// of a wave, so both operands come from HBM about once even when neither matrix fits in L2 -- in the
+// MoE GEMMs a plain M-fastest order re-read the activations once per weight tile column (6 GB of DRAM
+// reads for 1 GB of operands).
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& m_tile, int& n_tile) {
+  const int per_group = group_m * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * group_m;
+  const int gsize = min(group_m, m_tiles - first_m);
+  const int in_group = tile - group * per_group;
+  m_tile = first_m + in_group % gsize;
+  n_tile = in_group / gsize;
+}
 
 template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(192, 1)
@@ -138,7 +156,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total; tile += tile_step) {
-        const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+        int m_tile, n_tile;
+        tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
         const int m0 = m_tile * kRowsPerTile + static_cast<int>(rank) * kBM;
         const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -225,7 +244,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t buf_phase = 0;
     const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty0, 0) : tempty0;
     for (int tile = first_tile; tile < total; tile += tile_step) {
-      const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      int m_tile, n_tile;
+      tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
       const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
       // channel scales of this tile -> shared memory (each warp keeps its own copy: no cross-warp barrier)
       if (EPI != EPI_I32) {
@@ -476,6 +496,7 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.b_rows_per_expert = c.b_rows_per_expert; p.up_row_offset = c.up_row_offset;
   p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
   p.row_absmax = c.row_absmax; p.error_word = c.error_word;
+  p.group_m = PAIR ? 8 : 16;            // 2048 activation rows per group
   p.a_zero = c.a_zero; p.a_rowsum = c.a_rowsum; p.b_zero = c.b_zero; p.b_rowsum = c.b_rowsum;
   auto kern = w8a8_gemm_kernel<BN, EPI, PAIR>;
   static thread_local int configured_device = -1;
@@ -534,7 +555,7 @@ int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, con
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = 2 * I; c.up_row_offset = I;
   c.row_absmax = row_absmax; c.error_word = error_word;
   MP_CUDA_TRY(cudaMemsetAsync(row_absmax, 0, sizeof(unsigned int) * (size_t)padded_rows, st));
-  return launch_gemm<256, EPI_SWIGLU>(c, st);
+  return launch_gemm<256, EPI_SWIGLU, true>(c, st);   // expert segments are 256-row aligned: pair tiles fit
 }
 
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
@@ -545,7 +566,7 @@ int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, cons
   c.a_scale = scale2; c.b_scale = w2_scale; c.out = d_out;
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = H;
   c.error_word = error_word;
-  return launch_gemm<256, EPI_F16>(c, st);
+  return launch_gemm<256, EPI_F16, true>(c, st);
 }
 
 }  // namespace mp
@@ -598,6 +619,7 @@ extern "C" int mp_w8a8_affine_gemm(const void* qx_u8, const void* x_scale_f32, c
   c.b_zero = static_cast<const float*>(w_zero_f32); c.b_rowsum = static_cast<const int*>(w_rowsum_i32);
   c.bias = static_cast<const __half*>(bias_f16); c.out = y_f16; c.error_word = error_word;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, N)) return launch_gemm<256, EPI_AFFINE, true>(c, st);
   const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_AFFINE>(c, st);
   return launch_gemm<256, EPI_AFFINE>(c, st);

@@ -6,7 +6,7 @@ each rank is
 
 1. route + gather + per-token int8 quantisation of the local tokens over ALL
    experts (``ops.moe_route_gather_quant``): rows sorted by expert, every
-   expert segment padded to a multiple of 128 rows;
+   expert segment padded to a multiple of 256 rows;
 2. exchange of the per-expert row counts, then ``all_to_all_single`` of the
    int8 rows and of their fp32 scales -- the chunk for rank ``p`` is the
    contiguous run of its experts' segments, so nothing is re-packed before
@@ -33,7 +33,8 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-TILE = 128
+TILE = 128          # unit in which the device plan counts tiles
+SEGMENT_ALIGN = 256  # every expert segment starts at a multiple of this (an even number of tiles)
 
 
 def expert_partition(num_experts: int, world_size: int) -> list[tuple[int, int]]:
@@ -45,7 +46,7 @@ def expert_partition(num_experts: int, world_size: int) -> list[tuple[int, int]]
 
 
 def _pad(n: np.ndarray | int):
-    return (n + TILE - 1) // TILE * TILE
+    return (n + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
 
 
 @dataclass
@@ -55,7 +56,7 @@ class ExchangePlan:
     gather_map: np.ndarray        # int32 [padded_rows]: expert-sorted row -> row in the receive buffer (-1 = padding)
     scatter_map: np.ndarray       # int32 [recv_rows]: receive-buffer row -> expert-sorted row (-1 = padding)
     plan_ints: np.ndarray         # int32 device plan: counts | cursors | segment offsets | tile count | tile experts
-    padded_rows: int              # rows of the expert-sorted buffers (multiple of 128, >= 128)
+    padded_rows: int              # rows of the expert-sorted buffers (multiple of 256, >= 256)
     recv_rows: int
 
 
@@ -64,7 +65,7 @@ def plan_exchange(send_counts: np.ndarray, recv_counts: np.ndarray, plan_len: in
 
     ``send_counts[p, e]``: rows this rank routes to local expert ``e`` of rank ``p``;
     ``recv_counts[s, e]``: rows rank ``s`` routes to this rank's local expert ``e``.
-    Segments are padded to 128 rows on the wire, exactly as the router laid them out.
+    Segments are padded to 256 rows on the wire, exactly as the router laid them out.
     """
     send_counts = np.asarray(send_counts, dtype=np.int64)
     recv_counts = np.asarray(recv_counts, dtype=np.int64)
@@ -82,7 +83,7 @@ def plan_exchange(send_counts: np.ndarray, recv_counts: np.ndarray, plan_len: in
             off += recv_pad[s, e]
     per_expert = recv_counts.sum(axis=0)              # real rows per local expert
     padded = _pad(per_expert)
-    padded_rows = max(int(padded.sum()), TILE)
+    padded_rows = max(int(padded.sum()), SEGMENT_ALIGN)
     gather_map = np.full(padded_rows, -1, dtype=np.int32)
     scatter_map = np.full(max(recv_rows, 1), -1, dtype=np.int32)
     seg_off = np.zeros(e_loc + 1, dtype=np.int64)

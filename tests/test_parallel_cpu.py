@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from mindpipe_b200.column_parallel import assemble_gathered, shard_packed_linear, shard_rows
-from mindpipe_b200.expert_parallel import TILE, expert_partition, plan_exchange
+from mindpipe_b200.expert_parallel import SEGMENT_ALIGN, TILE, expert_partition, plan_exchange
 
 
 def test_expert_partition_is_disjoint_and_complete():
@@ -30,12 +30,12 @@ def test_plan_exchange_layout():
     recv[2] = 0                                             # a peer that sends nothing
     recv[:, 1][recv[:, 1] > 250] = 0
     pl = plan_exchange(send, recv)
-    pad = lambda a: (a + TILE - 1) // TILE * TILE
+    pad = lambda a: (a + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
     assert pl.send_splits == list(pad(send).sum(axis=1))
     assert pl.recv_splits == list(pad(recv).sum(axis=1))
     assert pl.recv_rows == sum(pl.recv_splits)
     per_expert = recv.sum(axis=0)
-    assert pl.padded_rows == max(int(pad(per_expert).sum()), TILE)
+    assert pl.padded_rows == max(int(pad(per_expert).sum()), SEGMENT_ALIGN)
     # the gather map is a bijection between real received rows and real sorted rows
     real_sorted = np.nonzero(pl.gather_map >= 0)[0]
     assert real_sorted.size == per_expert.sum()
@@ -57,7 +57,7 @@ def test_plan_exchange_layout():
 
 def test_plan_exchange_no_rows():
     pl = plan_exchange(np.zeros((2, 1), int), np.zeros((2, 1), int))
-    assert pl.recv_rows == 0 and pl.padded_rows == TILE and pl.plan_ints[3 * 1 + 1] == 0
+    assert pl.recv_rows == 0 and pl.padded_rows == SEGMENT_ALIGN and pl.plan_ints[3 * 1 + 1] == 0
     assert (pl.gather_map == -1).all()
 
 
@@ -90,9 +90,9 @@ def _ep_worker(rank, world, port, ret):
         e_loc = e // world
         ids = torch.stack([torch.randperm(e)[:k] for _ in range(t)]).to(torch.int32)
         hidden = torch.randn(t, h)
-        # CPU stand-in for the router kernel: sort entries by expert into 128-padded segments
+        # CPU stand-in for the router kernel: sort entries by expert into 256-padded segments
         counts = torch.bincount(ids.flatten().long(), minlength=e)
-        pad = (counts + TILE - 1) // TILE * TILE
+        pad = (counts + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
         seg = torch.cat([torch.zeros(1, dtype=torch.long), pad.cumsum(0)])
         dest = torch.empty(t * k, dtype=torch.long)
         cursor = seg[:-1].clone()
