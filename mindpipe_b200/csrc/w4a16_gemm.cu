@@ -5,6 +5,7 @@
 //   warp 0      TMA producer for the activation tile x[128 MT x 64] (128-byte swizzle)
 //   warp 1      MMA issuer: tcgen05.mma kind::f16, M=128, N=256, K=16, fp32 in TMEM
 //   next 4 MT   epilogue warps: tcgen05.ld -> (+bias) -> fp16 -> global
+//               (for M > 256 two CTAs of a cluster share each MMA, see Cfg)
 //   last 8      dequant producers: stream the packed int4 words of the weight tile
 //               [256 rows x 64 columns] from global memory with 128-bit loads, expand
 //               them with dequant8 (exactly f16((u - z) * s), the reference's Wdq) and
@@ -26,22 +27,27 @@ constexpr int kBN = 256;
 constexpr int kBK = 64;            // fp16 elements of K per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kSubBytes = 128 * kBK * 2;   // one 128-row activation sub-tile: 16 KB
-constexpr int kBBytes = kBN * kBK * 2;     // 32 KB
 constexpr int kTmemCols = 2 * kBN;         // all 512 columns
 constexpr int kDequantWarps = 8;
 // MT = 128-row activation sub-tiles per block tile.  MT = 1: 128 x 256 tile, two accumulator
 // buffers (the epilogue of a tile overlaps the next main loop).  MT = 2: 256 x 256 tile whose two
 // accumulators share one dequantised weight tile -- half the dequant work per flop, one buffer.
-template <int MT>
+// PAIR (with MT = 2): two CTAs of a cluster share every MMA (cta_group::2, M = 256 per instruction:
+// 128 rows from each CTA), so a pair computes a 512 x 256 tile and each CTA dequantises and stages
+// only 128 of the 256 weight rows -- half the dequant work and a third less shared-memory traffic
+// per flop than the single-CTA 256 x 256 tile.
+template <int MT, bool PAIR = false>
 struct Cfg {
-  static constexpr int kBM = 128 * MT;
-  static constexpr int kStages = MT == 1 ? 4 : 3;
+  static constexpr int kBM = 128 * MT;                       // activation rows per CTA
+  static constexpr int kStages = PAIR ? 4 : (MT == 1 ? 4 : 3);
   static constexpr int kABytes = MT * kSubBytes;
+  static constexpr int kBRows = PAIR ? kBN / 2 : kBN;        // weight rows this CTA dequantises
+  static constexpr int kBStage = kBRows * kBK * 2;
   static constexpr int kBufs = MT == 1 ? 2 : 1;
   static constexpr int kEpiWarps = 4 * MT;
   static constexpr int kFirstDequantWarp = 2 + kEpiWarps;
   static constexpr int kThreads = 32 * (2 + kEpiWarps + kDequantWarps);
-  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + 256;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBStage) + 256;
 };
 }  // namespace w4
 
@@ -55,11 +61,12 @@ struct W4GemmParams {
   int* error_word;
 };
 
-template <int MT>
-__global__ void __launch_bounds__(w4::Cfg<MT>::kThreads, 1)
+template <int MT, bool PAIR>
+__global__ void __launch_bounds__(w4::Cfg<MT, PAIR>::kThreads, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams p) {
   using namespace w4;
-  using C = Cfg<MT>;
+  using C = Cfg<MT, PAIR>;
+  constexpr int kBStage = C::kBStage;
   constexpr int kStages = C::kStages;
   constexpr int kABytes = C::kABytes;
   constexpr int kBM = C::kBM;
@@ -67,34 +74,55 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = smem;
   unsigned char* sB = smem + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + kStages * kBBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + kStages * kBStage);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
   const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // PAIR: rank 0 of the cluster leads: it issues the MMAs and owns the "stage full" and "accumulator
+  // free" barriers, on which the peer's TMA bytes, dequant warps and epilogue warps arrive remotely;
+  // both CTAs own "stage empty" and "accumulator full" barriers that the leader's commits arrive on.
+  // Every wait is on a barrier of the waiting CTA.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  constexpr int kCtas = PAIR ? 2 : 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full0 + 8 * s, 1 + kDequantWarps);   // TMA producer's expect_tx arrival + the dequant warps
+      // leader: the TMA producer's expect_tx arrival + its dequant warps (+ one relayed arrival for the
+      // peer's dequant warps); peer: its dequant warps only (its relay thread waits on this one)
+      mbar_init(full0 + 8 * s, leader ? 1 + kDequantWarps + (PAIR ? 1 : 0) : kDequantWarps);
       mbar_init(empty0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, C::kEpiWarps);
+      mbar_init(tempty0 + 8 * b, kCtas * C::kEpiWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) {            // the peer's barriers exist before anything signals them
+    cluster_arrive();
+    cluster_wait();
+  }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total = p.m_tiles * p.n_tiles;
+  const int total = p.m_tiles * p.n_tiles;                   // m_tiles counts tiles of kCtas * kBM rows
+  const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+  const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
+  const uint32_t full_leader0 = PAIR ? map_to_cta(full0, 0) : full0;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -102,47 +130,86 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * kBM;
+      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+        const int m0 = (tile % p.m_tiles) * (kCtas * kBM) + static_cast<int>(rank) * kBM;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
-          const uint32_t full = full0 + 8 * stage;
-          mbar_arrive_expect_tx(full, kABytes);
+          if (PAIR) {
+            const uint32_t full = full_leader0 + 8 * stage;      // both CTAs' bytes are counted by the leader
+            if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * kABytes);
 #pragma unroll
-          for (int sub = 0; sub < MT; ++sub)
-            tma_load_2d(smem_u32(sA + stage * kABytes + sub * kSubBytes), &tmap_x, full, kb * kBK, m0 + sub * 128);
+            for (int sub = 0; sub < MT; ++sub)
+              tma_load_2d_pair(smem_u32(sA + stage * kABytes + sub * kSubBytes), &tmap_x, full, kb * kBK,
+                               m0 + sub * 128);
+          } else {
+            const uint32_t full = full0 + 8 * stage;
+            mbar_arrive_expect_tx(full, kABytes);
+#pragma unroll
+            for (int sub = 0; sub < MT; ++sub)
+              tma_load_2d(smem_u32(sA + stage * kABytes + sub * kSubBytes), &tmap_x, full, kb * kBK, m0 + sub * 128);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1 && !leader) {
+    // peer CTA: relay "my half of the weight tile is in place" to the leader with ONE cluster-scope
+    // arrival per stage (the eight dequant warps arrive on the local barrier, which is cheap)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          mbar_arrive_cluster(full_leader0 + 8 * stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, 128, kBN);
+      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, kCtas * 128, kBN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
         if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;        // MT == 2: the accumulators sit at columns 0 and 256
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * kBBytes));
+          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * kBStage));
 #pragma unroll
           for (int sub = 0; sub < MT; ++sub) {
             const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * kABytes + sub * kSubBytes));
 #pragma unroll
-            for (int kk = 0; kk < kBK / kUmmaK; ++kk)   // +32 bytes of K per step
-              umma_f16(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {  // +32 bytes of K per step
+              if (PAIR) {
+                umma_f16_pair(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+              } else {
+                umma_f16(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+              }
+            }
           }
-          umma_commit(empty0 + 8 * stage);
+          if (PAIR) {                      // release the stage in both CTAs
+            umma_commit_pair(empty0 + 8 * stage);
+            umma_commit_pair(map_to_cta(empty0 + 8 * stage, 1));
+          } else {
+            umma_commit(empty0 + 8 * stage);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull0 + 8 * buf);
+        if (PAIR) {                        // publish the accumulators to both CTAs' epilogues
+          umma_commit_pair(tfull0 + 8 * buf);
+          umma_commit_pair(map_to_cta(tfull0 + 8 * buf, 1));
+        } else {
+          umma_commit(tfull0 + 8 * buf);
+        }
         if (++buf == C::kBufs) { buf = 0; buf_phase ^= 1; }
       }
     }
@@ -151,11 +218,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
     const int sub = (warp - 2) >> 2;              // which 128-row accumulator (MT == 2)
     int buf = 0;
     uint32_t buf_phase = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty0, 0) : tempty0;
+    for (int tile = first_tile; tile < total; tile += tile_step) {
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
-      const int row = m_tile * kBM + sub * 128 + quarter * 32 + lane;
+      const int row = m_tile * (kCtas * kBM) + static_cast<int>(rank) * kBM + sub * 128 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const int n0 = n_tile * kBN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (buf + sub) * kBN;
@@ -194,51 +262,69 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+      if (lane == 0) {
+        if (PAIR) {
+          mbar_arrive_cluster(tempty_leader0 + 8 * buf);
+        } else {
+          mbar_arrive(tempty0 + 8 * buf);
+        }
+      }
       if (++buf == C::kBufs) { buf = 0; buf_phase ^= 1; }
     }
   } else {
-    // ---- dequant producers: thread dt owns row dt of the weight tile ----
+    // ---- dequant producers: 256 threads expand this CTA's rows of the weight tile; a thread owns one
+    // row (all 64 columns of the k-block) or, with 128 rows per CTA (PAIR), one 32-column half of a row ----
+    constexpr int kTPR = 256 / C::kBRows;                              // threads per row: 1 or 2
+    constexpr int kVec = 2 / kTPR;                                     // 128-bit loads per thread and k-block
     const int dt = threadIdx.x - C::kFirstDequantWarp * 32;            // 0..255
+    const int r = dt / kTPR;                                           // row of this CTA's weight tile
+    const int part = dt % kTPR;                                        // which half of the row's k-block
     const int words_per_row = p.K >> 3;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    const int row_off = (dt >> 3) * 1024 + (dt & 7) * 128;   // row dt of a K-major tile with 128-byte rows
-    const int sw = dt & 7;
-    for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-      const int n = (tile / p.m_tiles) * kBN + dt;
+    const int row_off = (r >> 3) * 1024 + (r & 7) * 128;     // row r of a K-major tile with 128-byte rows
+    const int sw = r & 7;
+    for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+      const int n = (tile / p.m_tiles) * kBN + static_cast<int>(rank) * C::kBRows + r;
       const bool n_ok = n < p.N;
-      const uint32_t* row = p.packed + (size_t)(n_ok ? n : 0) * words_per_row;
+      const uint32_t* row = p.packed + (size_t)(n_ok ? n : 0) * words_per_row + part * 4;
       const uint32_t* szp = p.sz + (n_ok ? n : 0);
       // software pipeline: the words of the next kPrefetch k-blocks are in flight while one is
       // expanded (a k-block lasts about 1000 tensor cycles, a global load under load about as long)
       constexpr int kPrefetch = 3;
-      uint4 q0[kPrefetch], q1[kPrefetch];
+      uint4 q[kPrefetch][kVec];
       uint32_t szq[kPrefetch];
-      auto fetch = [&](int kb, uint4& a, uint4& b, uint32_t& z) {
+      auto fetch = [&](int kb, uint4 (&dst)[kVec], uint32_t& z) {
         const bool live = n_ok && kb < p.k_blocks;
         const uint32_t* src = row + kb * (kBK / 8);
-        a = live ? ldg_stream_v4(src) : make_uint4(0, 0, 0, 0);
-        b = live ? ldg_stream_v4(src + 4) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int v = 0; v < kVec; ++v) dst[v] = live ? ldg_stream_v4(src + 4 * v) : make_uint4(0, 0, 0, 0);
         z = live ? __ldg(szp + (size_t)((kb * kBK) / p.group) * p.N) : 0u;
       };
 #pragma unroll
-      for (int d = 0; d < kPrefetch; ++d) fetch(d, q0[d], q1[d], szq[d]);
+      for (int d = 0; d < kPrefetch; ++d) fetch(d, q[d], szq[d]);
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        const uint4 c0 = q0[0], c1 = q1[0];
+        uint4 cur[kVec];
+#pragma unroll
+        for (int v = 0; v < kVec; ++v) cur[v] = q[0][v];
         const uint32_t szc = szq[0];
 #pragma unroll
-        for (int d = 0; d + 1 < kPrefetch; ++d) { q0[d] = q0[d + 1]; q1[d] = q1[d + 1]; szq[d] = szq[d + 1]; }
-        fetch(kb + kPrefetch, q0[kPrefetch - 1], q1[kPrefetch - 1], szq[kPrefetch - 1]);
+        for (int d = 0; d + 1 < kPrefetch; ++d) {
+#pragma unroll
+          for (int v = 0; v < kVec; ++v) q[d][v] = q[d + 1][v];
+          szq[d] = szq[d + 1];
+        }
+        fetch(kb + kPrefetch, q[kPrefetch - 1], szq[kPrefetch - 1]);
         const __half2 hz = *reinterpret_cast<const __half2*>(&szc);
         const ScaleZero sp = make_scale_zero(__low2half(hz), __high2half(hz));
         if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag))) { ok = false; break; }
-        unsigned char* row_base = sB + stage * kBBytes + row_off;
+        unsigned char* row_base = sB + stage * kBStage + row_off;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {                             // 16-byte chunk j = columns 8j..8j+7
-          const uint4& src = j < 4 ? c0 : c1;
-          const uint32_t word = (j & 3) == 0 ? src.x : (j & 3) == 1 ? src.y : (j & 3) == 2 ? src.z : src.w;
+        for (int jj = 0; jj < 4 * kVec; ++jj) {                   // 16-byte chunk j = columns 8j..8j+7
+          const int j = part * 4 + jj;
+          const uint4& src = cur[jj >> 2];
+          const uint32_t word = (jj & 3) == 0 ? src.x : (jj & 3) == 1 ? src.y : (jj & 3) == 2 ? src.z : src.w;
           __half2 v[4];
           dequant8(word, sp, v);
           const uint32_t a = h2_as_u32(v[0]), b = h2_as_u32(v[1]), c = h2_as_u32(v[2]), d = h2_as_u32(v[3]);
@@ -251,13 +337,20 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
         }
         fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * stage);
+        if (lane == 0) mbar_arrive(full0 + 8 * stage);      // this CTA's barrier (the peer's is relayed)
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
   }
 
   __syncthreads();
+  if (PAIR) {
+    // a CTA that gave up tells its peer (whose waits poll the flag) before both meet at the cluster
+    // barrier; the peer cannot have left yet, so its shared memory is still there
+    if (*abort_flag && threadIdx.x == 0) st_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u), 1u);
+    cluster_arrive();       // the leader's MMAs read the peer's shared memory: nobody leaves early
+    cluster_wait();
+  }
   if (*abort_flag) {
     if (threadIdx.x == 0 && p.error_word) atomicExch(p.error_word, 2);
     const uint64_t t0 = globaltimer_ns();
@@ -266,15 +359,20 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   }
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, w4::kTmemCols);
+    if (PAIR) {
+      tmem_dealloc_pair(tmem_base, w4::kTmemCols);
+    } else {
+      tmem_dealloc(tmem_base, w4::kTmemCols);
+    }
   }
 }
 
-template <int MT>
+template <int MT, bool PAIR = false>
 static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st) {
-  using C = w4::Cfg<MT>;
-  p.m_tiles = (p.M + C::kBM - 1) / C::kBM;
-  auto kern = w4a16_gemm_kernel<MT>;
+  using C = w4::Cfg<MT, PAIR>;
+  constexpr int kTileRows = (PAIR ? 2 : 1) * C::kBM;
+  p.m_tiles = (p.M + kTileRows - 1) / kTileRows;
+  auto kern = w4a16_gemm_kernel<MT, PAIR>;
   static thread_local int configured_device = -1;
   int device = 0;
   MP_CUDA_TRY(cudaGetDevice(&device));
@@ -283,6 +381,23 @@ static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st
     configured_device = device;
   }
   const long long total = (long long)p.m_tiles * p.n_tiles;
+  if (PAIR) {
+    const int pairs = (int)(total < kSmCount / 2 ? total : kSmCount / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tx, p));
+    return MP_OK;
+  }
   const int grid = (int)(total < kSmCount ? total : kSmCount);
   kern<<<grid, C::kThreads, C::kSmem, st>>>(tx, p);
   MP_LAUNCH_CHECK();
@@ -313,6 +428,7 @@ extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32
   p.k_blocks = K / w4::kBK;
   p.error_word = error_word;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M > 256) return launch_w4_gemm<2, true>(tx, p, st);     // 512 x 256 tiles on CTA pairs
   if (M > 128) return launch_w4_gemm<2>(tx, p, st);
   return launch_w4_gemm<1>(tx, p, st);
 }
