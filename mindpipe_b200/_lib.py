@@ -19,6 +19,7 @@ _lib = None
 
 # name -> (restype, argtypes); mirrors include/mindpipe_b200.h one to one.
 _P, _I, _Z = c_void_p, c_int, c_size_t
+_U = ctypes.c_uint
 SIGNATURES = {
     "mp_abi_version": (_I, []),
     "mp_status_string": (c_char_p, [_I]),
@@ -30,6 +31,8 @@ SIGNATURES = {
     "mp_w4a16_decode_workspace_bytes_ex": (_Z, [_I, _I, _I, _I]),
     "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
+    "mp_w4a16_rowparallel_push": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _U, _P]),
+    "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _I, _U, _I, _I, _I, _P, _P, _P, _P]),
     "mp_w4a16_linear_decode_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_w4a16_linear_decode_static_max_bytes": (_Z, []),

@@ -56,6 +56,17 @@ __device__ __forceinline__ __half hmul_t(__half a, __half b) { return f2h(__fmul
 //  * fp32 route (tiny scales, where 2^-e is not an fp16 number): x * (1/s) in fp32 is within 3 ulps
 //    of the correctly rounded quotient and rounds to the same fp16 value unless it lies within 8 fp32
 //    ulps of an fp16 rounding midpoint; only then is the IEEE division carried out.
+// Row-parallel decode: where a GPU's partial sums go.  partial[q] is rank q's buffer
+// [world][m_cap][N] fp32 (slot r written by rank r), flags[q] its arrival words [world].
+constexpr int kMaxPeerRanks = 16;
+struct DecodePush {
+  float* partial[kMaxPeerRanks];
+  unsigned int* flags[kMaxPeerRanks];
+  int* block_counter;        // local device int, zero between calls
+  int world, rank, m_cap;
+  unsigned int epoch;
+};
+
 constexpr float kRoundMagic = 12582912.0f;   // 1.5 * 2^23: (v + magic) holds rint(v) in its low mantissa bits
 
 struct RowQuant {

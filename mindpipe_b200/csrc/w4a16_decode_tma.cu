@@ -65,6 +65,7 @@ struct DecodeTmaParams {
   int stages_per_block;    // per cluster rank
   int groups_per_stage;    // rows of the (scale, zero) box
   int* error_word;
+  DecodePush push;         // row-parallel mode (PUSH kernels only)
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -122,7 +123,11 @@ __device__ __forceinline__ uint4 scale_odd_pairs(uint4 v) {
   return v;
 }
 
-template <bool HALF, bool FOLD>
+// PUSH (row-parallel linear, K sharded over GPUs): instead of rounding to fp16 the owner blocks store
+// their fp32 sums into slot `rank` of EVERY peer's partial-sum buffer (plain peer stores over NVLink,
+// issued as each cluster finishes, so the transfer overlaps the rest of the grid's compute); the last
+// block of the grid then publishes this rank's arrival on every peer with a release store.
+template <bool HALF, bool FOLD, bool PUSH>
 __global__ void __launch_bounds__(dt::kThreads, 2)
 w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_sz, const DecodeTmaParams p) {
@@ -385,8 +390,28 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       float s = 0.0f;
       for (int src = 0; src < ck; ++src) s += slots[(src * MROWS + m) * cols + c];   // rank order: deterministic
       if (n < p.N) {
-        if (p.bias) s += h2f(p.bias[n]);
-        p.y[(size_t)m * p.N + n] = f2h(s);
+        if constexpr (PUSH) {
+          const size_t at = ((size_t)p.push.rank * p.push.m_cap + m) * p.N + n;
+          for (int q = 0; q < p.push.world; ++q) p.push.partial[q][at] = s;
+        } else {
+          if (p.bias) s += h2f(p.bias[n]);
+          p.y[(size_t)m * p.N + n] = f2h(s);
+        }
+      }
+    }
+    if constexpr (PUSH) {
+      __threadfence_system();                           // this thread's peer stores before the count below
+      __syncthreads();
+      if (tid == 0) {
+        const int blocks = static_cast<int>(gridDim.x * gridDim.y);
+        if (atomicAdd(p.push.block_counter, 1) == blocks - 1) {       // every block of this GPU has pushed
+          atomicExch(p.push.block_counter, 0);                        // re-armed for the next call
+          __threadfence_system();
+          for (int q = 0; q < p.push.world; ++q) {
+            unsigned int* flag = p.push.flags[q] + p.push.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.push.epoch) : "memory");
+          }
+        }
       }
     }
   } else {
@@ -413,11 +438,11 @@ int read_and_clear_decode_error(int* value) {
   return MP_OK;
 }
 
-template <bool HALF, bool FOLD>
+template <bool HALF, bool FOLD, bool PUSH>
 static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tsz, const DecodeTmaParams& p,
                       int row_blocks, int ck, cudaStream_t st) {
   using C = dt::Cfg<HALF>;
-  auto kern = w4a16_decode_tma_kernel<HALF, FOLD>;
+  auto kern = w4a16_decode_tma_kernel<HALF, FOLD, PUSH>;
   static thread_local int configured_device = -1;
   int device = 0;
   MP_CUDA_TRY(cudaGetDevice(&device));
@@ -451,7 +476,7 @@ static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtens
 // register-streaming kernel): M > 16, K % 64 != 0, N % 4 != 0, group sizes that neither divide nor
 // are a multiple of 256.
 int launch_decode_tma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
-                      int group, cudaStream_t st) {
+                      int group, cudaStream_t st, const DecodePush* push) {
   if (M > 16 || K % 64 != 0 || N % 4 != 0) return MP_ERR_UNSUPPORTED;
   if (!((group <= dt::kStageK && dt::kStageK % group == 0) || group % dt::kStageK == 0)) return MP_ERR_UNSUPPORTED;
   if (!aligned(x, 16) || !aligned(packed, 16) || !aligned(sz, 16)) return MP_ERR_UNSUPPORTED;
@@ -496,9 +521,15 @@ int launch_decode_tma(const void* x, const void* packed, const void* sz, const v
   // M <= 8 (measured 10-15 % faster on the 70B shapes, neutral on the 7B ones); with 9..16 tokens the
   // extra MMAs of the ones row cost what the shorter dequantisation saves, so that case keeps the
   // exact per-weight form.
-  if (half && group % 128 == 0) return launch_tma<true, true>(tw, tx, tsz, p, row_blocks, ck, st);
-  return half ? launch_tma<true, false>(tw, tx, tsz, p, row_blocks, ck, st)
-              : launch_tma<false, false>(tw, tx, tsz, p, row_blocks, ck, st);
+  if (push) {
+    p.push = *push;
+    if (half && group % 128 == 0) return launch_tma<true, true, true>(tw, tx, tsz, p, row_blocks, ck, st);
+    return half ? launch_tma<true, false, true>(tw, tx, tsz, p, row_blocks, ck, st)
+                : launch_tma<false, false, true>(tw, tx, tsz, p, row_blocks, ck, st);
+  }
+  if (half && group % 128 == 0) return launch_tma<true, true, false>(tw, tx, tsz, p, row_blocks, ck, st);
+  return half ? launch_tma<true, false, false>(tw, tx, tsz, p, row_blocks, ck, st)
+              : launch_tma<false, false, false>(tw, tx, tsz, p, row_blocks, ck, st);
 }
 
 }  // namespace mp

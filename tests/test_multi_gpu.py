@@ -1,5 +1,6 @@
-"""Multi-GPU parity (needs >= 2 GPUs; skipped otherwise): expert-parallel MoE and
-column-parallel W4A16 against the single-GPU path, over NCCL, one process per GPU."""
+"""Multi-GPU parity (needs >= 2 GPUs; skipped otherwise): expert-parallel MoE, column-parallel and
+row-parallel W4A16 against the single-GPU path, one process per GPU."""
+import datetime
 import os
 import socket
 
@@ -20,7 +21,9 @@ def _free_port():
 def _worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short collective timeout: if one rank fails, the others error out instead of waiting for it
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from mindpipe_b200 import ops, synth
         from mindpipe_b200.column_parallel import ColumnParallelW4A16Linear
@@ -60,17 +63,36 @@ def _worker(rank, world, port, ret):
         x = synth.normal_activation(8, k, seed=2).to(dev)
         cp = ColumnParallelW4A16Linear.from_full(packed, scale, zero, None, k, device=dev)
         ok_col = torch.equal(cp(x), single(x))
-        ret[rank] = (bool(ok_moe), bool(ok_col))
+        # ---- row-parallel W4A16 (K sharded, partial sums pushed to the peers by the decode kernel) ----
+        from mindpipe_b200.row_parallel import RowParallelW4A16Linear, shard_columns
+        bias = (synth.normal_activation(1, n, seed=2, index=5)[0] * 0.1).to(torch.float16).to(dev)
+        single_b = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=bias, in_features=k, out_features=n,
+                                        zero_point=zero)
+        rp = RowParallelW4A16Linear.from_full(packed, scale, zero, bias, 128, device=dev)
+        c0, c1 = shard_columns(k, world, rank, 128)
+        ok_row = True
+        for i, m in enumerate((1, 8, 16, 5, 16)):      # five calls: both partial buffers are reused
+            xm = synth.normal_activation(m, k, seed=3, index=i).to(dev)
+            y = rp(xm[:, c0:c1].contiguous())
+            ops.check_device_errors()
+            want = single_b(xm).float()
+            ok_row = ok_row and ((y.float() - want).norm() / want.norm()).item() <= 1e-2
+            everyone = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(everyone, y)
+            ok_row = ok_row and all(torch.equal(e, everyone[0]) for e in everyone)    # rank-order sum: same bits
+            y2 = rp.forward_nccl(xm[:, c0:c1].contiguous())
+            ok_row = ok_row and ((y2.float() - want).norm() / want.norm()).item() <= 1e-2
+        ret[rank] = (bool(ok_moe), bool(ok_col), bool(ok_row))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_expert_parallel_and_column_parallel_match_single_gpu():
+def test_expert_parallel_column_parallel_and_row_parallel_match_single_gpu():
     world = min(torch.cuda.device_count(), 4)
     while 8 % world:
         world -= 1
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert all(v == (True, True) for v in dict(ret).values()), dict(ret)
+    assert all(v == (True, True, True) for v in dict(ret).values()), dict(ret)

@@ -11,6 +11,7 @@ import torch.multiprocessing as mp
 
 from mindpipe_b200.column_parallel import assemble_gathered, shard_packed_linear, shard_rows
 from mindpipe_b200.expert_parallel import SEGMENT_ALIGN, TILE, expert_partition, plan_exchange
+from mindpipe_b200.row_parallel import pack_nibbles, shard_columns, shard_packed_linear_columns, unpack_nibbles
 
 
 def test_expert_partition_is_disjoint_and_complete():
@@ -140,6 +141,35 @@ def test_expert_parallel_exchange_world2_gloo():
     ret = mgr.dict()
     mp.spawn(_ep_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_parallel_column_shards(world):
+    """K-sharding of the packed format: every shard dequantises to its column slice of the full Wdq
+    (zero points are re-packed because a shard's first group need not start a packed word: 28 groups
+    over 8 ranks gives 3.5 words per rank), and the shards' partial products add up to the full one."""
+    from oracle import pseudo_quant as O
+    from mindpipe_b200 import synth
+    n, k, g = 24, 3584 * 2, 128                      # 56 groups: 7 per rank at world 8
+    w = synth.normal_weight(n, k, seed=11, index=0).numpy()
+    wdq, scales, zeros, codes = O.w4_group_asym_quantize(w, g)
+    packed = torch.from_numpy(O.pack_int4_unsigned(codes))
+    zp = torch.from_numpy(O.pack_int4_unsigned(zeros.astype(np.uint8)))
+    assert np.array_equal(pack_nibbles(unpack_nibbles(zp, k // g)).numpy(), zp.numpy())
+    x = synth.normal_activation(3, k, seed=11, index=1).numpy().astype(np.float32)
+    total = np.zeros((3, n), np.float32)
+    for rank in range(world):
+        lo, hi = shard_columns(k, world, rank, g)
+        p, s_, z = shard_packed_linear_columns(packed, torch.from_numpy(scales), zp, world, rank, g)
+        part = O.w4_dequant(p.numpy(), s_.numpy(), z.numpy(), n, hi - lo, g)
+        assert np.array_equal(part.view(np.uint16), wdq[:, lo:hi].view(np.uint16))
+        total += x[:, lo:hi] @ part.astype(np.float32).T
+    full = x @ wdq.astype(np.float32).T
+    assert np.abs(total - full).max() <= 1e-3 * np.abs(full).max()
+    with pytest.raises(ValueError):
+        shard_columns(k, 3, 0, g)
+    with pytest.raises(ValueError):
+        shard_columns(1024, 8, 0, 256)                # 128 columns per rank is not a whole group of 256
 
 
 def test_expert_parallel_constructor_rejects_wrong_partition():
