@@ -189,6 +189,50 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def measure_row_parallel(world, rank, dev, dist, iters=50):
+    """Llama-2-70B down_proj (8192 x 28672, W4A16 g128) at decode M=16 with the input features sharded
+    over the ranks: the decode kernel pushes its partial sums to every peer, a finish kernel adds them."""
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    from mindpipe_b200.row_parallel import RowParallelW4A16Linear
+    n, k = 8192, 28672
+    if k % (world * 256):
+        return {"skipped": f"{k} input features do not split into 256-column stages over {world} ranks"}
+    k_loc = k // world
+    w = synth.normal_weight(n, k_loc, seed=7, index=rank).to(dev)             # this rank's column slice
+    packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+    del w
+    local = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k_loc, out_features=n,
+                                 zero_point=zero)
+    layer = RowParallelW4A16Linear(local, None, max_rows=M_DECODE)
+    x = synth.normal_activation(M_DECODE, k_loc, seed=7, index=100 + rank).to(dev)
+
+    def timed(fn):
+        for _ in range(5):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3
+
+    us_fused = timed(lambda: layer(x))
+    ops.check_device_errors()
+    us_nccl = timed(lambda: layer.forward_nccl(x))
+    us_local = timed(lambda: local(x))
+    return {"config": f"llama2-70b down_proj 8192x28672 W4A16 g128, M={M_DECODE}, K sharded over {world} ranks",
+            "us_fused_push_allreduce": us_fused, "us_local_gemm_plus_nccl_allreduce": us_nccl,
+            "us_local_gemm_only": us_local, "n_gpus": world,
+            "algorithmic_gbs_whole_job": w4a16_bytes(n, k, M_DECODE) / (us_fused * 1e-6) / 1e9}
+
+
 def measure_moe(world, rank, dev, dist, iters=5):
     """Mixtral-8x7B-shaped W8A8 MoE layer (8 experts, hidden 4096, ffn 14336, top-2, 8192 tokens):
     experts sharded over the ranks, tokens data-sharded, all-to-all dispatch/combine.  tokens/s of the
@@ -402,6 +446,12 @@ def run_ours(args, rank, world, local_rank):
             moe_extra = measure_moe(world, rank, dev, dist)
         except Exception as err:          # the headline number must not depend on the extra
             moe_extra = {"error": f"{type(err).__name__}: {err}"[:200]}
+    tp_extra = None
+    if args.moe and world > 1:            # the sharded 70B down_proj: decode kernel fused with its all-reduce
+        try:
+            tp_extra = measure_row_parallel(world, rank, dev, dist)
+        except Exception as err:
+            tp_extra = {"error": f"{type(err).__name__}: {err}"[:200]}
 
     if rank == 0:
         bytes_step = step_bytes(M_DECODE)
@@ -434,6 +484,8 @@ def run_ours(args, rank, world, local_rank):
             "tflops": world * step_flops(M_DECODE) * args.steps / (ms * 1e-3) / 1e12,
             "moe_w8a8": moe_extra,
         }
+        if tp_extra is not None:
+            line["tp_row_parallel"] = tp_extra
         if world == 1 and not args.no_cpu_baseline:
             cores = torch.get_num_threads()
             sets, xs = build_cpu_sets(2, M_DECODE)
@@ -536,6 +588,22 @@ def run_suite(args, local_rank):
             fl = 2 * 2048 * n * k
             emit(suite="w4a16_prefill", N=n, K=k, M=2048, us=t * 1e6, tflops=fl / t / 1e12,
                  frac_of_measured_bf16_burst=fl / t / 1e12 / peaks["bf16_tflops"])
+    if "midm" in want or "all" in want:
+        # batch sizes between decode and prefill, through the dispatching entry (ops.w4a16_linear)
+        for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
+            copies = max(2, int(300e6 // (n * k // 2)) + 1)
+            mods = []
+            for c in range(copies):
+                w = synth.normal_weight(n, k, seed=c, index=0).to(dev)
+                packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+                mods.append((packed, ops.w4a16_prepare(scale, zero, k)))
+                del w
+            for m in (32, 64, 128, 256, 512, 1024):
+                x = synth.normal_activation(m, k, seed=0).to(dev)
+                t = timed_graph([(lambda pk=pk, sz=sz: ops.w4a16_linear(x, pk, sz)) for pk, sz in mods], rounds=2)
+                emit(suite="w4a16_mid_m", N=n, K=k, M=m, us=t * 1e6, gbs=w4a16_bytes(n, k, m) / t / 1e9,
+                     tflops=2 * m * n * k / t / 1e12)
+            del mods
     if "w8a8" in want or "all" in want:
         for (n, k) in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
             m = 4096

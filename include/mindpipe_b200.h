@@ -148,6 +148,19 @@ int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const
 int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                             const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                             int* error_word, mp_stream_t stream);
+/*
+ * Same, with scratch for split-K: with few output tiles (M <= 256 and a narrow
+ * N) the K range of every tile is cut into slices so that all SMs stream
+ * weights; the slices' fp32 partial tiles go to `workspace` and a second kernel
+ * adds them in slice order (deterministic).  mp_w4a16_prefill_workspace_bytes
+ * returns the size needed (0 = no split for this shape); a null workspace
+ * means no split.
+ */
+size_t mp_w4a16_prefill_workspace_bytes(int M, int N, int K);
+int mp_w4a16_linear_prefill_ex(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                               const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                               void* workspace, size_t workspace_bytes, int* error_word,
+                               mp_stream_t stream);
 
 /*
  * The workspace split-K decode linear for callers that cannot allocate device

@@ -58,6 +58,9 @@ struct W4GemmParams {
   __half* y;
   int M, N, K, group;
   int m_tiles, n_tiles, k_blocks;
+  int k_split;              // > 1: each tile's K range is cut into this many work items ...
+  int kb_per_split;         // ... of this many k-blocks, whose fp32 partial tiles go to `partial`
+  float* partial;           // [k_split][M][N] fp32 (split-K only)
   int* error_word;
 };
 
@@ -119,7 +122,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total = p.m_tiles * p.n_tiles;                   // m_tiles counts tiles of kCtas * kBM rows
+  // work item = (tile, K slice); m_tiles counts tiles of kCtas * kBM rows
+  const int total = p.m_tiles * p.n_tiles * p.k_split;
   const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
   const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
   const uint32_t full_leader0 = PAIR ? map_to_cta(full0, 0) : full0;
@@ -130,9 +134,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+      for (int work = first_tile; ok && work < total; work += tile_step) {
+        const int tile = work / p.k_split;
+        const int kb0 = (work - tile * p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         const int m0 = (tile % p.m_tiles) * (kCtas * kBM) + static_cast<int>(rank) * kBM;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
           if (PAIR) {
             const uint32_t full = full_leader0 + 8 * stage;      // both CTAs' bytes are counted by the leader
@@ -159,8 +165,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int work = first_tile; ok && work < total; work += tile_step) {
+        const int kb0 = (work % p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           mbar_arrive_cluster(full_leader0 + 8 * stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -175,11 +182,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+      for (int work = first_tile; ok && work < total; work += tile_step) {
+        const int kb0 = (work % p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;        // MT == 2: the accumulators sit at columns 0 and 256
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(sB + stage * kBStage));
@@ -189,9 +197,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
 #pragma unroll
             for (int kk = 0; kk < kBK / kUmmaK; ++kk) {  // +32 bytes of K per step
               if (PAIR) {
-                umma_f16_pair(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+                umma_f16_pair(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != kb0 || kk != 0));
               } else {
-                umma_f16(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+                umma_f16(d_tmem + sub * kBN, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != kb0 || kk != 0));
               }
             }
           }
@@ -219,7 +227,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
     int buf = 0;
     uint32_t buf_phase = 0;
     const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty0, 0) : tempty0;
-    for (int tile = first_tile; tile < total; tile += tile_step) {
+    for (int work = first_tile; work < total; work += tile_step) {
+      const int tile = work / p.k_split, split = work - tile * p.k_split;
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
@@ -232,6 +241,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
+        if (p.k_split > 1) {
+          // split-K: this K slice's fp32 partial tile; a second kernel adds the slices in order
+          if (row_ok) {
+            float* dst = p.partial + ((size_t)split * p.M + row) * p.N + n0 + c0;
+            if (n0 + c0 + 32 <= p.N && (p.N % 4) == 0) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+            }
+          }
+          continue;
+        }
         uint32_t packed_out[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -285,7 +310,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
     bool ok = true;
     const int row_off = (r >> 3) * 1024 + (r & 7) * 128;     // row r of a K-major tile with 128-byte rows
     const int sw = r & 7;
-    for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+    for (int work = first_tile; ok && work < total; work += tile_step) {
+      const int tile = work / p.k_split;
+      const int kb0 = (work - tile * p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
       const int n = (tile / p.m_tiles) * kBN + static_cast<int>(rank) * C::kBRows + r;
       const bool n_ok = n < p.N;
       const uint32_t* row = p.packed + (size_t)(n_ok ? n : 0) * words_per_row + part * 4;
@@ -296,15 +323,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
       uint4 q[kPrefetch][kVec];
       uint32_t szq[kPrefetch];
       auto fetch = [&](int kb, uint4 (&dst)[kVec], uint32_t& z) {
-        const bool live = n_ok && kb < p.k_blocks;
+        const bool live = n_ok && kb < kb1;
         const uint32_t* src = row + kb * (kBK / 8);
 #pragma unroll
         for (int v = 0; v < kVec; ++v) dst[v] = live ? ldg_stream_v4(src + 4 * v) : make_uint4(0, 0, 0, 0);
         z = live ? __ldg(szp + (size_t)((kb * kBK) / p.group) * p.N) : 0u;
       };
 #pragma unroll
-      for (int d = 0; d < kPrefetch; ++d) fetch(d, q[d], szq[d]);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int d = 0; d < kPrefetch; ++d) fetch(kb0 + d, q[d], szq[d]);
+      for (int kb = kb0; kb < kb1; ++kb) {
         uint4 cur[kVec];
 #pragma unroll
         for (int v = 0; v < kVec; ++v) cur[v] = q[0][v];
@@ -367,6 +394,50 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
   }
 }
 
+// y = f16(sum of the K slices' partial tiles, in slice order (+ bias))
+__global__ void __launch_bounds__(256)
+w4a16_splitk_reduce_kernel(const float* __restrict__ partial, int k_split, int M, int N,
+                           const __half* __restrict__ bias, __half* __restrict__ y) {
+  const int quads = N >> 2;
+  const size_t slice = (size_t)M * N;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += gridDim.x * blockDim.x) {
+    const int m = i / quads, n = (i - m * quads) << 2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < k_split; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + s * slice + (size_t)m * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias) {
+      acc.x += h2f(bias[n]); acc.y += h2f(bias[n + 1]); acc.z += h2f(bias[n + 2]); acc.w += h2f(bias[n + 3]);
+    }
+    const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(y + (size_t)m * N + n) = make_uint2(h2_as_u32(lo), h2_as_u32(hi));
+  }
+}
+
+// With few output tiles (batch sizes just above the decode kernels' range, or a narrow N) most SMs
+// would idle while a handful stream all the weights: cut K so that about one work item per SM (per
+// CTA pair for M > 256) exists.  Returns 1 when the tiles alone fill the machine or N % 4 != 0.
+static int prefill_k_split(int M, int N, int K) {
+  if (N % 4 != 0) return 1;
+  const int n_tiles = (N + w4::kBN - 1) / w4::kBN;
+  int tiles, units;
+  if (M > 256) {
+    tiles = ((M + 511) / 512) * n_tiles;
+    units = kSmCount / 2;
+  } else {
+    tiles = (M > 128 ? (M + 255) / 256 : (M + 127) / 128) * n_tiles;
+    units = kSmCount;
+  }
+  const int k_blocks = K / w4::kBK;
+  int ks = units / tiles;
+  if (ks > k_blocks / 4) ks = k_blocks / 4;          // at least four k-blocks per slice
+  if (ks > 16) ks = 16;
+  if (ks < 2) return 1;
+  const int per = (k_blocks + ks - 1) / ks;
+  return (k_blocks + per - 1) / per;                  // no empty slice
+}
+
 template <int MT, bool PAIR = false>
 static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st) {
   using C = w4::Cfg<MT, PAIR>;
@@ -380,7 +451,7 @@ static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmem));
     configured_device = device;
   }
-  const long long total = (long long)p.m_tiles * p.n_tiles;
+  const long long total = (long long)p.m_tiles * p.n_tiles * p.k_split;
   if (PAIR) {
     const int pairs = (int)(total < kSmCount / 2 ? total : kSmCount / 2);
     cudaLaunchConfig_t cfg{};
@@ -408,9 +479,23 @@ static int launch_w4_gemm(const CUtensorMap& tx, W4GemmParams p, cudaStream_t st
 
 using namespace mp;
 
+extern "C" size_t mp_w4a16_prefill_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % w4::kBK != 0) return 0;
+  const int ks = prefill_k_split(M, N, K);
+  return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+}
+
 extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                                        const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                                        int* error_word, mp_stream_t stream) {
+  return mp_w4a16_linear_prefill_ex(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, nullptr, 0,
+                                    error_word, stream);
+}
+
+extern "C" int mp_w4a16_linear_prefill_ex(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                          const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                          void* workspace, size_t workspace_bytes, int* error_word,
+                                          mp_stream_t stream) {
   if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
   if (K % w4::kBK != 0 || group % w4::kBK != 0 || K % group != 0) return MP_ERR_UNSUPPORTED;
   if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 16)) return MP_ERR_ALIGNMENT;
@@ -427,8 +512,23 @@ extern "C" int mp_w4a16_linear_prefill(const void* x_f16, const void* packed_i32
   p.n_tiles = (N + w4::kBN - 1) / w4::kBN;
   p.k_blocks = K / w4::kBK;
   p.error_word = error_word;
+  p.k_split = 1;
+  p.kb_per_split = p.k_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M > 256) return launch_w4_gemm<2, true>(tx, p, st);     // 512 x 256 tiles on CTA pairs
-  if (M > 128) return launch_w4_gemm<2>(tx, p, st);
-  return launch_w4_gemm<1>(tx, p, st);
+  const int ks = workspace ? prefill_k_split(M, N, K) : 1;    // without scratch: one K slice per tile
+  if (ks > 1) {
+    if (workspace_bytes < (size_t)ks * M * N * sizeof(float)) return MP_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return MP_ERR_ALIGNMENT;
+    p.k_split = ks;
+    p.kb_per_split = (p.k_blocks + ks - 1) / ks;
+    p.partial = static_cast<float*>(workspace);
+  }
+  rc = M > 256 ? launch_w4_gemm<2, true>(tx, p, st)          // 512 x 256 tiles on CTA pairs
+       : M > 128 ? launch_w4_gemm<2>(tx, p, st) : launch_w4_gemm<1>(tx, p, st);
+  if (rc != MP_OK || ks == 1) return rc;
+  int blocks = (M * (N / 4) + 255) / 256;
+  if (blocks > 2 * kSmCount) blocks = 2 * kSmCount;
+  w4a16_splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.partial, ks, M, N, p.bias, p.y);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
 }

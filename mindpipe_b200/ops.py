@@ -42,13 +42,14 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
-    """Zero-initialised scratch, one per (device, stream), grown on demand.
+def _workspace(nbytes: int, device: torch.device, kind: str = "decode") -> torch.Tensor:
+    """Zero-initialised scratch, one per (device, stream, kind), grown on demand.
 
-    The kernels that use it leave it zeroed where it has to be, so it is
-    cleared only when it is (re)allocated.
+    The decode kernels leave their part zeroed where it has to be, so it is
+    cleared only when it is (re)allocated; the prefill split-K partial sums
+    (kind "prefill") overwrite theirs freely, hence the separate buffer.
     """
-    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(), kind)
     with _ws_lock:
         ws = _workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
@@ -211,8 +212,12 @@ def w4a16_linear_decode_static(x, weight_packed, scale_zero, bias=None, out=None
     return y
 
 
-def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None):
-    """``y = x @ dequant(W)^T (+bias)`` on the fp16 tensor cores with the dequant fused in."""
+def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None, *, workspace=None):
+    """``y = x @ dequant(W)^T (+bias)`` on the fp16 tensor cores with the dequant fused in.
+
+    Shapes with few output tiles (M <= 256, narrow N) split K and need scratch: ``workspace`` (uint8)
+    defaults to the cached per-(device, stream) buffer.
+    """
     x2 = _req(x, "x", torch.float16, 2)
     p = _req(weight_packed, "weight_packed", torch.int32, 2)
     sz = _req(scale_zero, "scale_zero", torch.float16, 3)
@@ -225,8 +230,15 @@ def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None):
     y = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     if m == 0:
         return y
-    st = _lib.load().mp_w4a16_linear_prefill(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
-                                             m, n, k, k // groups, _error_word(x2.device).data_ptr(), _stream())
+    lib = _lib.load()
+    nbytes = lib.mp_w4a16_prefill_workspace_bytes(m, n, k)
+    if workspace is not None:
+        ws = _req(workspace, "workspace", torch.uint8, 1)
+    else:
+        ws = _workspace(nbytes, x2.device, "prefill") if nbytes else None
+    st = lib.mp_w4a16_linear_prefill_ex(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
+                                        m, n, k, k // groups, _ptr(ws), 0 if ws is None else ws.numel(),
+                                        _error_word(x2.device).data_ptr(), _stream())
     _lib.check(st, "w4a16_linear_prefill", M=m, N=n, K=k, group=k // groups)
     return y
 
@@ -234,16 +246,19 @@ def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None):
 def w4a16_linear(x, weight_packed, scale_zero, bias=None):
     """W4A16 linear for any number of rows.
 
-    Up to 64 rows go to the weight-streaming decode kernel, more to the
-    tensor-core prefill kernel; shapes the prefill kernel does not take
-    (K or the group size not a multiple of 64) are processed in 64-row slabs.
+    Up to 16 rows go to the weight-streaming decode kernel, more to the
+    tensor-core prefill kernel (which splits K when the batch gives it few
+    tiles); shapes the prefill kernel does not take (K or the group size not
+    a multiple of 64) are processed by the decode kernels in 64-row slabs.
     """
     m, k = x.shape
-    if m <= 64:
+    if m <= 16:
         return w4a16_linear_decode(x, weight_packed, scale_zero, bias)
     group = k // scale_zero.shape[0]
     if k % 64 == 0 and group % 64 == 0:
         return w4a16_linear_prefill(x, weight_packed, scale_zero, bias)
+    if m <= 64:
+        return w4a16_linear_decode(x, weight_packed, scale_zero, bias)
     outs = [w4a16_linear_decode(x[i:i + 64], weight_packed, scale_zero, bias) for i in range(0, m, 64)]
     return torch.cat(outs, dim=0)
 

@@ -240,7 +240,34 @@ def test_prefill_cfg2_m2048_row_sample(n, k):
     assert O.rel_frobenius(y, ref) <= TOL
 
 
-def test_linear_dispatch_uses_prefill_above_64_rows(golden):
+@pytest.mark.parametrize("m,n,k", [(17, 256, 2048), (65, 256, 2048), (128, 512, 4096), (200, 1024, 1024),
+                                   (256, 4096, 4096), (512, 1024, 2048), (700, 512, 1024)])
+def test_prefill_split_k_small_batches(m, n, k):
+    """Few output tiles: K is cut into slices (fp32 partial tiles + an ordered sum).  Same result as the
+    unsplit kernel to fp32 summation order, run-to-run identical, and within tolerance of the oracle."""
+    from mindpipe_b200 import _lib, ops
+    assert _lib.load().mp_w4a16_prefill_workspace_bytes(m, n, k) > 0          # these shapes do split
+    w = synth.normal_weight(n, k, seed=m, index=0).cuda()
+    packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+    sz = ops.w4a16_prepare(scale, zero, k)
+    x = synth.normal_activation(m, k, seed=m, index=1).cuda()
+    bias = (synth.normal_activation(1, n, seed=m, index=2)[0] * 0.1).to(torch.float16).cuda()
+    y = ops.w4a16_linear_prefill(x, packed, sz, bias)
+    ops.check_device_errors()
+    assert torch.equal(y, ops.w4a16_linear_prefill(x, packed, sz, bias))
+    wdq = ops.w4a16_dequant(packed, scale, zero, n, k).float()
+    ref = x.float() @ wdq.T + bias.float()
+    assert ((y.float() - ref).norm() / ref.norm()).item() <= TOL
+    # a null workspace turns the split off: one K slice per tile, same math
+    y1 = torch.empty_like(y)
+    st = _lib.load().mp_w4a16_linear_prefill(x.data_ptr(), packed.data_ptr(), sz.data_ptr(), bias.data_ptr(),
+                                             y1.data_ptr(), m, n, k, 128, ops._error_word(x.device).data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert ((y.float() - y1.float()).abs().max() / ref.abs().max()).item() <= 2e-3
+
+
+def test_linear_dispatch_uses_prefill_above_16_rows(golden):
     from mindpipe_b200 import ops
     w = synth.normal_weight(256, 512, seed=4, index=1).cuda()
     x = synth.normal_activation(200, 512, seed=4, index=2).cuda()
