@@ -604,6 +604,26 @@ def run_suite(args, local_rank):
                 emit(suite="w4a16_mid_m", N=n, K=k, M=m, us=t * 1e6, gbs=w4a16_bytes(n, k, m) / t / 1e9,
                      tflops=2 * m * n * k / t / 1e12)
             del mods
+    if "midm" in want or "all" in want:
+        # the W8A8 linear (per-token quant + int8 GEMM) at decode / small-batch row counts
+        for (n, k) in [(4096, 4096), (14336, 4096), (4096, 14336)]:
+            copies = max(2, int(300e6 // (n * k)) + 1)
+            ws_ = []
+            for c in range(copies):
+                w = synth.normal_weight(n, k, seed=c, index=0).to(dev)
+                qw, sw, _ = ops.act_quant_per_token(w)
+                ws_.append((qw, sw))
+                del w
+            for m in (1, 16, 64, 256, 1024):
+                x = synth.outlier_activation(m, k, seed=0).to(dev)
+
+                def lin(qw, sw):
+                    qx, sx, _ = ops.act_quant_per_token(x)
+                    return ops.w8a8_gemm(qx, sx, qw, sw)
+                t = timed_graph([(lambda qw=qw, sw=sw: lin(qw, sw)) for qw, sw in ws_], rounds=2)
+                emit(suite="w8a8_mid_m", N=n, K=k, M=m, us=t * 1e6, weight_gbs=n * k / t / 1e9,
+                     tops=2 * m * n * k / t / 1e12)
+            del ws_
     if "w8a8" in want or "all" in want:
         for (n, k) in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
             m = 4096

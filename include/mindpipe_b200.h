@@ -250,6 +250,19 @@ int mp_add_rmsnorm_quant(const void* x_f16, void* residual_f16, const void* gamm
 int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const void* w_i8, const void* w_scale_f32,
                  const void* bias_f16, void* y_f16, int M, int N, int K, int* error_word,
                  mp_stream_t stream);
+/*
+ * Same, with scratch for split-K.  At decode and small-batch row counts the
+ * GEMM is a weight stream over few output tiles; the K range of every tile is
+ * then cut into slices so that all SMs stream weights, the slices' raw int32
+ * partial tiles go to `workspace`, and a second kernel adds them (integer
+ * sums: the split changes no output bit) and applies the scales.
+ * mp_w8a8_gemm_workspace_bytes returns the size needed (0 = no split for this
+ * shape); a null workspace means no split.
+ */
+size_t mp_w8a8_gemm_workspace_bytes(int M, int N, int K);
+int mp_w8a8_gemm_ex(const void* qx_i8, const void* x_scale_f32, const void* w_i8,
+                    const void* w_scale_f32, const void* bias_f16, void* y_f16, int M, int N, int K,
+                    void* workspace, size_t workspace_bytes, int* error_word, mp_stream_t stream);
 
 /*
  * Raw accumulators acc[M,N] = qx . w^T as int32: npu_quant_matmul with

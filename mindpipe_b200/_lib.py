@@ -44,6 +44,8 @@ SIGNATURES = {
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "mp_add_rmsnorm_quant": (_I, [_P, _P, _P, ctypes.c_float, _I, _I, _P, _P, _P]),
     "mp_w8a8_gemm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_w8a8_gemm_workspace_bytes": (_Z, [_I, _I, _I]),
+    "mp_w8a8_gemm_ex": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P, _P]),
     "mp_w8a8_gemm_i32": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_affine_quant_per_row": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),
     "mp_w8a8_affine_gemm": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),

@@ -38,6 +38,9 @@ enum : int { EPI_F16 = 0, EPI_I32 = 1, EPI_SWIGLU = 2, EPI_AFFINE = 3 };   // AF
 struct GemmParams {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
+  int k_split;                 // > 1: a tile's K range is cut into this many work items of kb_per_split k-blocks,
+  int kb_per_split;            //      whose raw int32 partial tiles go to `partial` ([k_split][M][N])
+  int* partial;
   int group_m;                 // tile order: groups of this many M tiles are swept across all of N before the next group
   const int* m_tiles_dev;      // grouped: number of 128-row tiles in use (device side)
   const int* tile_expert;      // grouped: expert of each 128-row tile
@@ -70,6 +73,12 @@ struct GemmCfg {
   static constexpr int kScaleBytes = 3 * 4 * 256 * 4;   // per epilogue warp: 256 channel scales (+ zero points, row sums)
   static constexpr size_t kSmem = 1024 + (size_t)kStages * (kABytes + kBBytes) + kBarBytes + kScaleBytes;
 };
+
+// acc * s_token * s_channel (+ bias) with every fp32 operation rounded on its own (no contraction into
+// an fma), so that the GEMM epilogue and the split-K reduce kernel produce the same bits.
+__device__ __forceinline__ float scaled_output(int acc, float s_token, float s_channel) {
+  return __fmul_rn(__fmul_rn(static_cast<float>(acc), s_token), s_channel);
+}
 
 // Tile order.  Concurrent CTAs work on consecutive tile numbers; a group of `group_m` M tiles is swept
 // over all N tiles before the next group starts (M fastest inside the group).  The activation rows of
@@ -143,7 +152,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // tiles are 128 (PAIR: 256) rows of the activations; the grouped plan counts 128-row units
   const int m_units = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
   const int m_tiles = PAIR ? (m_units + 1) / 2 : m_units;
-  const int total = m_tiles * p.n_tiles;
+  const int total = m_tiles * p.n_tiles * p.k_split;           // work items: (tile, K slice)
   const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
   const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
   constexpr int kRowsPerTile = PAIR ? 2 * kBM : kBM;
@@ -155,12 +164,14 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+      for (int work = first_tile; ok && work < total; work += tile_step) {
+        const int tile = work / p.k_split;
+        const int kb0 = (work - tile * p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         int m_tile, n_tile;
         tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
         const int m0 = m_tile * kRowsPerTile + static_cast<int>(rank) * kBM;
         const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
           if (PAIR) {
             // both CTAs' bytes are counted on the leader's barrier
@@ -199,11 +210,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total; tile += tile_step) {
+      for (int work = first_tile; ok && work < total; work += tile_step) {
+        const int kb0 = (work % p.k_split) * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1, abort_flag)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint64_t a_desc = umma_desc_k_sw128(smem_u32(sA + stage * Cfg::kABytes));
@@ -212,9 +224,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
             // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in 16-byte address units
             if (PAIR) {
-              umma_i8_pair(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+              umma_i8_pair(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != kb0 || kk != 0));
             } else {
-              umma_i8(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+              umma_i8(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != kb0 || kk != 0));
             }
           }
           if (PAIR) {                      // release the stage in both CTAs
@@ -243,7 +255,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int buf = 0;
     uint32_t buf_phase = 0;
     const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty0, 0) : tempty0;
-    for (int tile = first_tile; tile < total; tile += tile_step) {
+    for (int work = first_tile; work < total; work += tile_step) {
+      const int tile = work / p.k_split, split = work - tile * p.k_split;
       int m_tile, n_tile;
       tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
       const int e_row0 = p.tile_expert ? p.tile_expert[PAIR ? 2 * m_tile : m_tile] * p.b_rows_per_expert : 0;
@@ -330,9 +343,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t r[32];
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
-          if (EPI == EPI_I32) {
+          if (EPI == EPI_I32 || p.k_split > 1) {
+            // raw accumulators: the int32 output, or this K slice's partial tile (a second kernel adds the
+            // slices -- integer sums, so the split changes no bit -- and applies the scales)
             if (row_ok) {
-              int* dst = static_cast<int*>(p.out) + (size_t)row * p.N + n0 + c0;
+              int* dst = (p.k_split > 1 ? p.partial + (size_t)split * p.M * p.N : static_cast<int*>(p.out)) +
+                         (size_t)row * p.N + n0 + c0;
               if (n0 + c0 + 32 <= p.N && (p.N % 4) == 0) {
 #pragma unroll
                 for (int v = 0; v < 8; ++v)
@@ -361,12 +377,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 v0 = static_cast<float>(t0) * sa * my_scales[c0 + j];
                 v1 = static_cast<float>(t1) * sa * my_scales[c0 + j + 1];
               } else {
-                v0 = static_cast<float>(static_cast<int>(r[j])) * sa * my_scales[c0 + j];
-                v1 = static_cast<float>(static_cast<int>(r[j + 1])) * sa * my_scales[c0 + j + 1];
+                v0 = scaled_output(static_cast<int>(r[j]), sa, my_scales[c0 + j]);
+                v1 = scaled_output(static_cast<int>(r[j + 1]), sa, my_scales[c0 + j + 1]);
               }
               if (p.bias) {
-                if (n0 + c0 + j < p.N) v0 += h2f(p.bias[n0 + c0 + j]);
-                if (n0 + c0 + j + 1 < p.N) v1 += h2f(p.bias[n0 + c0 + j + 1]);
+                if (n0 + c0 + j < p.N) v0 = __fadd_rn(v0, h2f(p.bias[n0 + c0 + j]));
+                if (n0 + c0 + j + 1 < p.N) v1 = __fadd_rn(v1, h2f(p.bias[n0 + c0 + j + 1]));
               }
               hp[j >> 1] = h2_as_u32(__floats2half2_rn(v0, v1));
             }
@@ -464,7 +480,40 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void
   return MP_OK;
 }
 
+// Sum of the K slices' int32 partial tiles, then the epilogue of the unsplit kernel with the same
+// operations in the same order (so a split changes no output bit): f16(float(acc) * s_token * s_channel (+ bias)),
+// or the raw int32 sum.
+template <bool F16OUT>
+__global__ void __launch_bounds__(256)
+w8a8_splitk_reduce_kernel(const int* __restrict__ partial, int k_split, int M, int N, const float* __restrict__ a_scale,
+                          const float* __restrict__ b_scale, const __half* __restrict__ bias, void* __restrict__ out) {
+  const int quads = N >> 2;
+  const size_t slice = (size_t)M * N;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += gridDim.x * blockDim.x) {
+    const int m = i / quads, n = (i - m * quads) << 2;
+    int4 acc = make_int4(0, 0, 0, 0);
+    for (int s = 0; s < k_split; ++s) {
+      const int4 v = *reinterpret_cast<const int4*>(partial + s * slice + (size_t)m * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (F16OUT) {
+      const float sa = a_scale[m];
+      float v0 = scaled_output(acc.x, sa, b_scale[n]), v1 = scaled_output(acc.y, sa, b_scale[n + 1]);
+      float v2 = scaled_output(acc.z, sa, b_scale[n + 2]), v3 = scaled_output(acc.w, sa, b_scale[n + 3]);
+      if (bias) {
+        v0 = __fadd_rn(v0, h2f(bias[n])); v1 = __fadd_rn(v1, h2f(bias[n + 1]));
+        v2 = __fadd_rn(v2, h2f(bias[n + 2])); v3 = __fadd_rn(v3, h2f(bias[n + 3]));
+      }
+      const __half2 lo = __floats2half2_rn(v0, v1), hi = __floats2half2_rn(v2, v3);
+      *reinterpret_cast<uint2*>(static_cast<__half*>(out) + (size_t)m * N + n) = make_uint2(h2_as_u32(lo), h2_as_u32(hi));
+    } else {
+      *reinterpret_cast<int4*>(static_cast<int*>(out) + (size_t)m * N + n) = acc;
+    }
+  }
+}
+
 struct GemmCall {
+  int k_split = 1; int* partial = nullptr;
   const float* a_zero = nullptr; const int* a_rowsum = nullptr; const float* b_zero = nullptr; const int* b_rowsum = nullptr;
   const void* a; const void* b;
   int M, N, K;
@@ -497,6 +546,9 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
   p.row_absmax = c.row_absmax; p.error_word = c.error_word;
   p.group_m = PAIR ? 8 : 16;            // 2048 activation rows per group
+  p.k_split = c.k_split > 1 ? c.k_split : 1;
+  p.kb_per_split = (p.k_blocks + p.k_split - 1) / p.k_split;
+  p.partial = c.partial;
   p.a_zero = c.a_zero; p.a_rowsum = c.a_rowsum; p.b_zero = c.b_zero; p.b_rowsum = c.b_rowsum;
   auto kern = w8a8_gemm_kernel<BN, EPI, PAIR>;
   static thread_local int configured_device = -1;
@@ -525,9 +577,35 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
     MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     return MP_OK;
   }
-  const long long total = (long long)p.m_tiles * p.n_tiles;
+  const long long total = (long long)p.m_tiles * p.n_tiles * p.k_split;
   const int grid = (int)(total < kSmCount ? total : kSmCount);
   kern<<<grid, 192, Cfg::kSmem, st>>>(ta, tb, p);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+// Few output tiles (decode and small batches: the GEMM is a weight stream, and a CTA sustains only
+// ~130 GB/s on its own): cut K until about one work item per SM exists.  Needs N % 4 == 0.
+static int w8a8_k_split(int M, int N, int K) {
+  if (N % 4 != 0 || N <= 128) return 1;
+  const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  if (tiles256 >= kSmCount) return 1;                       // the 128 x 256 form fills the machine
+  const int tiles = ((M + 127) / 128) * ((N + 127) / 128);  // 128 x 128 tiles are used below that
+  const int k_blocks = (K + kBK - 1) / kBK;
+  int ks = kSmCount / tiles;
+  if (ks > k_blocks / 4) ks = k_blocks / 4;
+  if (ks > 16) ks = 16;
+  if (ks < 2) return 1;
+  const int per = (k_blocks + ks - 1) / ks;
+  return (k_blocks + per - 1) / per;                        // no empty slice
+}
+
+template <bool F16OUT>
+static int launch_splitk_reduce(const GemmCall& c, cudaStream_t st) {
+  int blocks = (c.M * (c.N / 4) + 255) / 256;
+  if (blocks > 2 * kSmCount) blocks = 2 * kSmCount;
+  w8a8_splitk_reduce_kernel<F16OUT><<<blocks, 256, 0, st>>>(c.partial, c.k_split, c.M, c.N, c.a_scale, c.b_scale, c.bias,
+                                                           c.out);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }
@@ -573,9 +651,22 @@ int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, cons
 
 using namespace mp;
 
+extern "C" size_t mp_w8a8_gemm_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || use_pair(M, N)) return 0;
+  const int ks = w8a8_k_split(M, N, K);
+  return ks > 1 ? (size_t)ks * M * N * sizeof(int) : 0;
+}
+
 extern "C" int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const void* w_i8, const void* w_scale_f32,
                             const void* bias_f16, void* y_f16, int M, int N, int K, int* error_word,
                             mp_stream_t stream) {
+  return mp_w8a8_gemm_ex(qx_i8, x_scale_f32, w_i8, w_scale_f32, bias_f16, y_f16, M, N, K, nullptr, 0, error_word,
+                         stream);
+}
+
+extern "C" int mp_w8a8_gemm_ex(const void* qx_i8, const void* x_scale_f32, const void* w_i8, const void* w_scale_f32,
+                               const void* bias_f16, void* y_f16, int M, int N, int K, void* workspace,
+                               size_t workspace_bytes, int* error_word, mp_stream_t stream) {
   int rc = check_gemm_args(qx_i8, w_i8, y_f16, M, N, K);
   if (rc != MP_OK) return rc;
   if (!x_scale_f32 || !w_scale_f32) return MP_ERR_INVALID_ARG;
@@ -585,6 +676,16 @@ extern "C" int mp_w8a8_gemm(const void* qx_i8, const void* x_scale_f32, const vo
   c.bias = static_cast<const __half*>(bias_f16); c.out = y_f16; c.error_word = error_word;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (use_pair(M, N)) return launch_gemm<256, EPI_F16, true>(c, st);
+  const int ks = workspace ? w8a8_k_split(M, N, K) : 1;        // without scratch: one K slice per tile
+  if (ks > 1) {
+    if (workspace_bytes < (size_t)ks * M * N * sizeof(int)) return MP_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return MP_ERR_ALIGNMENT;
+    c.k_split = ks;
+    c.partial = static_cast<int*>(workspace);
+    rc = launch_gemm<128, EPI_F16>(c, st);
+    if (rc != MP_OK) return rc;
+    return launch_splitk_reduce<true>(c, st);
+  }
   const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   if (N <= 128 || tiles256 < kSmCount) return launch_gemm<128, EPI_F16>(c, st);
   return launch_gemm<256, EPI_F16>(c, st);

@@ -308,8 +308,12 @@ def check_device_errors(device=None) -> None:
             raise _lib.MindPipeKernelError(f"device {idx}: a bounded wait inside a tensor-core kernel timed out")
 
 
-def w8a8_gemm(qx, x_scale, weight_i8, weight_scale, bias=None):
-    """``f16((qx @ w^T) * x_scale[:,None] * w_scale[None,:] (+bias))`` with int32 accumulation."""
+def w8a8_gemm(qx, x_scale, weight_i8, weight_scale, bias=None, *, workspace=None):
+    """``f16((qx @ w^T) * x_scale[:,None] * w_scale[None,:] (+bias))`` with int32 accumulation.
+
+    At decode / small-batch row counts K is split over the SMs (bit-identical result); the scratch for
+    that is ``workspace`` (uint8) or the cached per-(device, stream) buffer.
+    """
     a = _req(qx, "qx", torch.int8, 2)
     b = _req(weight_i8, "weight", torch.int8, 2)
     sa = _req(x_scale, "x_scale", torch.float32, 1)
@@ -322,8 +326,15 @@ def w8a8_gemm(qx, x_scale, weight_i8, weight_scale, bias=None):
     y = torch.empty((m, n), dtype=torch.float16, device=a.device)
     if m == 0:
         return y
-    st = _lib.load().mp_w8a8_gemm(a.data_ptr(), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), _ptr(bi), y.data_ptr(),
-                                  m, n, k, _error_word(a.device).data_ptr(), _stream())
+    lib = _lib.load()
+    nbytes = lib.mp_w8a8_gemm_workspace_bytes(m, n, k)
+    if workspace is not None:
+        ws = _req(workspace, "workspace", torch.uint8, 1)
+    else:
+        ws = _workspace(nbytes, a.device, "w8a8") if nbytes else None
+    st = lib.mp_w8a8_gemm_ex(a.data_ptr(), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), _ptr(bi), y.data_ptr(),
+                             m, n, k, _ptr(ws), 0 if ws is None else ws.numel(), _error_word(a.device).data_ptr(),
+                             _stream())
     _lib.check(st, "w8a8_gemm", M=m, N=n, K=k)
     return y
 

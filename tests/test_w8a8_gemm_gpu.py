@@ -71,6 +71,32 @@ def test_int32_cta_pair_form_bit_exact(m, n, k):
     assert np.array_equal(acc.cpu().numpy().astype(np.int64), exact_acc(qx, qw))
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 1024, 2048), (64, 4096, 1024), (200, 512, 4096), (16, 4096, 14336)])
+def test_split_k_small_batches_change_no_bit(m, n, k):
+    """Few output tiles: K is cut into slices whose int32 partial tiles are added by a second kernel.
+    Integer sums are order independent and the scale epilogue is the same arithmetic, so the result is
+    bit-identical to the unsplit kernel (called with a null workspace)."""
+    from mindpipe_b200 import _lib, ops
+    lib = _lib.load()
+    assert lib.mp_w8a8_gemm_workspace_bytes(m, n, k) > 0
+    qx, qw = dev(rand_i8((m, k), 7)), dev(rand_i8((n, k), 8))
+    rng = np.random.default_rng(9)
+    sx = dev(rng.uniform(0.01, 0.1, m).astype(np.float32))
+    sw = dev(rng.uniform(0.001, 0.01, n).astype(np.float32))
+    bias = dev(rng.standard_normal(n).astype(np.float16))
+    y = ops.w8a8_gemm(qx, sx, qw, sw, bias)
+    ops.check_device_errors()
+    y1 = torch.empty_like(y)
+    st = lib.mp_w8a8_gemm(qx.data_ptr(), sx.data_ptr(), qw.data_ptr(), sw.data_ptr(), bias.data_ptr(), y1.data_ptr(),
+                          m, n, k, ops._error_word(qx.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    ops.check_device_errors()
+    assert torch.equal(y, y1)
+    acc = exact_acc(qx.cpu().numpy(), qw.cpu().numpy()).astype(np.float32)
+    want = (acc * sx.cpu().numpy()[:, None] * sw.cpu().numpy()[None, :] + bias.cpu().numpy().astype(np.float32))
+    assert O.rel_frobenius(y.cpu().numpy(), want.astype(np.float16)) <= 1e-3
+
+
 def _w8a8_case(m, n, k, seed, bias=False):
     from mindpipe_b200 import ops
     x = synth.outlier_activation(m, k, seed=seed, index=100).numpy()
