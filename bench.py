@@ -223,13 +223,40 @@ def measure_row_parallel(world, rank, dev, dist, iters=50):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) * 1e3
 
-    us_fused = timed(lambda: layer(x))
+    def timed_graph(fn):
+        """`iters` calls captured in one graph and replayed ONCE (every call carries its own epoch, so
+        the graph must not be replayed twice); removes the host launch path from the measurement."""
+        for _ in range(5):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(device=dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(iters):
+                    fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(side):
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3
+
+    us_fused_eager = timed(lambda: layer(x))
     ops.check_device_errors()
+    us_fused = timed_graph(lambda: layer(x))
+    ops.check_device_errors()
+    us_local = timed_graph(lambda: local(x))
     us_nccl = timed(lambda: layer.forward_nccl(x))
-    us_local = timed(lambda: local(x))
     return {"config": f"llama2-70b down_proj 8192x28672 W4A16 g128, M={M_DECODE}, K sharded over {world} ranks",
-            "us_fused_push_allreduce": us_fused, "us_local_gemm_plus_nccl_allreduce": us_nccl,
-            "us_local_gemm_only": us_local, "n_gpus": world,
+            "us_fused_push_allreduce": us_fused, "us_fused_eager_launches": us_fused_eager,
+            "us_local_gemm_only": us_local, "us_local_gemm_plus_nccl_allreduce_eager": us_nccl, "n_gpus": world,
             "algorithmic_gbs_whole_job": w4a16_bytes(n, k, M_DECODE) / (us_fused * 1e-6) / 1e9}
 
 

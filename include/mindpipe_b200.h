@@ -106,24 +106,25 @@ int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const v
  * a tensor-parallel runtime shards down_proj / o_proj; the reference computes
  * the unsharded nn.Linear, quantizer.py:109-130): y = sum over ranks of
  * x[:, K_r] @ dequant(W[:, K_r])^T, M <= 16.
- *   _push    runs the decode kernel on this rank's shard and stores its fp32
- *            partial sums into slot `rank` of EVERY peer's partial buffer
- *            ([world][m_cap][N] fp32, peer-mapped memory), then raises this
- *            rank's arrival word (value `epoch`) on every peer.  block_counter
- *            is a device int that is zero between calls.
+ *   _push    runs the decode kernel on this rank's shard, leaves its fp32
+ *            partial sums in this rank's own buffer ([M][N] fp32, peer-mapped
+ *            memory) and, once every block has stored, raises this rank's
+ *            arrival word (value `epoch`) on every peer.  block_counter is a
+ *            device int that is zero between calls.
  *   _finish  waits (bounded, 2 s -> error word 5) until all arrival words of
- *            this rank have reached `epoch`, adds the slots in rank order
- *            (+bias) and writes fp16: every rank gets the same bits.
- * Use two partial buffers alternately (a peer may already push call n+1 while
- * this rank still sums call n) and a strictly increasing epoch.
+ *            this rank have reached `epoch`, reads every rank's buffer over
+ *            NVLink, adds them in rank order (+bias) and writes fp16: every
+ *            rank gets the same bits.
+ * Use two partial buffers alternately (a peer may still read call n while this
+ * rank already computes call n+1) and a strictly increasing epoch.
  */
 int mp_w4a16_rowparallel_push(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
-                              void* const* peer_partial_f32, void* const* peer_flags_u32,
-                              int* block_counter, int world, int rank, int M, int N, int K_local,
-                              int group, int m_cap, unsigned int epoch, mp_stream_t stream);
-int mp_w4a16_rowparallel_finish(const void* partial_f32, const void* flags_u32, int world,
-                                unsigned int epoch, int M, int N, int m_cap, const void* bias_f16,
-                                void* y_f16, int* error_word, mp_stream_t stream);
+                              void* partial_f32, void* const* peer_flags_u32, int* block_counter,
+                              int world, int rank, int M, int N, int K_local, int group,
+                              unsigned int epoch, mp_stream_t stream);
+int mp_w4a16_rowparallel_finish(void* const* peer_partial_f32, const void* flags_u32, int world,
+                                unsigned int epoch, int M, int N, const void* bias_f16, void* y_f16,
+                                int* error_word, mp_stream_t stream);
 
 /*
  * Host-buffer form of the decode linear for M <= 16, for a host that keeps its

@@ -56,14 +56,15 @@ __device__ __forceinline__ __half hmul_t(__half a, __half b) { return f2h(__fmul
 //  * fp32 route (tiny scales, where 2^-e is not an fp16 number): x * (1/s) in fp32 is within 3 ulps
 //    of the correctly rounded quotient and rounds to the same fp16 value unless it lies within 8 fp32
 //    ulps of an fp16 rounding midpoint; only then is the IEEE division carried out.
-// Row-parallel decode: where a GPU's partial sums go.  partial[q] is rank q's buffer
-// [world][m_cap][N] fp32 (slot r written by rank r), flags[q] its arrival words [world].
+// Row-parallel decode: the kernel leaves its fp32 partial sums in this GPU's own buffer
+// ([M][N]) and, once every block has stored, raises this rank's arrival word on every peer
+// (flags[q] = rank q's arrival words [world]); the peers then read the buffer over NVLink.
 constexpr int kMaxPeerRanks = 16;
 struct DecodePush {
-  float* partial[kMaxPeerRanks];
+  float* partial;            // this rank's buffer (peer-mapped memory)
   unsigned int* flags[kMaxPeerRanks];
   int* block_counter;        // local device int, zero between calls
-  int world, rank, m_cap;
+  int world, rank;
   unsigned int epoch;
 };
 

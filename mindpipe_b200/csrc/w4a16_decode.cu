@@ -544,12 +544,18 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   return launch_decode<4, false, 2, 4>(p, pl, st);
 }
 
-// ---- row-parallel decode: K sharded over GPUs, partial sums pushed to every peer, then summed -------------
-// out[m, n] = f16(sum_r partial[r][m][n] (+ bias)), ranks in ascending order (every GPU computes the same bits).
-// Each block first waits (bounded) until every rank's arrival word has reached `epoch`.
+// ---- row-parallel decode: K sharded over GPUs; every rank leaves its partial sums in its own buffer,
+// raises its arrival word on the peers, and each rank adds all buffers ------------------------------------
+struct PeerPartials {
+  const float* p[kMaxPeerRanks];
+};
+
+// out[m, n] = f16(sum_r partial_r[m][n] (+ bias)), ranks in ascending order (every GPU computes the same
+// bits); partial_r is read from rank r's memory over NVLink.  Each block first waits (bounded) until every
+// rank's arrival word has reached `epoch`.
 __global__ void __launch_bounds__(256)
-rowparallel_finish_kernel(const float* __restrict__ partial, const unsigned int* __restrict__ flags, int world,
-                          unsigned int epoch, int M, int N, int m_cap, const __half* __restrict__ bias,
+rowparallel_finish_kernel(PeerPartials partial, const unsigned int* __restrict__ flags, int world,
+                          unsigned int epoch, int M, int N, const __half* __restrict__ bias,
                           __half* __restrict__ y, int* error_word) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
@@ -561,7 +567,7 @@ rowparallel_finish_kernel(const float* __restrict__ partial, const unsigned int*
     for (unsigned int it = 0;; ++it) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if (static_cast<int>(v - epoch) >= 0) break;                  // rank threadIdx.x has pushed (wrap-safe)
+      if (static_cast<int>(v - epoch) >= 0) break;                  // rank threadIdx.x has stored (wrap-safe)
       if ((it & 0xFF) == 0xFF) {
         uint64_t now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
@@ -580,7 +586,7 @@ rowparallel_finish_kernel(const float* __restrict__ partial, const unsigned int*
     const int m = i / quads, n = (i - m * quads) << 2;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
-      const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)r * m_cap + m) * N + n);
+      const float4 v = *reinterpret_cast<const float4*>(partial.p[r] + (size_t)m * N + n);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     if (bias) {
@@ -592,40 +598,46 @@ rowparallel_finish_kernel(const float* __restrict__ partial, const unsigned int*
 }
 
 extern "C" int mp_w4a16_rowparallel_push(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
-                                         void* const* peer_partial_f32, void* const* peer_flags_u32,
-                                         int* block_counter, int world, int rank, int M, int N, int K_local, int group,
-                                         int m_cap, unsigned int epoch, mp_stream_t stream) {
-  if (!x_f16 || !packed_i32 || !sz_f16x2 || !peer_partial_f32 || !peer_flags_u32 || !block_counter || M <= 0 ||
-      N <= 0 || K_local <= 0 || group <= 0)
+                                         void* partial_f32, void* const* peer_flags_u32, int* block_counter,
+                                         int world, int rank, int M, int N, int K_local, int group,
+                                         unsigned int epoch, mp_stream_t stream) {
+  if (!x_f16 || !packed_i32 || !sz_f16x2 || !partial_f32 || !peer_flags_u32 || !block_counter || M <= 0 || N <= 0 ||
+      K_local <= 0 || group <= 0)
     return MP_ERR_INVALID_ARG;
-  if (world < 1 || world > kMaxPeerRanks || rank < 0 || rank >= world || M > m_cap) return MP_ERR_INVALID_ARG;
+  if (world < 1 || world > kMaxPeerRanks || rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
   if (M > 16 || K_local % group != 0 || N % 4 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(partial_f32, 16)) return MP_ERR_ALIGNMENT;
   DecodePush push{};
   for (int q = 0; q < world; ++q) {
-    if (!peer_partial_f32[q] || !peer_flags_u32[q]) return MP_ERR_INVALID_ARG;
-    if (!aligned(peer_partial_f32[q], 16)) return MP_ERR_ALIGNMENT;
-    push.partial[q] = static_cast<float*>(peer_partial_f32[q]);
+    if (!peer_flags_u32[q]) return MP_ERR_INVALID_ARG;
     push.flags[q] = static_cast<unsigned int*>(peer_flags_u32[q]);
   }
+  push.partial = static_cast<float*>(partial_f32);
   push.block_counter = block_counter;
-  push.world = world; push.rank = rank; push.m_cap = m_cap; push.epoch = epoch;
-  // only the TMA-fed kernel has the push epilogue; shapes it does not take are reported as unsupported
+  push.world = world; push.rank = rank; push.epoch = epoch;
+  // only the TMA-fed kernel has this epilogue; shapes it does not take are reported as unsupported
   return launch_decode_tma(x_f16, packed_i32, sz_f16x2, nullptr, nullptr, M, N, K_local, group,
                            static_cast<cudaStream_t>(stream), &push);
 }
 
-extern "C" int mp_w4a16_rowparallel_finish(const void* partial_f32, const void* flags_u32, int world,
-                                           unsigned int epoch, int M, int N, int m_cap, const void* bias_f16,
-                                           void* y_f16, int* error_word, mp_stream_t stream) {
-  if (!partial_f32 || !flags_u32 || !y_f16 || world < 1 || world > kMaxPeerRanks || M <= 0 || N <= 0 || M > m_cap)
+extern "C" int mp_w4a16_rowparallel_finish(void* const* peer_partial_f32, const void* flags_u32, int world,
+                                           unsigned int epoch, int M, int N, const void* bias_f16, void* y_f16,
+                                           int* error_word, mp_stream_t stream) {
+  if (!peer_partial_f32 || !flags_u32 || !y_f16 || world < 1 || world > kMaxPeerRanks || M <= 0 || N <= 0)
     return MP_ERR_INVALID_ARG;
   if (N % 4 != 0) return MP_ERR_UNSUPPORTED;
-  if (!aligned(partial_f32, 16) || !aligned(y_f16, 8)) return MP_ERR_ALIGNMENT;
+  if (!aligned(y_f16, 8)) return MP_ERR_ALIGNMENT;
+  PeerPartials pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_partial_f32[r]) return MP_ERR_INVALID_ARG;
+    if (!aligned(peer_partial_f32[r], 16)) return MP_ERR_ALIGNMENT;
+    pp.p[r] = static_cast<const float*>(peer_partial_f32[r]);
+  }
   int blocks = (M * (N / 4) + 255) / 256;
   if (blocks > kSmCount) blocks = kSmCount;
   rowparallel_finish_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(partial_f32), static_cast<const unsigned int*>(flags_u32), world, epoch, M, N, m_cap,
-      static_cast<const __half*>(bias_f16), static_cast<__half*>(y_f16), error_word);
+      pp, static_cast<const unsigned int*>(flags_u32), world, epoch, M, N, static_cast<const __half*>(bias_f16),
+      static_cast<__half*>(y_f16), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

@@ -124,9 +124,11 @@ __device__ __forceinline__ uint4 scale_odd_pairs(uint4 v) {
 }
 
 // PUSH (row-parallel linear, K sharded over GPUs): instead of rounding to fp16 the owner blocks store
-// their fp32 sums into slot `rank` of EVERY peer's partial-sum buffer (plain peer stores over NVLink,
-// issued as each cluster finishes, so the transfer overlaps the rest of the grid's compute); the last
-// block of the grid then publishes this rank's arrival on every peer with a release store.
+// their fp32 sums into this GPU's partial-sum buffer, and the last block of the grid publishes this
+// rank's arrival on every peer with a system-scope release store; the peers' finish kernels then read
+// the buffer over NVLink.  (Storing into the peers' buffers from every block was tried first: the
+// system-scope fence each block then needs before it may count itself done waits for its NVLink writes
+// and cost 18 us on a 31 us kernel.)
 template <bool HALF, bool FOLD, bool PUSH>
 __global__ void __launch_bounds__(dt::kThreads, 2)
 w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -391,8 +393,7 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       for (int src = 0; src < ck; ++src) s += slots[(src * MROWS + m) * cols + c];   // rank order: deterministic
       if (n < p.N) {
         if constexpr (PUSH) {
-          const size_t at = ((size_t)p.push.rank * p.push.m_cap + m) * p.N + n;
-          for (int q = 0; q < p.push.world; ++q) p.push.partial[q][at] = s;
+          p.push.partial[(size_t)m * p.N + n] = s;
         } else {
           if (p.bias) s += h2f(p.bias[n]);
           p.y[(size_t)m * p.N + n] = f2h(s);
@@ -400,11 +401,11 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       }
     }
     if constexpr (PUSH) {
-      __threadfence_system();                           // this thread's peer stores before the count below
-      __syncthreads();
+      __syncthreads();                                  // the block's stores ...
       if (tid == 0) {
+        __threadfence();                                // ... are ordered before its count (fences are cumulative)
         const int blocks = static_cast<int>(gridDim.x * gridDim.y);
-        if (atomicAdd(p.push.block_counter, 1) == blocks - 1) {       // every block of this GPU has pushed
+        if (atomicAdd(p.push.block_counter, 1) == blocks - 1) {       // every block of this GPU has stored
           atomicExch(p.push.block_counter, 0);                        // re-armed for the next call
           __threadfence_system();
           for (int q = 0; q < p.push.world; ++q) {
@@ -461,7 +462,7 @@ static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtens
   attrs[0].val.clusterDim.y = ck;
   attrs[0].val.clusterDim.z = 1;
   int n_attrs = 1;
-  if (g_decode_pdl) {
+  if (g_decode_pdl && !PUSH) {      // a push launch shares its block counter with the previous one: no early start
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     n_attrs = 2;

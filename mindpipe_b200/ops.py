@@ -123,7 +123,8 @@ def w4a16_prepare(weight_scale, weight_zero_point, in_features: int):
 
 
 def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int = 0, workspace=None, out=None):
-    """``y[M,N] = x[M,K] @ dequant(W)^T (+bias)`` for M <= 64 (decode shapes).
+    """``y[M,N] = x[M,K] @ dequant(W)^T (+bias)`` with the weight-streaming kernels (M <= 64; meant for
+    M <= 16 -- above that ``w4a16_linear`` prefers the split-K tensor-core GEMM).
 
     ``workspace`` (uint8, zero-filled when created, not shared by calls that
     may overlap) defaults to a cached buffer per device and stream.

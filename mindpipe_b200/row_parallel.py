@@ -6,11 +6,11 @@ Rank ``r`` of ``P`` holds columns ``[r*K/P, (r+1)*K/P)`` of the weight (tensor p
 row-parallel kind, what a serving runtime does for ``down_proj`` / ``o_proj``; the reference computes
 the unsharded ``nn.Linear``, algorithm/quantization/ptq/awq/source/awq/quantize/quantizer.py:109-130).
 
-The reduction is fused into the decode kernel: its epilogue stores the fp32 partial sums straight into
-every peer's buffer over NVLink (``torch.distributed._symmetric_memory`` peer mappings), the grid's last
-block raises an arrival word on every peer, and a small second kernel waits for all arrival words and
-adds the ``P`` slots in rank order -- so all ranks end with bit-identical fp16 outputs, no NCCL call
-and no host synchronisation sit on the path.  ``forward_nccl`` is the plain fallback (local linear +
+The exchange is driven from the device: the decode kernel leaves its fp32 partial sums in a peer-mapped
+buffer (``torch.distributed._symmetric_memory``) and its last block raises an arrival word on every
+peer; a small second kernel waits for all arrival words, reads the ``P`` buffers over NVLink and adds
+them in rank order -- so all ranks end with bit-identical fp16 outputs, and no NCCL call, barrier
+kernel or host synchronisation sits on the path.  ``forward_nccl`` is the plain fallback (local linear +
 ``all_reduce``) for process groups without peer mappings.
 """
 from __future__ import annotations
@@ -85,7 +85,7 @@ class RowParallelW4A16Linear(torch.nn.Module):
     def _setup_symmetric(self):
         import torch.distributed._symmetric_memory as symm
         dev = self.local.weight_packed.device
-        self.slot_bytes = self.world * self.max_rows * self.out_features * 4        # one [P][m_cap][N] fp32 buffer
+        self.slot_bytes = self.max_rows * self.out_features * 4                      # one [m_cap][N] fp32 buffer
         self.off_partial = 256                                                        # arrival words first
         total = self.off_partial + 2 * self.slot_bytes
         self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
@@ -123,17 +123,17 @@ class RowParallelW4A16Linear(torch.nn.Module):
         if self.local._scale_zero is None:
             self.local.process_weights_after_loading()
         self.epoch += 1
-        par = self.epoch & 1                         # a peer may push call n+1 while this rank still sums call n
+        par = self.epoch & 1                         # a peer may still read call n while this rank computes call n+1
         stream = torch.cuda.current_stream().cuda_stream
         y = torch.empty((m, self.out_features), dtype=torch.float16, device=x2.device)
-        st = lib.mp_w4a16_rowparallel_push(x2.data_ptr(), self.local.weight_packed.data_ptr(),
-                                           self.local._scale_zero.data_ptr(), self.p_partial[par], self.p_flags,
-                                           self.counter.data_ptr(), self.world, self.rank, m, self.out_features, k_loc,
-                                           self.local.group_size, self.max_rows, self.epoch, stream)
-        _lib.check(st, "w4a16_rowparallel_push", M=m, N=self.out_features, K_local=k_loc)
         mine = self.buf.data_ptr()
-        st = lib.mp_w4a16_rowparallel_finish(mine + self.off_partial + par * self.slot_bytes, mine, self.world,
-                                             self.epoch, m, self.out_features, self.max_rows,
+        st = lib.mp_w4a16_rowparallel_push(x2.data_ptr(), self.local.weight_packed.data_ptr(),
+                                           self.local._scale_zero.data_ptr(),
+                                           mine + self.off_partial + par * self.slot_bytes, self.p_flags,
+                                           self.counter.data_ptr(), self.world, self.rank, m, self.out_features, k_loc,
+                                           self.local.group_size, self.epoch, stream)
+        _lib.check(st, "w4a16_rowparallel_push", M=m, N=self.out_features, K_local=k_loc)
+        st = lib.mp_w4a16_rowparallel_finish(self.p_partial[par], mine, self.world, self.epoch, m, self.out_features,
                                              None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
                                              ops._error_word(x2.device).data_ptr(), stream)
         _lib.check(st, "w4a16_rowparallel_finish", M=m, N=self.out_features)
