@@ -107,24 +107,28 @@ int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const v
  * the unsharded nn.Linear, quantizer.py:109-130): y = sum over ranks of
  * x[:, K_r] @ dequant(W[:, K_r])^T, M <= 16.
  *   _push    runs the decode kernel on this rank's shard, leaves its fp32
- *            partial sums in this rank's own buffer ([M][N] fp32, peer-mapped
- *            memory) and, once every block has stored, raises this rank's
- *            arrival word (value `epoch`) on every peer.  block_counter is a
- *            device int that is zero between calls.
+ *            partial sums in one of this rank's two buffers ([M][N] fp32 each,
+ *            peer-mapped memory; the call number's parity picks it, because a
+ *            peer may still read call n while this rank computes call n+1) and,
+ *            once every block has stored, advances the call number in
+ *            epoch_counter (device word, zero at start) and raises it as this
+ *            rank's arrival word on every peer.  block_counter is a device int
+ *            that is zero between calls.
  *   _finish  waits (bounded, 2 s -> error word 5) until all arrival words of
- *            this rank have reached `epoch`, reads every rank's buffer over
- *            NVLink, adds them in rank order (+bias) and writes fp16: every
- *            rank gets the same bits.
- * Use two partial buffers alternately (a peer may still read call n while this
- * rank already computes call n+1) and a strictly increasing epoch.
+ *            this rank have reached the call number, reads every rank's buffer
+ *            over NVLink, adds them in rank order (+bias) and writes fp16:
+ *            every rank gets the same bits.
+ * No argument changes from call to call, so the pair can sit in a captured CUDA
+ * graph (replayed the same number of times on every rank).
  */
 int mp_w4a16_rowparallel_push(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
-                              void* partial_f32, void* const* peer_flags_u32, int* block_counter,
-                              int world, int rank, int M, int N, int K_local, int group,
-                              unsigned int epoch, mp_stream_t stream);
-int mp_w4a16_rowparallel_finish(void* const* peer_partial_f32, const void* flags_u32, int world,
-                                unsigned int epoch, int M, int N, const void* bias_f16, void* y_f16,
-                                int* error_word, mp_stream_t stream);
+                              void* partial0_f32, void* partial1_f32, void* const* peer_flags_u32,
+                              int* block_counter, void* epoch_counter_u32, int world, int rank, int M,
+                              int N, int K_local, int group, mp_stream_t stream);
+int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void* const* peer_partial1_f32,
+                                const void* flags_u32, int world, const void* epoch_counter_u32, int M,
+                                int N, const void* bias_f16, void* y_f16, int* error_word,
+                                mp_stream_t stream);
 
 /*
  * Host-buffer form of the decode linear for M <= 16, for a host that keeps its
@@ -373,6 +377,9 @@ int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk
  *                   of every peer's flag array (uint32[world], zero at start) and
  *                   waits, for at most 2 s, until all local slots reached it; a
  *                   timeout sets *error_word = 4 and returns.
+ * mp_peer_barrier_counted  the same barrier with the epoch kept in a device word
+ *                   (zero at start) that the kernel advances itself, so that a
+ *                   captured CUDA graph containing it can be replayed.
  * mp_moe_ep_plan    reads every peer's routing plan (as written by
  *                   mp_moe_route_gather_quant over all `num_experts` experts)
  *                   and lays out this rank's expert-sorted buffer: xplan_i32
@@ -382,11 +389,13 @@ int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk
  *                   routed buffers (int8 rows + fp32 scales) into sorted order.
  * mp_moe_ep_push    stores each result row into its source rank's result buffer
  *                   at the row's original position.
- * capacity_rows: rows of the expert-sorted buffers (multiple of 128; an upper
+ * capacity_rows: rows of the expert-sorted buffers (multiple of 256; an upper
  * bound, e.g. mp_moe_padded_rows(local experts, world * tokens * k)).
  */
 int mp_peer_barrier(const void* const* peer_flag_ptrs, int world, int rank, unsigned int epoch,
                     int* error_word, mp_stream_t stream);
+int mp_peer_barrier_counted(const void* const* peer_flag_ptrs, int world, int rank,
+                            void* epoch_counter_u32, int* error_word, mp_stream_t stream);
 size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
 int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
                    int capacity_rows, void* xplan_i32, mp_stream_t stream);

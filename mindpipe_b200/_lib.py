@@ -31,8 +31,8 @@ SIGNATURES = {
     "mp_w4a16_decode_workspace_bytes_ex": (_Z, [_I, _I, _I, _I]),
     "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
-    "mp_w4a16_rowparallel_push": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _U, _P]),
-    "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _I, _U, _I, _I, _P, _P, _P, _P]),
+    "mp_w4a16_rowparallel_push": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_w4a16_linear_decode_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_w4a16_prefill_workspace_bytes": (_Z, [_I, _I, _I]),
@@ -58,6 +58,7 @@ SIGNATURES = {
     "mp_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "mp_gather_rows": (_I, [_P, _P, _I, _I, _P, _P]),
     "mp_peer_barrier": (_I, [_P, _I, _I, ctypes.c_uint, _P, _P]),
+    "mp_peer_barrier_counted": (_I, [_P, _I, _I, _P, _P, _P]),
     "mp_moe_ep_plan_ints": (_Z, [_I, _I, _I]),
     "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),

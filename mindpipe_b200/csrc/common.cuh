@@ -61,11 +61,11 @@ __device__ __forceinline__ __half hmul_t(__half a, __half b) { return f2h(__fmul
 // (flags[q] = rank q's arrival words [world]); the peers then read the buffer over NVLink.
 constexpr int kMaxPeerRanks = 16;
 struct DecodePush {
-  float* partial;            // this rank's buffer (peer-mapped memory)
+  float* partial[2];         // this rank's two buffers (peer-mapped memory), used alternately
   unsigned int* flags[kMaxPeerRanks];
   int* block_counter;        // local device int, zero between calls
+  unsigned int* epoch;       // local device word: number of calls completed (this call is *epoch + 1)
   int world, rank;
-  unsigned int epoch;
 };
 
 constexpr float kRoundMagic = 12582912.0f;   // 1.5 * 2^23: (v + magic) holds rint(v) in its low mantissa bits

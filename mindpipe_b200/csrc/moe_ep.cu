@@ -38,7 +38,8 @@ __device__ __forceinline__ uint64_t ep_timer_ns() {
 }
 
 // flags[r] on rank p is written by rank r.  Thread r < world: publish, then wait for peer r.
-__global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int epoch, int* error_word) {
+__device__ __forceinline__ void peer_barrier_body(const PeerPtrs& peer_flags, int world, int rank, unsigned int epoch,
+                                                  int* error_word) {
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();                                           // everything this GPU wrote so far is visible
@@ -56,6 +57,24 @@ __global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, un
     }
   }
   __threadfence_system();
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int epoch, int* error_word) {
+  peer_barrier_body(peer_flags, world, rank, epoch, error_word);
+}
+
+// Same, with the epoch kept in device memory and advanced by the kernel itself: the launch carries no
+// per-call value, so a captured CUDA graph containing it can be replayed (every rank replays the same
+// sequence of barriers, so the counters advance in step).
+__global__ void peer_barrier_counted_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int* epoch_counter,
+                                            int* error_word) {
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_counter + 1;
+    *epoch_counter = s_epoch;
+  }
+  __syncthreads();
+  peer_barrier_body(peer_flags, world, rank, s_epoch, error_word);
 }
 
 // Extended plan of the receiving rank (ints):
@@ -171,6 +190,18 @@ extern "C" int mp_peer_barrier(const void* const* peer_flag_ptrs, int world, int
   if (rc != MP_OK) return rc;
   if (rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
   peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, world, rank, epoch, error_word);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_peer_barrier_counted(const void* const* peer_flag_ptrs, int world, int rank,
+                                       void* epoch_counter_u32, int* error_word, mp_stream_t stream) {
+  PeerPtrs pf;
+  int rc = fill_peers(pf, peer_flag_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (rank < 0 || rank >= world || !epoch_counter_u32) return MP_ERR_INVALID_ARG;
+  peer_barrier_counted_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      pf, world, rank, static_cast<unsigned int*>(epoch_counter_u32), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

@@ -547,7 +547,7 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
 // ---- row-parallel decode: K sharded over GPUs; every rank leaves its partial sums in its own buffer,
 // raises its arrival word on the peers, and each rank adds all buffers ------------------------------------
 struct PeerPartials {
-  const float* p[kMaxPeerRanks];
+  const float* p[2][kMaxPeerRanks];     // [buffer parity][rank]
 };
 
 // out[m, n] = f16(sum_r partial_r[m][n] (+ bias)), ranks in ascending order (every GPU computes the same
@@ -555,11 +555,13 @@ struct PeerPartials {
 // rank's arrival word has reached `epoch`.
 __global__ void __launch_bounds__(256)
 rowparallel_finish_kernel(PeerPartials partial, const unsigned int* __restrict__ flags, int world,
-                          unsigned int epoch, int M, int N, const __half* __restrict__ bias,
-                          __half* __restrict__ y, int* error_word) {
+                          const unsigned int* __restrict__ epoch_counter, int M, int N,
+                          const __half* __restrict__ bias, __half* __restrict__ y, int* error_word) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
+  const unsigned int epoch = *epoch_counter;           // advanced by the push kernel that ran before this one
+  const float* const* src = partial.p[epoch & 1u];
   if (threadIdx.x < world) {
     const unsigned int* f = flags + threadIdx.x;
     uint64_t t0;
@@ -586,7 +588,7 @@ rowparallel_finish_kernel(PeerPartials partial, const unsigned int* __restrict__
     const int m = i / quads, n = (i - m * quads) << 2;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
-      const float4 v = *reinterpret_cast<const float4*>(partial.p[r] + (size_t)m * N + n);
+      const float4 v = *reinterpret_cast<const float4*>(src[r] + (size_t)m * N + n);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     if (bias) {
@@ -598,46 +600,51 @@ rowparallel_finish_kernel(PeerPartials partial, const unsigned int* __restrict__
 }
 
 extern "C" int mp_w4a16_rowparallel_push(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
-                                         void* partial_f32, void* const* peer_flags_u32, int* block_counter,
-                                         int world, int rank, int M, int N, int K_local, int group,
-                                         unsigned int epoch, mp_stream_t stream) {
-  if (!x_f16 || !packed_i32 || !sz_f16x2 || !partial_f32 || !peer_flags_u32 || !block_counter || M <= 0 || N <= 0 ||
-      K_local <= 0 || group <= 0)
+                                         void* partial0_f32, void* partial1_f32, void* const* peer_flags_u32,
+                                         int* block_counter, void* epoch_counter_u32, int world, int rank, int M, int N,
+                                         int K_local, int group, mp_stream_t stream) {
+  if (!x_f16 || !packed_i32 || !sz_f16x2 || !partial0_f32 || !partial1_f32 || !peer_flags_u32 || !block_counter ||
+      !epoch_counter_u32 || M <= 0 || N <= 0 || K_local <= 0 || group <= 0)
     return MP_ERR_INVALID_ARG;
   if (world < 1 || world > kMaxPeerRanks || rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
   if (M > 16 || K_local % group != 0 || N % 4 != 0) return MP_ERR_UNSUPPORTED;
-  if (!aligned(partial_f32, 16)) return MP_ERR_ALIGNMENT;
+  if (!aligned(partial0_f32, 16) || !aligned(partial1_f32, 16)) return MP_ERR_ALIGNMENT;
   DecodePush push{};
   for (int q = 0; q < world; ++q) {
     if (!peer_flags_u32[q]) return MP_ERR_INVALID_ARG;
     push.flags[q] = static_cast<unsigned int*>(peer_flags_u32[q]);
   }
-  push.partial = static_cast<float*>(partial_f32);
+  push.partial[0] = static_cast<float*>(partial0_f32);
+  push.partial[1] = static_cast<float*>(partial1_f32);
   push.block_counter = block_counter;
-  push.world = world; push.rank = rank; push.epoch = epoch;
+  push.epoch = static_cast<unsigned int*>(epoch_counter_u32);
+  push.world = world; push.rank = rank;
   // only the TMA-fed kernel has this epilogue; shapes it does not take are reported as unsupported
   return launch_decode_tma(x_f16, packed_i32, sz_f16x2, nullptr, nullptr, M, N, K_local, group,
                            static_cast<cudaStream_t>(stream), &push);
 }
 
-extern "C" int mp_w4a16_rowparallel_finish(void* const* peer_partial_f32, const void* flags_u32, int world,
-                                           unsigned int epoch, int M, int N, const void* bias_f16, void* y_f16,
-                                           int* error_word, mp_stream_t stream) {
-  if (!peer_partial_f32 || !flags_u32 || !y_f16 || world < 1 || world > kMaxPeerRanks || M <= 0 || N <= 0)
+extern "C" int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void* const* peer_partial1_f32,
+                                           const void* flags_u32, int world, const void* epoch_counter_u32, int M,
+                                           int N, const void* bias_f16, void* y_f16, int* error_word,
+                                           mp_stream_t stream) {
+  if (!peer_partial0_f32 || !peer_partial1_f32 || !flags_u32 || !epoch_counter_u32 || !y_f16 || world < 1 ||
+      world > kMaxPeerRanks || M <= 0 || N <= 0)
     return MP_ERR_INVALID_ARG;
   if (N % 4 != 0) return MP_ERR_UNSUPPORTED;
   if (!aligned(y_f16, 8)) return MP_ERR_ALIGNMENT;
   PeerPartials pp{};
   for (int r = 0; r < world; ++r) {
-    if (!peer_partial_f32[r]) return MP_ERR_INVALID_ARG;
-    if (!aligned(peer_partial_f32[r], 16)) return MP_ERR_ALIGNMENT;
-    pp.p[r] = static_cast<const float*>(peer_partial_f32[r]);
+    if (!peer_partial0_f32[r] || !peer_partial1_f32[r]) return MP_ERR_INVALID_ARG;
+    if (!aligned(peer_partial0_f32[r], 16) || !aligned(peer_partial1_f32[r], 16)) return MP_ERR_ALIGNMENT;
+    pp.p[0][r] = static_cast<const float*>(peer_partial0_f32[r]);
+    pp.p[1][r] = static_cast<const float*>(peer_partial1_f32[r]);
   }
   int blocks = (M * (N / 4) + 255) / 256;
   if (blocks > kSmCount) blocks = kSmCount;
   rowparallel_finish_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      pp, static_cast<const unsigned int*>(flags_u32), world, epoch, M, N, static_cast<const __half*>(bias_f16),
-      static_cast<__half*>(y_f16), error_word);
+      pp, static_cast<const unsigned int*>(flags_u32), world, static_cast<const unsigned int*>(epoch_counter_u32), M, N,
+      static_cast<const __half*>(bias_f16), static_cast<__half*>(y_f16), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

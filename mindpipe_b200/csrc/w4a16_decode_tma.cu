@@ -385,6 +385,10 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   }
   cluster.sync();                                    // remote stores are visible; nobody is written to after this
+  // PUSH: this call's number; the counter is advanced by the grid's last block, after every block has
+  // read it here, and its parity picks the partial buffer
+  [[maybe_unused]] const unsigned int push_epoch = PUSH ? *p.push.epoch + 1u : 0u;
+  [[maybe_unused]] float* push_dst = PUSH ? p.push.partial[push_epoch & 1u] : nullptr;
   if (!*abort_flag) {
     for (int e = tid; e < p.M * cols; e += dt::kThreads) {
       const int m = e / cols, c = e - m * cols;
@@ -393,7 +397,7 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       for (int src = 0; src < ck; ++src) s += slots[(src * MROWS + m) * cols + c];   // rank order: deterministic
       if (n < p.N) {
         if constexpr (PUSH) {
-          p.push.partial[(size_t)m * p.N + n] = s;
+          push_dst[(size_t)m * p.N + n] = s;
         } else {
           if (p.bias) s += h2f(p.bias[n]);
           p.y[(size_t)m * p.N + n] = f2h(s);
@@ -407,10 +411,11 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const int blocks = static_cast<int>(gridDim.x * gridDim.y);
         if (atomicAdd(p.push.block_counter, 1) == blocks - 1) {       // every block of this GPU has stored
           atomicExch(p.push.block_counter, 0);                        // re-armed for the next call
+          *p.push.epoch = push_epoch;
           __threadfence_system();
           for (int q = 0; q < p.push.world; ++q) {
             unsigned int* flag = p.push.flags[q] + p.push.rank;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.push.epoch) : "memory");
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(push_epoch) : "memory");
           }
         }
       }

@@ -175,9 +175,10 @@ class ExpertParallelMoE(torch.nn.Module):
 
 class SymmetricExpertParallelMoE(torch.nn.Module):
     """Expert-parallel W8A8 MoE whose dispatch and return run over NVLink peer memory, driven
-    entirely from the device: no row count ever visits the host, so a forward is a fixed sequence
-    of stream-ordered launches (route -> barrier -> plan -> pull -> expert stage -> push ->
-    barrier -> combine).
+    entirely from the device: no row count ever visits the host and the barrier epochs live in
+    device memory, so a forward is a fixed sequence of stream-ordered launches (route -> barrier ->
+    plan -> pull -> expert stage -> push -> barrier -> combine) that can be captured in a CUDA graph
+    and replayed (every rank must replay it the same number of times).
 
     Each rank keeps its routing plan, routed int8 rows, their scales and a result buffer in one
     symmetric allocation that every peer maps (``torch.distributed._symmetric_memory``).  Peers
@@ -238,14 +239,13 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
                                  device=dev)
         self.q_sorted = torch.empty((self.sorted_cap, self.hidden), dtype=torch.int8, device=dev)
         self.s_sorted = torch.empty(self.sorted_cap, dtype=torch.float32, device=dev)
-        self.epoch = 0
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)     # advanced by the barrier kernel itself
 
     def _barrier(self):
         from . import _lib, ops
-        self.epoch += 1
-        st = _lib.load().mp_peer_barrier(self.p_flags, self.world, self.rank, self.epoch,
-                                         ops._error_word(self.buf.device).data_ptr(),
-                                         torch.cuda.current_stream().cuda_stream)
+        st = _lib.load().mp_peer_barrier_counted(self.p_flags, self.world, self.rank, self.epoch.data_ptr(),
+                                                 ops._error_word(self.buf.device).data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream)
         _lib.check(st, "peer_barrier", world=self.world, rank=self.rank)
 
     @torch.no_grad()

@@ -77,7 +77,6 @@ class RowParallelW4A16Linear(torch.nn.Module):
         if local_linear.bias is not None:
             raise ValueError("the local shard must not carry the bias (it would be added once per rank)")
         self.bias = bias
-        self.epoch = 0
         self.symmetric = bool(symmetric)
         if self.symmetric:
             self._setup_symmetric()
@@ -97,7 +96,8 @@ class RowParallelW4A16Linear(torch.nn.Module):
         self.p_flags = (ctypes.c_void_p * self.world)(*bases)
         self.p_partial = [(ctypes.c_void_p * self.world)(*[b + self.off_partial + par * self.slot_bytes for b in bases])
                           for par in range(2)]
-        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)     # blocks of the running call that have stored
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)       # calls completed (advanced by the kernel)
 
     @staticmethod
     def from_full(packed, scale, zero_point, bias, group_size: int, group=None, device=None, **kw):
@@ -122,18 +122,16 @@ class RowParallelW4A16Linear(torch.nn.Module):
             raise ValueError(f"x_local must be [<= {self.max_rows}, {self.local.in_features}], got {tuple(x2.shape)}")
         if self.local._scale_zero is None:
             self.local.process_weights_after_loading()
-        self.epoch += 1
-        par = self.epoch & 1                         # a peer may still read call n while this rank computes call n+1
         stream = torch.cuda.current_stream().cuda_stream
         y = torch.empty((m, self.out_features), dtype=torch.float16, device=x2.device)
-        mine = self.buf.data_ptr()
+        mine = self.buf.data_ptr() + self.off_partial
         st = lib.mp_w4a16_rowparallel_push(x2.data_ptr(), self.local.weight_packed.data_ptr(),
-                                           self.local._scale_zero.data_ptr(),
-                                           mine + self.off_partial + par * self.slot_bytes, self.p_flags,
-                                           self.counter.data_ptr(), self.world, self.rank, m, self.out_features, k_loc,
-                                           self.local.group_size, self.epoch, stream)
+                                           self.local._scale_zero.data_ptr(), mine, mine + self.slot_bytes,
+                                           self.p_flags, self.counter.data_ptr(), self.epoch.data_ptr(), self.world,
+                                           self.rank, m, self.out_features, k_loc, self.local.group_size, stream)
         _lib.check(st, "w4a16_rowparallel_push", M=m, N=self.out_features, K_local=k_loc)
-        st = lib.mp_w4a16_rowparallel_finish(self.p_partial[par], mine, self.world, self.epoch, m, self.out_features,
+        st = lib.mp_w4a16_rowparallel_finish(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(), self.world,
+                                             self.epoch.data_ptr(), m, self.out_features,
                                              None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
                                              ops._error_word(x2.device).data_ptr(), stream)
         _lib.check(st, "w4a16_rowparallel_finish", M=m, N=self.out_features)

@@ -54,6 +54,19 @@ def _worker(rank, world, port, ret):
             out2 = sym(hs[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
         ops.check_device_errors()
         ok_moe = ok_moe and torch.equal(out2, ref[a:b])
+        # the forward is a fixed launch sequence (barrier epochs live on the device): capture and replay it
+        xa, ia, wa = hs[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous()
+        side = torch.cuda.Stream(device=dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                out3 = sym(xa, ia, wa)
+            for _ in range(3):
+                out3.zero_()
+                graph.replay()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        ok_moe = ok_moe and torch.equal(out3, ref[a:b])
         # ---- column-parallel W4A16 vs single GPU ----
         n, k = 1024, 2048
         wt = synth.normal_weight(n, k, seed=2).to(dev)
@@ -82,6 +95,20 @@ def _worker(rank, world, port, ret):
             ok_row = ok_row and all(torch.equal(e, everyone[0]) for e in everyone)    # rank-order sum: same bits
             y2 = rp.forward_nccl(xm[:, c0:c1].contiguous())
             ok_row = ok_row and ((y2.float() - want).norm() / want.norm()).item() <= 1e-2
+        # replayed from a CUDA graph (the call counter lives on the device)
+        x16 = synth.normal_activation(16, k, seed=3, index=99).to(dev)[:, c0:c1].contiguous()
+        y_eager = rp(x16).clone()
+        side = torch.cuda.Stream(device=dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                y_graph = rp(x16)
+            for _ in range(3):
+                y_graph.zero_()
+                graph.replay()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        ok_row = ok_row and torch.equal(y_graph, y_eager)
         ret[rank] = (bool(ok_moe), bool(ok_col), bool(ok_row))
     finally:
         dist.destroy_process_group()
