@@ -84,6 +84,7 @@ class ClockSampler:
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
+        self._ready = threading.Event()      # NVML is up and the first sample has been taken
         self._thr = None
 
     def _run(self):
@@ -100,6 +101,7 @@ class ClockSampler:
             }
             while not self._stop.is_set():
                 self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                self._ready.set()
                 r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
                 for bit, name in names.items():
                     if r & bit:
@@ -107,10 +109,12 @@ class ClockSampler:
                 time.sleep(0.02)
         except Exception as err:  # NVML missing: report that instead of clocks
             self.reasons.add(f"nvml_unavailable:{type(err).__name__}")
+            self._ready.set()
 
     def __enter__(self):
         self._thr = threading.Thread(target=self._run, daemon=True)
         self._thr.start()
+        self._ready.wait(timeout=10)         # NVML start-up must not eat the region that is to be sampled
         return self
 
     def __exit__(self, *exc):
