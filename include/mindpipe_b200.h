@@ -396,6 +396,29 @@ int mp_peer_barrier(const void* const* peer_flag_ptrs, int world, int rank, unsi
                     int* error_word, mp_stream_t stream);
 int mp_peer_barrier_counted(const void* const* peer_flag_ptrs, int world, int rank,
                             void* epoch_counter_u32, int* error_word, mp_stream_t stream);
+/*
+ * Row-parallel W8A8 linear (input features sharded over `world` GPUs) -- the role of
+ * npu_mm_all_reduce_base(qx, W, hcom, reduce_op="sum", dequant_scale, pertoken_scale)
+ * (acceleration/runtime_patches/vllm_ascend.patch:1428-1449): every rank quantises
+ * its activation slice per token (mp_act_quant_per_token, scales into peer-mapped
+ * memory), multiplies it with its weight slice into raw int32 accumulators in
+ * peer-mapped memory (mp_w8a8_gemm_i32), then
+ *   mp_peer_signal              advances the call counter (device word) and raises
+ *                               it as this rank's arrival word on every peer;
+ *   mp_w8a8_rowparallel_finish  waits (bounded, 2 s -> error word 5) for all arrival
+ *                               words, reads every rank's accumulators and token
+ *                               scales over NVLink and writes
+ *                               f16(sum_r acc_r * xscale_r[m] * w_scale[n] (+bias)),
+ *                               fp32 adds in rank order: the same bits on every rank.
+ * Use two accumulator/scale buffers alternately (a peer may still read call n
+ * while this rank computes call n+1).
+ */
+int mp_peer_signal(const void* const* peer_flag_ptrs, int world, int rank, void* epoch_counter_u32,
+                   mp_stream_t stream);
+int mp_w8a8_rowparallel_finish(const void* const* peer_acc_i32, const void* const* peer_xscale_f32,
+                               const void* flags_u32, int world, const void* epoch_counter_u32, int M,
+                               int N, const void* w_scale_f32, const void* bias_f16, void* y_f16,
+                               int* error_word, mp_stream_t stream);
 size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
 int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
                    int capacity_rows, void* xplan_i32, mp_stream_t stream);

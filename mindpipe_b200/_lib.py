@@ -59,6 +59,8 @@ SIGNATURES = {
     "mp_gather_rows": (_I, [_P, _P, _I, _I, _P, _P]),
     "mp_peer_barrier": (_I, [_P, _I, _I, ctypes.c_uint, _P, _P]),
     "mp_peer_barrier_counted": (_I, [_P, _I, _I, _P, _P, _P]),
+    "mp_peer_signal": (_I, [_P, _I, _I, _P, _P]),
+    "mp_w8a8_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P]),
     "mp_moe_ep_plan_ints": (_Z, [_I, _I, _I]),
     "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),

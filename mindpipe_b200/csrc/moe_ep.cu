@@ -206,6 +206,129 @@ extern "C" int mp_peer_barrier_counted(const void* const* peer_flag_ptrs, int wo
   return MP_OK;
 }
 
+// ---- row-parallel W8A8 linear: K sharded over GPUs ------------------------------------------------------
+// Every rank quantises its activation slice per token, multiplies it with its weight slice into raw
+// int32 accumulators kept in peer-mapped memory, and announces them; every rank then reads all the
+// accumulators and per-token scales over NVLink and sums the dequantised partial products in rank order.
+
+// After this rank's GEMM (stream order): advance the call counter and raise it on every peer.
+__global__ void peer_signal_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int* epoch_counter) {
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_counter + 1;
+    *epoch_counter = s_epoch;
+  }
+  __syncthreads();
+  if (threadIdx.x >= world) return;
+  __threadfence_system();                                           // the accumulators and scales are visible first
+  unsigned int* remote = static_cast<unsigned int*>(peer_flags.p[threadIdx.x]) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(s_epoch) : "memory");
+}
+
+struct PeerPair {
+  const void* acc[kMaxRanks];
+  const void* xscale[kMaxRanks];
+};
+
+// y[m, n] = f16(sum_r float(acc_r[m, n]) * xscale_r[m] * wscale[n] (+ bias)): each product rounded on its own,
+// fp32 adds in rank order, one rounding to fp16 -- the same bits on every rank.
+__global__ void __launch_bounds__(256)
+w8a8_rowparallel_finish_kernel(PeerPair peers, const unsigned int* __restrict__ flags, int world,
+                               const unsigned int* __restrict__ epoch_counter, int M, int N,
+                               const float* __restrict__ w_scale, const __half* __restrict__ bias,
+                               __half* __restrict__ y, int* error_word) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const unsigned int epoch = *epoch_counter;           // advanced by this rank's signal kernel before this launch
+  if (threadIdx.x < world) {
+    const unsigned int* f = flags + threadIdx.x;
+    const uint64_t t0 = ep_timer_ns();
+    for (unsigned int it = 0;; ++it) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (static_cast<int>(v - epoch) >= 0) break;
+      if ((it & 0xFF) == 0xFF && ep_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, report, write nothing
+        s_ok = 0;
+        if (error_word) atomicExch(error_word, 5);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int quads = N >> 2;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += gridDim.x * blockDim.x) {
+    const int m = i / quads, n = (i - m * quads) << 2;
+    const float4 sw = *reinterpret_cast<const float4*>(w_scale + n);
+    // all ranks' loads are issued before the first add: one NVLink round trip, not one per rank
+    int4 a[kMaxRanks];
+    float sx[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < world) {
+        a[r] = *reinterpret_cast<const int4*>(static_cast<const int*>(peers.acc[r]) + (size_t)m * N + n);
+        sx[r] = static_cast<const float*>(peers.xscale[r])[m];
+      }
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < world) {
+        sum.x = __fadd_rn(sum.x, __fmul_rn(__fmul_rn(static_cast<float>(a[r].x), sx[r]), sw.x));
+        sum.y = __fadd_rn(sum.y, __fmul_rn(__fmul_rn(static_cast<float>(a[r].y), sx[r]), sw.y));
+        sum.z = __fadd_rn(sum.z, __fmul_rn(__fmul_rn(static_cast<float>(a[r].z), sx[r]), sw.z));
+        sum.w = __fadd_rn(sum.w, __fmul_rn(__fmul_rn(static_cast<float>(a[r].w), sx[r]), sw.w));
+      }
+    if (bias) {
+      sum.x = __fadd_rn(sum.x, __half2float(bias[n])); sum.y = __fadd_rn(sum.y, __half2float(bias[n + 1]));
+      sum.z = __fadd_rn(sum.z, __half2float(bias[n + 2])); sum.w = __fadd_rn(sum.w, __half2float(bias[n + 3]));
+    }
+    const __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
+    uint2 out;
+    out.x = *reinterpret_cast<const uint32_t*>(&lo);
+    out.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(y + (size_t)m * N + n) = out;
+  }
+}
+
+extern "C" int mp_peer_signal(const void* const* peer_flag_ptrs, int world, int rank, void* epoch_counter_u32,
+                              mp_stream_t stream) {
+  PeerPtrs pf;
+  int rc = fill_peers(pf, peer_flag_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (rank < 0 || rank >= world || !epoch_counter_u32) return MP_ERR_INVALID_ARG;
+  peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, world, rank,
+                                                                     static_cast<unsigned int*>(epoch_counter_u32));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_w8a8_rowparallel_finish(const void* const* peer_acc_i32, const void* const* peer_xscale_f32,
+                                          const void* flags_u32, int world, const void* epoch_counter_u32, int M,
+                                          int N, const void* w_scale_f32, const void* bias_f16, void* y_f16,
+                                          int* error_word, mp_stream_t stream) {
+  if (!peer_acc_i32 || !peer_xscale_f32 || !flags_u32 || !epoch_counter_u32 || !w_scale_f32 || !y_f16 || world < 1 ||
+      world > kMaxRanks || M <= 0 || N <= 0)
+    return MP_ERR_INVALID_ARG;
+  if (N % 4 != 0) return MP_ERR_UNSUPPORTED;
+  PeerPair pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_acc_i32[r] || !peer_xscale_f32[r]) return MP_ERR_INVALID_ARG;
+    if (!aligned(peer_acc_i32[r], 16)) return MP_ERR_ALIGNMENT;
+    pp.acc[r] = peer_acc_i32[r];
+    pp.xscale[r] = peer_xscale_f32[r];
+  }
+  if (!aligned(w_scale_f32, 16) || !aligned(y_f16, 8)) return MP_ERR_ALIGNMENT;
+  long long blocks = ((long long)M * (N / 4) + 255) / 256;
+  if (blocks > 4 * kSmCount) blocks = 4 * kSmCount;
+  w8a8_rowparallel_finish_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pp, static_cast<const unsigned int*>(flags_u32), world, static_cast<const unsigned int*>(epoch_counter_u32), M, N,
+      static_cast<const float*>(w_scale_f32), static_cast<const __half*>(bias_f16), static_cast<__half*>(y_f16),
+      error_word);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
 extern "C" size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows) {
   const int max_tiles = capacity_rows / kEpTile;
   const size_t std_ints = (size_t)3 * num_local_experts + 2 + max_tiles;
@@ -239,7 +362,7 @@ extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const*
   if (rc != MP_OK) return rc;
   if (!xplan_i32 || !q_sorted_i8 || !scale_sorted_f32 || H <= 0 || H % 16 != 0) return MP_ERR_INVALID_ARG;
   const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
-  ep_pull_kernel<<<4 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_pull_kernel<<<16 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pq, ps, static_cast<const int*>(xplan_i32), world, num_local_experts, ext, H / 16,
       static_cast<uint4*>(q_sorted_i8), static_cast<float*>(scale_sorted_f32));
   MP_LAUNCH_CHECK();
@@ -253,7 +376,7 @@ extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, i
   if (rc != MP_OK) return rc;
   if (!d_sorted_f16 || !xplan_i32 || H <= 0 || H % 8 != 0) return MP_ERR_INVALID_ARG;
   const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
-  ep_push_kernel<<<4 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_push_kernel<<<16 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(d_sorted_f16), static_cast<const int*>(xplan_i32), world, num_local_experts, ext,
       H / 8, pb);
   MP_LAUNCH_CHECK();

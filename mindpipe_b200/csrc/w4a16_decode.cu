@@ -586,11 +586,15 @@ rowparallel_finish_kernel(PeerPartials partial, const unsigned int* __restrict__
   const int quads = N >> 2;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += gridDim.x * blockDim.x) {
     const int m = i / quads, n = (i - m * quads) << 2;
+    // all ranks' loads are issued before the first add: one NVLink round trip, not one per rank
+    float4 v[kMaxPeerRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxPeerRanks; ++r)
+      if (r < world) v[r] = *reinterpret_cast<const float4*>(src[r] + (size_t)m * N + n);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = *reinterpret_cast<const float4*>(src[r] + (size_t)m * N + n);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
+#pragma unroll
+    for (int r = 0; r < kMaxPeerRanks; ++r)
+      if (r < world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
     if (bias) {
       acc.x += h2f(bias[n]); acc.y += h2f(bias[n + 1]); acc.z += h2f(bias[n + 2]); acc.w += h2f(bias[n + 3]);
     }

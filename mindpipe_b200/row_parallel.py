@@ -146,3 +146,108 @@ class RowParallelW4A16Linear(torch.nn.Module):
         if self.bias is not None:
             y = y + self.bias.to(torch.float32)
         return y.to(torch.float16)
+
+
+class RowParallelW8A8Linear(torch.nn.Module):
+    """W8A8 linear sharded by input features, the role of the runtime's fused "int8 matmul + all-reduce"
+    (``npu_mm_all_reduce_base``, acceleration/runtime_patches/vllm_ascend.patch:1428-1449).
+
+    Rank ``r`` holds ``weight[:, K_r]`` (int8 ``[N, K/P]``) and the per-channel ``weight_scale[N]`` of the
+    whole weight (the same on every rank, as stored in a W8A8 checkpoint);
+    ``forward(x_local)`` takes ``x[:, K_r]`` (fp16), quantises it per token *on this rank* (each rank has
+    its own per-token scales, as in the runtime op), multiplies into raw int32 accumulators that live
+    in peer-mapped memory, raises an arrival word on the peers, and a finish kernel on every rank reads all
+    accumulators and token scales over NVLink and adds the dequantised partial products in rank order:
+    bit-identical outputs on all ranks, no NCCL call or host synchronisation on the path.
+    """
+
+    def __init__(self, weight_i8, weight_scale, bias=None, group=None, max_rows: int = 256):
+        super().__init__()
+        import torch.distributed._symmetric_memory as symm
+        if weight_i8.dtype != torch.int8 or weight_i8.dim() != 2:
+            raise TypeError("weight_i8 must be an int8 [N, K_local] tensor")
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.weight = weight_i8.contiguous()
+        self.weight_scale = weight_scale.detach().flatten().to(torch.float32).contiguous()
+        self.bias = None if bias is None else bias.detach().to(torch.float16).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        if self.weight_scale.numel() != self.out_features:
+            raise ValueError("weight_scale must have one entry per output feature")
+        self.max_rows = int(max_rows)
+        dev = self.weight.device
+        al = lambda n: (n + 255) // 256 * 256
+        self.acc_bytes = al(self.max_rows * self.out_features * 4)
+        self.scale_bytes = al(self.max_rows * 4)
+        self.off_acc = [256, 256 + self.acc_bytes + self.scale_bytes]                # two (acc | xscale) buffers
+        self.off_scale = [o + self.acc_bytes for o in self.off_acc]
+        self.buf = symm.empty(256 + 2 * (self.acc_bytes + self.scale_bytes), dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize(dev)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        dist.barrier(self.group)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        mk = lambda off: (ctypes.c_void_p * self.world)(*[b + off for b in bases])
+        self.p_flags = mk(0)
+        self.p_acc = [mk(o) for o in self.off_acc]
+        self.p_scale = [mk(o) for o in self.off_scale]
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)     # calls completed (advanced on the device)
+        self.calls = 0
+
+    @staticmethod
+    def from_float(linear: torch.nn.Linear, group=None, **kw):
+        """Quantise the FULL fp16 weight per output channel (the a8 producer: fp16 arithmetic) and keep
+        this rank's column slice.  The per-channel scale comes from the whole row, so it is the same
+        on every rank -- as in a W8A8 checkpoint, whose ``weight_scale`` is stored once per channel."""
+        from . import ops
+        g = dist.group.WORLD if group is None else group
+        world, rank = dist.get_world_size(g), dist.get_rank(g)
+        q, s, _ = ops.act_quant_per_token(linear.weight.detach().contiguous())
+        k = q.shape[1]
+        if k % world:
+            raise ValueError(f"{k} input features do not divide over {world} ranks")
+        lo, hi = rank * k // world, (rank + 1) * k // world
+        return RowParallelW8A8Linear(q[:, lo:hi].contiguous(), s, linear.bias, g, **kw)
+
+    @torch.no_grad()
+    def forward(self, x_local):
+        from . import _lib, ops
+        lib = _lib.load()
+        x2 = x_local.reshape(-1, x_local.shape[-1]).contiguous()
+        m, k_loc = x2.shape
+        if m > self.max_rows or k_loc != self.in_features or x2.dtype != torch.float16:
+            raise ValueError(f"x_local must be fp16 [<= {self.max_rows}, {self.in_features}], got {tuple(x2.shape)}")
+        par = self.calls & 1                         # a peer may still read call n while this rank computes call n+1
+        self.calls += 1
+        stream = torch.cuda.current_stream().cuda_stream
+        base = self.buf.data_ptr()
+        acc_ptr, scale_ptr = base + self.off_acc[par], base + self.off_scale[par]
+        qx = torch.empty((m, k_loc), dtype=torch.int8, device=x2.device)
+        y = torch.empty((m, self.out_features), dtype=torch.float16, device=x2.device)
+        err = ops._error_word(x2.device).data_ptr()
+        _lib.check(lib.mp_act_quant_per_token(x2.data_ptr(), m, k_loc, qx.data_ptr(), scale_ptr, None, stream),
+                   "act_quant_per_token", M=m, K=k_loc)
+        _lib.check(lib.mp_w8a8_gemm_i32(qx.data_ptr(), self.weight.data_ptr(), acc_ptr, m, self.out_features, k_loc, err,
+                                        stream), "w8a8_gemm_i32", M=m, N=self.out_features, K=k_loc)
+        _lib.check(lib.mp_peer_signal(self.p_flags, self.world, self.rank, self.epoch.data_ptr(), stream), "peer_signal")
+        _lib.check(lib.mp_w8a8_rowparallel_finish(self.p_acc[par], self.p_scale[par], base, self.world,
+                                                  self.epoch.data_ptr(), m, self.out_features,
+                                                  self.weight_scale.data_ptr(),
+                                                  None if self.bias is None else self.bias.data_ptr(), y.data_ptr(), err,
+                                                  stream), "w8a8_rowparallel_finish", M=m, N=self.out_features)
+        return y.reshape(*x_local.shape[:-1], self.out_features)
+
+    @torch.no_grad()
+    def forward_nccl(self, x_local):
+        """Per-rank W8A8 linear in fp32, then ``all_reduce`` (sum order is the library's)."""
+        from . import ops
+        x2 = x_local.reshape(-1, x_local.shape[-1]).contiguous()
+        qx, sx, _ = ops.act_quant_per_token(x2)
+        acc = ops.w8a8_gemm_i32(qx, self.weight)
+        y = acc.to(torch.float32) * sx[:, None] * self.weight_scale[None, :]
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        if self.bias is not None:
+            y = y + self.bias.to(torch.float32)
+        return y.to(torch.float16).reshape(*x_local.shape[:-1], self.out_features)

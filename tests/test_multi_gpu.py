@@ -4,6 +4,7 @@ import datetime
 import os
 import socket
 
+import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
@@ -109,7 +110,46 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         ops.check_device_errors()
         ok_row = ok_row and torch.equal(y_graph, y_eager)
-        ret[rank] = (bool(ok_moe), bool(ok_col), bool(ok_row))
+        # ---- row-parallel W8A8 (per-rank token scales, int32 accumulators summed over NVLink) ----
+        from mindpipe_b200.row_parallel import RowParallelW8A8Linear
+        from oracle import pseudo_quant as O
+        n8, k8 = 512, 2048
+        w8 = synth.normal_weight(n8, k8, seed=4)
+        b8 = (synth.normal_activation(1, n8, seed=4, index=5)[0] * 0.1).to(torch.float16)
+        k_lo, k_hi = rank * k8 // world, (rank + 1) * k8 // world
+        full8 = torch.nn.Linear(k8, n8, bias=True).half().to(dev)
+        full8.weight.data.copy_(w8)
+        full8.bias.data.copy_(b8)
+        rp8 = RowParallelW8A8Linear.from_float(full8, max_rows=300)      # full-row channel scales, column shard
+        _, qw_full, sw_full = O.absmax_quant_last_dim(w8.numpy())
+        ok_row8 = True
+        for i, m8 in enumerate((1, 16, 300, 64)):
+            x8 = synth.outlier_activation(m8, k8, seed=5, index=i)
+            y8 = rp8(x8[:, k_lo:k_hi].to(dev).contiguous())
+            ops.check_device_errors()
+            # oracle: the reference's per-rank pieces (per-token int8 activations, per-channel int8 weights,
+            # int32 accumulate, scale) summed over the shards in rank order
+            want = np.zeros((m8, n8), np.float32)
+            for r in range(world):
+                a, b = r * k8 // world, (r + 1) * k8 // world
+                _, qx_r, sx_r = O.absmax_quant_last_dim(x8[:, a:b].numpy())
+                acc_r = O.int32_accumulate(qx_r, np.ascontiguousarray(qw_full[:, a:b])).astype(np.float32)
+                want = want + (acc_r * sx_r.astype(np.float32).reshape(-1, 1)) * sw_full.astype(np.float32).reshape(1, -1)
+            want = (want + b8.numpy().astype(np.float32)).astype(np.float16)
+            exact = np.array_equal(y8.cpu().numpy().view(np.uint16), want.view(np.uint16))
+            everyone = [torch.empty_like(y8) for _ in range(world)]
+            dist.all_gather(everyone, y8)
+            same = all(torch.equal(e, everyone[0]) for e in everyone)
+            # against the unquantised linear this is per-token int8 with x20 outlier channels: a sanity bound only
+            full = (x8.float() @ w8.float().T + b8.float()).to(dev)
+            sane = ((y8.float() - full).norm() / full.norm()).item() <= 0.15
+            y8n = rp8.forward_nccl(x8[:, k_lo:k_hi].to(dev).contiguous())
+            close = ((y8n.float() - y8.float()).norm() / full.norm()).item() <= 2e-3
+            if not (exact and same and sane and close):
+                print(f"rank {rank} row-parallel W8A8 m={m8}: exact={exact} same={same} sane={sane} close={close}",
+                      flush=True)
+            ok_row8 = ok_row8 and exact and same and sane and close
+        ret[rank] = (bool(ok_moe), bool(ok_col), bool(ok_row), bool(ok_row8))
     finally:
         dist.destroy_process_group()
 
@@ -122,4 +162,4 @@ def test_expert_parallel_column_parallel_and_row_parallel_match_single_gpu():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert all(v == (True, True, True) for v in dict(ret).values()), dict(ret)
+    assert all(v == (True, True, True, True) for v in dict(ret).values()), dict(ret)
