@@ -355,6 +355,19 @@ int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, c
                         const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
                         const void* w2_scale_f32, void* d_out_f16, void* workspace,
                         size_t workspace_bytes, int* error_word, mp_stream_t stream);
+/*
+ * Expert-parallel form of the stage: the second GEMM's epilogue stores every
+ * result row straight into the result buffer of the rank the token came from
+ * (peer stores over NVLink; peer_back_ptrs[s] = rank s's buffer [its routed
+ * rows][H] fp16), located through the extended plan mp_moe_ep_plan wrote, so
+ * there is no sorted result buffer and no separate return kernel.
+ */
+int mp_moe_expert_stage_scatter(const void* routed_q_i8, const void* routed_scale_f32,
+                                const void* xplan_i32, int capacity_rows, int H, int I,
+                                int num_local_experts, int world, const void* w13_q_i8,
+                                const void* w13_scale_f32, const void* w2_q_i8, const void* w2_scale_f32,
+                                void* const* peer_back_ptrs, void* workspace, size_t workspace_bytes,
+                                int* error_word, mp_stream_t stream);
 
 /*
  * out[t] = sum_j f16(d[dest_row(t,j)] * w[t,j]) in fp16, experts in ascending

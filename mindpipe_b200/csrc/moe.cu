@@ -289,18 +289,17 @@ extern "C" size_t mp_moe_expert_stage_workspace_bytes(int padded_rows, int I) {
   return align256(P * I * 2) + align256(P * 4) + align256(P * I) + align256(P * 4);
 }
 
-extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
-                                   int padded_rows, int H, int I, int num_local_experts,
-                                   const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
-                                   const void* w2_scale_f32, void* d_out_f16, void* workspace,
-                                   size_t workspace_bytes, int* error_word, mp_stream_t stream) {
+static int expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32, int padded_rows,
+                        int H, int I, int num_local_experts, const void* w13_q_i8, const void* w13_scale_f32,
+                        const void* w2_q_i8, const void* w2_scale_f32, void* d_out_f16, const RowScatter* scatter,
+                        void* workspace, size_t workspace_bytes, int* error_word, mp_stream_t stream) {
   if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || !w2_q_i8 || !w2_scale_f32 ||
-      !d_out_f16 || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
+      (!d_out_f16 && !scatter) || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
     return MP_ERR_INVALID_ARG;
   if (padded_rows % kMoeSegmentAlign != 0 || H % 16 != 0 || I % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
   if (!workspace || workspace_bytes < mp_moe_expert_stage_workspace_bytes(padded_rows, I)) return MP_ERR_WORKSPACE;
   if (!aligned(workspace, 256) || !aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16) || !aligned(w2_q_i8, 16) ||
-      !aligned(d_out_f16, 16))
+      (d_out_f16 && !aligned(d_out_f16, 16)))
     return MP_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int E = num_local_experts;
@@ -320,7 +319,42 @@ extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_s
   moe_requant_kernel<<<padded_rows, 256, 0, st>>>(h, absmax, I, num_tiles, q2, scale2);
   MP_LAUNCH_CHECK();
   return launch_moe_gemm2(q2, scale2, w2_q_i8, static_cast<const float*>(w2_scale_f32), padded_rows, I, H, E,
-                          num_tiles, tile_expert, d_out_f16, error_word, st);
+                          num_tiles, tile_expert, d_out_f16, error_word, st, scatter);
+}
+
+extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
+                                   int padded_rows, int H, int I, int num_local_experts,
+                                   const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
+                                   const void* w2_scale_f32, void* d_out_f16, void* workspace,
+                                   size_t workspace_bytes, int* error_word, mp_stream_t stream) {
+  return expert_stage(routed_q_i8, routed_scale_f32, plan_i32, padded_rows, H, I, num_local_experts, w13_q_i8,
+                      w13_scale_f32, w2_q_i8, w2_scale_f32, d_out_f16, nullptr, workspace, workspace_bytes, error_word,
+                      stream);
+}
+
+// Expert-parallel form: the second GEMM's epilogue stores every result row straight into the result buffer
+// of the rank the token came from (peer stores over NVLink, located through the extended plan), so no
+// sorted result buffer and no separate return kernel exist.  xplan_i32 is the plan mp_moe_ep_plan wrote
+// (it begins with the standard plan); capacity_rows as given there.
+extern "C" int mp_moe_expert_stage_scatter(const void* routed_q_i8, const void* routed_scale_f32, const void* xplan_i32,
+                                           int capacity_rows, int H, int I, int num_local_experts, int world,
+                                           const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,
+                                           const void* w2_scale_f32, void* const* peer_back_ptrs, void* workspace,
+                                           size_t workspace_bytes, int* error_word, mp_stream_t stream) {
+  if (!peer_back_ptrs || world < 1 || world > kMoeMaxRanks || !xplan_i32) return MP_ERR_INVALID_ARG;
+  RowScatter sc{};
+  sc.xplan = static_cast<const int*>(xplan_i32);
+  sc.world = world;
+  sc.e_loc = num_local_experts;
+  sc.ext = 3 * num_local_experts + 2 + capacity_rows / kTileRows;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_back_ptrs[r]) return MP_ERR_INVALID_ARG;
+    if (!aligned(peer_back_ptrs[r], 16)) return MP_ERR_ALIGNMENT;
+    sc.back[r] = peer_back_ptrs[r];
+  }
+  return expert_stage(routed_q_i8, routed_scale_f32, xplan_i32, capacity_rows, H, I, num_local_experts, w13_q_i8,
+                      w13_scale_f32, w2_q_i8, w2_scale_f32, nullptr, &sc, workspace, workspace_bytes, error_word,
+                      stream);
 }
 
 extern "C" int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,

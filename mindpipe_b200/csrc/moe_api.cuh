@@ -14,6 +14,34 @@ __host__ __device__ constexpr int moe_segment_tiles(int rows) {
   return (rows + kMoeSegmentAlign - 1) / kMoeSegmentAlign * (kMoeSegmentAlign / kMoeTileRows);
 }
 
+// Expert-parallel return path fused into the second GEMM: where does expert-sorted row i go home to?
+// xplan is the receiving rank's extended plan (see ep_plan_kernel in moe_ep.cu), back[s] rank s's result
+// buffer ([rows of rank s's routed buffer][H] fp16, peer-mapped).
+constexpr int kMoeMaxRanks = 16;
+struct RowScatter {
+  const int* xplan;          // null: no scatter (rows are stored at their sorted position)
+  int world, e_loc, ext;
+  void* back[kMoeMaxRanks];
+};
+
+// Which (source rank, row of that rank's routed buffer) does sorted row i hold?  false = padding.
+__device__ __forceinline__ bool ep_locate(const int* xplan, int world, int e_loc, int ext, int i, int& s_out,
+                                          int& src_row) {
+  const int* seg = xplan + 2 * e_loc;
+  const int* cum = xplan + ext;
+  const int* src_seg = xplan + ext + e_loc * (world + 1);
+  if (i >= seg[e_loc]) return false;
+  int e = 0;
+  while (e + 1 < e_loc && i >= seg[e + 1]) ++e;
+  const int j = i - seg[e];
+  if (j >= cum[e * (world + 1) + world]) return false;
+  int s = 0;
+  while (s + 1 < world && j >= cum[e * (world + 1) + s + 1]) ++s;
+  s_out = s;
+  src_row = src_seg[e * world + s] + (j - cum[e * (world + 1) + s]);
+  return true;
+}
+
 // h[r, n] = f16(silu(f16(gate)) * f16(up)) for the expert-sorted int8 rows, plus per-row max |h|.
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
@@ -22,6 +50,6 @@ int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, con
 // d[r, :] = f16(acc * scale2[r] * w2_scale[e, :]) for the re-quantised rows.
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
                      int I, int H, int E, const int* num_tiles_dev, const int* tile_expert, void* d_out,
-                     int* error_word, cudaStream_t st);
+                     int* error_word, cudaStream_t st, const RowScatter* scatter = nullptr);
 
 }  // namespace mp

@@ -123,23 +123,6 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
   *num_tiles = tiles;
 }
 
-// Which (expert, source rank, row inside the source segment) does sorted row i hold?  -1 = padding.
-__device__ __forceinline__ bool ep_locate(const int* xplan, int world, int e_loc, int ext, int i, int& s_out,
-                                          int& src_row) {
-  const int* seg = xplan + 2 * e_loc;
-  const int* cum = xplan + ext;
-  const int* src_seg = xplan + ext + e_loc * (world + 1);
-  int e = 0;
-  while (e + 1 < e_loc && i >= seg[e + 1]) ++e;
-  const int j = i - seg[e];
-  if (j >= cum[e * (world + 1) + world]) return false;
-  int s = 0;
-  while (s + 1 < world && j >= cum[e * (world + 1) + s + 1]) ++s;
-  s_out = s;
-  src_row = src_seg[e * world + s] + (j - cum[e * (world + 1) + s]);
-  return true;
-}
-
 // Sorted row i <- peer row (int8 codes and fp32 scale).  Blocks stride over the rows in use.
 __global__ void __launch_bounds__(256)
 ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xplan, int world, int e_loc, int ext,

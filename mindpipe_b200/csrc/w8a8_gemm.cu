@@ -24,6 +24,7 @@
 // word, lets its copies land, frees its TMEM and returns.
 #include "common.cuh"
 #include "tc.cuh"
+#include "moe_api.cuh"
 
 namespace mp {
 
@@ -41,6 +42,7 @@ struct GemmParams {
   int k_split;                 // > 1: a tile's K range is cut into this many work items of kb_per_split k-blocks,
   int kb_per_split;            //      whose raw int32 partial tiles go to `partial` ([k_split][M][N])
   int* partial;
+  RowScatter scatter;          // expert-parallel GEMM2: rows are stored at home (peer memory), see moe_api.cuh
   int group_m;                 // tile order: groups of this many M tiles are swept across all of N before the next group
   const int* m_tiles_dev;      // grouped: number of 128-row tiles in use (device side)
   const int* tile_expert;      // grouped: expert of each 128-row tile
@@ -286,7 +288,16 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag))) break;
       tcgen05_fence_after();
       const int row = m_tile * kRowsPerTile + static_cast<int>(rank) * kBM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      bool row_ok = row < p.M;
+      // where this row's fp16 output goes: its sorted position, or (expert-parallel GEMM2) straight home
+      // into the source rank's result buffer over NVLink; padding rows are not stored at all
+      __half* out_row = static_cast<__half*>(p.out) + (size_t)row * p.N;
+      if (EPI == EPI_F16 && p.scatter.xplan) {
+        int home_rank = 0, home_row = 0;
+        row_ok = row_ok && ep_locate(p.scatter.xplan, p.scatter.world, p.scatter.e_loc, p.scatter.ext, row, home_rank,
+                                     home_row);
+        out_row = static_cast<__half*>(p.scatter.back[home_rank]) + (size_t)home_row * p.N;
+      }
       const float sa = (EPI != EPI_I32 && row_ok) ? p.a_scale[row] : 0.0f;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       if (EPI == EPI_SWIGLU) {
@@ -387,7 +398,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               hp[j >> 1] = h2_as_u32(__floats2half2_rn(v0, v1));
             }
             if (row_ok) {
-              __half* dst = static_cast<__half*>(p.out) + (size_t)row * p.N + n0 + c0;
+              __half* dst = out_row + n0 + c0;
               if (n0 + c0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
                 for (int v = 0; v < 4; ++v)
@@ -514,6 +525,7 @@ w8a8_splitk_reduce_kernel(const int* __restrict__ partial, int k_split, int M, i
 
 struct GemmCall {
   int k_split = 1; int* partial = nullptr;
+  const RowScatter* scatter = nullptr;
   const float* a_zero = nullptr; const int* a_rowsum = nullptr; const float* b_zero = nullptr; const int* b_rowsum = nullptr;
   const void* a; const void* b;
   int M, N, K;
@@ -549,6 +561,7 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.k_split = c.k_split > 1 ? c.k_split : 1;
   p.kb_per_split = (p.k_blocks + p.k_split - 1) / p.k_split;
   p.partial = c.partial;
+  if (c.scatter) p.scatter = *c.scatter;
   p.a_zero = c.a_zero; p.a_rowsum = c.a_rowsum; p.b_zero = c.b_zero; p.b_rowsum = c.b_rowsum;
   auto kern = w8a8_gemm_kernel<BN, EPI, PAIR>;
   static thread_local int configured_device = -1;
@@ -638,12 +651,13 @@ int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, con
 
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
                      int I, int H, int E, const int* num_tiles_dev, const int* tile_expert, void* d_out,
-                     int* error_word, cudaStream_t st) {
+                     int* error_word, cudaStream_t st, const RowScatter* scatter) {
   GemmCall c{};
   c.a = q2; c.b = w2_q; c.M = padded_rows; c.N = H; c.K = I; c.a_rows = padded_rows; c.b_rows_total = E * H;
   c.a_scale = scale2; c.b_scale = w2_scale; c.out = d_out;
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = H;
   c.error_word = error_word;
+  c.scatter = scatter;
   return launch_gemm<256, EPI_F16, true>(c, st);
 }
 

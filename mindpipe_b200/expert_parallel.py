@@ -177,19 +177,23 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
     """Expert-parallel W8A8 MoE whose dispatch and return run over NVLink peer memory, driven
     entirely from the device: no row count ever visits the host and the barrier epochs live in
     device memory, so a forward is a fixed sequence of stream-ordered launches (route -> barrier ->
-    plan -> pull -> expert stage -> push -> barrier -> combine) that can be captured in a CUDA graph
-    and replayed (every rank must replay it the same number of times).
+    plan -> pull -> expert stage, whose second GEMM stores the results at home -> barrier ->
+    combine) that can be captured in a CUDA graph and replayed (every rank must replay it the same
+    number of times).
 
     Each rank keeps its routing plan, routed int8 rows, their scales and a result buffer in one
     symmetric allocation that every peer maps (``torch.distributed._symmetric_memory``).  Peers
-    *pull* the rows their experts own and *push* the results back to the row's original position.
+    *pull* the rows their experts own; the second expert GEMM *stores* each result row at the row's
+    original position in the source rank's buffer from its epilogue.
     ``max_tokens_per_rank`` fixes the buffer sizes; the expert-sorted buffers are sized for the
     worst case (every token of every rank routed to this rank).
     """
 
-    def __init__(self, experts, num_experts: int, max_tokens_per_rank: int, top_k: int = 2, group=None):
+    def __init__(self, experts, num_experts: int, max_tokens_per_rank: int, top_k: int = 2, group=None,
+                 fuse_return: bool = True):
         super().__init__()
         import torch.distributed._symmetric_memory as symm
+        self.fuse_return = bool(fuse_return)     # second GEMM stores results at home instead of a push kernel
         from . import _lib
         self.experts = experts
         self.group = dist.group.WORLD if group is None else group
@@ -270,10 +274,21 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
                                       self.sorted_cap, h, self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), stream),
                    "moe_ep_pull")
         ex = self.experts
-        d_sorted = ops.moe_expert_stage(self.q_sorted, self.s_sorted, self.xplan, self.e_loc, ex.gate_up_proj,
-                                        ex.gate_up_proj_scale, ex.down_proj, ex.down_proj_scale)
-        _lib.check(lib.mp_moe_ep_push(d_sorted.data_ptr(), self.xplan.data_ptr(), self.world, self.e_loc,
-                                      self.sorted_cap, h, self.p_back, stream), "moe_ep_push")
+        if self.fuse_return:
+            # both grouped GEMMs; the second one's epilogue stores each result row at its original position in
+            # the source rank's buffer (peer stores over NVLink): the return path costs no kernel of its own
+            nbytes = lib.mp_moe_expert_stage_workspace_bytes(self.sorted_cap, self.inter)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=hs.device)
+            _lib.check(lib.mp_moe_expert_stage_scatter(
+                self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), self.xplan.data_ptr(), self.sorted_cap, h,
+                self.inter, self.e_loc, self.world, ex.gate_up_proj.data_ptr(), ex.gate_up_proj_scale.data_ptr(),
+                ex.down_proj.data_ptr(), ex.down_proj_scale.data_ptr(), self.p_back, ws.data_ptr(), nbytes,
+                ops._error_word(hs.device).data_ptr(), stream), "moe_expert_stage_scatter")
+        else:
+            d_sorted = ops.moe_expert_stage(self.q_sorted, self.s_sorted, self.xplan, self.e_loc, ex.gate_up_proj,
+                                            ex.gate_up_proj_scale, ex.down_proj, ex.down_proj_scale)
+            _lib.check(lib.mp_moe_ep_push(d_sorted.data_ptr(), self.xplan.data_ptr(), self.world, self.e_loc,
+                                          self.sorted_cap, h, self.p_back, stream), "moe_ep_push")
         self._barrier()                                    # every result row has landed at home
         out = ops.moe_combine(self.back, routing.dest_row, ids, w, t)
         return out.reshape(shape)

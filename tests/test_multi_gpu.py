@@ -50,7 +50,7 @@ def _worker(rank, world, port, ret):
         ok_moe = torch.equal(out, ref[a:b])           # same kernels, same rows: identical
         # the device-driven exchange over symmetric memory gives the same rows again
         from mindpipe_b200.expert_parallel import SymmetricExpertParallelMoE
-        sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7)
+        sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, fuse_return=False)
         for _ in range(3):                            # repeated forwards reuse the symmetric buffers
             out2 = sym(hs[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
         ops.check_device_errors()
@@ -68,6 +68,12 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         ops.check_device_errors()
         ok_moe = ok_moe and torch.equal(out3, ref[a:b])
+        # return path fused into the second GEMM's epilogue (rows stored at home over NVLink)
+        sym2 = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, fuse_return=True)
+        for _ in range(3):
+            out4 = sym2(xa, ia, wa)
+        ops.check_device_errors()
+        ok_moe = ok_moe and torch.equal(out4, ref[a:b])
         # ---- column-parallel W4A16 vs single GPU ----
         n, k = 1024, 2048
         wt = synth.normal_weight(n, k, seed=2).to(dev)
