@@ -297,7 +297,8 @@ def measure_moe(world, rank, dev, dist, iters=10):
         from mindpipe_b200.expert_parallel import ExpertParallelMoE, SymmetricExpertParallelMoE
         try:
             layer = SymmetricExpertParallelMoE(mod, shape.num_experts, max_tokens_per_rank=t_loc, top_k=shape.top_k)
-            exchange = "peer-memory pull/push kernels (symmetric memory, no host sync)"
+            exchange = ("peer-memory pull kernel, results stored at home by the second GEMM's epilogue"
+                        if layer.fuse_return else "peer-memory pull/push kernels") + " (symmetric memory, no host sync)"
         except Exception as err:      # no peer mapping available: NCCL all-to-all with host-side split sizes
             layer = ExpertParallelMoE(mod, shape.num_experts)
             exchange = f"nccl all_to_all_single ({type(err).__name__})"
