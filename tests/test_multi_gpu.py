@@ -50,7 +50,7 @@ def _worker(rank, world, port, ret):
         ok_moe = torch.equal(out, ref[a:b])           # same kernels, same rows: identical
         # the device-driven exchange over symmetric memory gives the same rows again
         from mindpipe_b200.expert_parallel import SymmetricExpertParallelMoE
-        sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, fuse_return=False)
+        sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7)
         for _ in range(3):                            # repeated forwards reuse the symmetric buffers
             out2 = sym(hs[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
         ops.check_device_errors()
