@@ -201,6 +201,32 @@ def test_errors_are_loud():
                                 torch.zeros(1, 8, 2, dtype=torch.float16, device="cuda"))
 
 
+def test_split_k_scratch_errors_are_loud():
+    """A scratch buffer that is too small is refused with the "workspace" status, never written past."""
+    from mindpipe_b200 import _lib, ops
+    lib = _lib.load()
+    m, n, k = 64, 512, 2048
+    need = lib.mp_w4a16_prefill_workspace_bytes(m, n, k)
+    assert need > 0
+    w = synth.normal_weight(n, k, seed=9, index=0).cuda()
+    packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+    sz = ops.w4a16_prepare(scale, zero, k)
+    x = synth.normal_activation(m, k, seed=9, index=1).cuda()
+    with pytest.raises(_lib.MindPipeKernelError, match="workspace"):
+        ops.w4a16_linear_prefill(x, packed, sz, workspace=torch.zeros(need - 16, dtype=torch.uint8, device="cuda"))
+    y = ops.w4a16_linear_prefill(x, packed, sz, workspace=torch.zeros(need, dtype=torch.uint8, device="cuda"))
+    assert torch.equal(y, ops.w4a16_linear_prefill(x, packed, sz))
+    # int8 GEMM: same contract
+    need8 = lib.mp_w8a8_gemm_workspace_bytes(16, 4096, 4096)
+    assert need8 > 0
+    qx = torch.zeros((16, 4096), dtype=torch.int8, device="cuda")
+    qw = torch.zeros((4096, 4096), dtype=torch.int8, device="cuda")
+    with pytest.raises(_lib.MindPipeKernelError, match="workspace"):
+        ops.w8a8_gemm(qx, torch.ones(16, device="cuda"), qw, torch.ones(4096, device="cuda"),
+                      workspace=torch.zeros(need8 // 2, dtype=torch.uint8, device="cuda"))
+    ops.check_device_errors()
+
+
 # ---------------------------------------------------------------- prefill (tcgen05) kernel
 def _prefill_case(n, k, m, group=128, seed=0, bias=False, rows=None):
     from mindpipe_b200 import ops
