@@ -406,13 +406,19 @@ def run_ours(args, rank, world, local_rank):
     _lib.load().mp_set_programmatic_launch(1 if args.pdl else 0)
 
     ws_bytes = max(ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) for _, (n, k) in layer_shapes())
-    ws = ops.new_workspace(ws_bytes, dev)          # the seven linears run back to back on one stream
+    # one scratch buffer per linear: with --fuse 0 --concurrent 1 some of them run side by side
+    ws = {name: ops.new_workspace(ws_bytes, dev) for name, _ in layer_shapes()}
+    umma_names = [name for name, (n, k) in layer_shapes() if ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) > 0]
+    tma_names = [name for name, _ in layer_shapes() if name not in umma_names]
+    kernel_names = " + ".join(
+        f"{kern} ({', '.join(names)})" for kern, names in (("w4a16_decode_umma_kernel", umma_names),
+                                                           ("w4a16_decode_tma_kernel", tma_names)) if names)
     y_dev = {name: torch.empty((M_DECODE, n), dtype=torch.float16, device=dev) for name, (n, k) in layer_shapes()}
 
     side = [torch.cuda.Stream(device=dev) for _ in range(2)]
 
     def launch(name, mod):
-        ops.w4a16_linear_decode(x_dev[name], mod.weight_packed, mod._scale_zero, workspace=ws, out=y_dev[name])
+        ops.w4a16_linear_decode(x_dev[name], mod.weight_packed, mod._scale_zero, workspace=ws[name], out=y_dev[name])
 
     def step(layer):
         """The layer's dependency structure: q, k, v side by side; o; gate, up side by side; down."""
@@ -530,7 +536,7 @@ def run_ours(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_src, "kernel": "w4a16_decode_tma_kernel",
+                         "traffic": traffic, "peak_source": peak_src, "kernel": kernel_names,
                          "launch_bytes_avg": bytes_step / launches_per_step,
                          "launch_us_avg": ms * 1e3 / (args.steps * launches_per_step)},
             "e2e": {"value": e2e_val, "unit": "GB/s",
@@ -623,13 +629,14 @@ def run_suite(args, local_rank):
             for m in (1, 16):
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
+                ws_dec = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, n, k), dev)
                 g = torch.cuda.CUDAGraph()
                 for pk, sz in mods:
-                    ops.w4a16_linear_decode(x, pk, sz, out=y)
+                    ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
                 torch.cuda.synchronize()
                 with torch.cuda.graph(g):
                     for pk, sz in mods:
-                        ops.w4a16_linear_decode(x, pk, sz, out=y)
+                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
                 t = timed(g.replay, 20) / copies
                 b = w4a16_bytes(n, k, m)
                 emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
@@ -746,6 +753,8 @@ def main():
     ap.add_argument("--moe", type=int, default=1, help="also measure the expert-parallel MoE layer (extra key)")
     ap.add_argument("--suite", default="", help="comma list of extra per-kernel lines: decode,prefill,w8a8,moe,all")
     ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
+    ap.add_argument("--decode-kernel", default="default", choices=["default", "auto", "umma", "mma_sync"],
+                    help="kernel behind the M <= 16 decode linears (default: the library's default)")
     ap.add_argument("--decode-shapes", default="", help="restrict the decode suite, e.g. 8192x28672,4096x4096 (NxK)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -757,6 +766,9 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:
+        if args.decode_kernel != "default":
+            from mindpipe_b200 import ops as _ops
+            _ops.set_decode_kernel(args.decode_kernel)
         if not args.suite_only:
             run_ours(args, rank, world, local_rank)
         if args.suite and rank == 0:

@@ -202,6 +202,29 @@ int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, con
 int mp_set_programmatic_launch(int enabled);
 
 /*
+ * Chooses the kernel behind the decode linears for M <= 16 (returns the
+ * previous choice, or MP_ERR_INVALID_ARG).  Both compute F.linear(x, Wdq) of
+ * awq/quantize/quantizer.py:109-130 with fp32 accumulation:
+ *   MP_DECODE_KERNEL_UMMA      tcgen05.mma with the dequantised weights as the
+ *                              tensor-memory operand (a thread expands one
+ *                              weight row and stores it with tcgen05.st)
+ *   MP_DECODE_KERNEL_MMA_SYNC  the mma.sync ring kernel (also the one behind
+ *                              the row-parallel entry points)
+ *   MP_DECODE_KERNEL_AUTO      (default) the tcgen05 kernel for 9..16 tokens on
+ *                              weights of at least 64 MiB packed, the mma.sync
+ *                              kernel otherwise
+ * The tcgen05 kernel divides the (row block, K stage) pairs evenly over a
+ * persistent grid and needs the workspace of mp_w4a16_decode_workspace_bytes
+ * (zero-filled when created, left ready for the next call, not shared by calls
+ * that overlap); without a workspace, and for shapes the chosen kernel does not
+ * take, the call falls through to the other kernels.
+ */
+#define MP_DECODE_KERNEL_MMA_SYNC 0
+#define MP_DECODE_KERNEL_UMMA 1
+#define MP_DECODE_KERNEL_AUTO 2
+int mp_set_decode_kernel(int kind);
+
+/*
  * Synchronously reads (and clears) the flag a decode kernel sets when one of
  * its bounded device-side waits gave up; *value == 0 means none did.  A
  * debugging aid: it synchronises with the device.

@@ -85,6 +85,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait for helper warps (a producer, an MMA issuer): between polls the warp sleeps, so that its
+// polling loop does not compete for issue slots with the warps that have work.  `sleep_ns` bounds the
+// latency this adds to the hand-off.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0x3F) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- CTA pairs (cluster of 2)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -32,7 +32,29 @@ namespace mp {
 int launch_decode_tma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
                       int group, cudaStream_t st, const DecodePush* push = nullptr);
 void set_decode_programmatic_launch(bool on);
+bool decode_programmatic_launch();
 int read_and_clear_decode_error(int* value);
+// tcgen05 kernel for M <= 16 with the weights as the tensor-memory operand (w4a16_decode_umma.cu)
+int launch_decode_umma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
+                       int group, void* workspace, size_t workspace_bytes, cudaStream_t st, bool pdl);
+size_t decode_umma_workspace_bytes();
+
+// Which kernel serves M <= 16: MP_DECODE_KERNEL_UMMA (tcgen05, weights through tensor memory),
+// MP_DECODE_KERNEL_MMA_SYNC (the mma.sync ring kernel) or MP_DECODE_KERNEL_AUTO (by shape).  Shapes the
+// chosen one does not take fall through.
+static int g_decode_kernel = MP_DECODE_KERNEL_AUTO;
+
+// AUTO: the tcgen05 kernel for 9 to 16 tokens (below that the mma.sync kernel's folded scales are cheaper
+// still) on weights of at least 64 MiB packed.  Measured on B200, kernel alone: 28672x8192 1.22x,
+// 8192x28672 1.11x, 22016x4096 1.14x, 12288x4096 1.08x, 8192x8192 1.0x, 4096x11008 0.6x; but inside a
+// back-to-back sequence of 7B-sized linears under programmatic dependent launch the persistent grid
+// overlaps its neighbours less than the mma.sync kernel's short blocks do (71.1 vs 69.5 us per layer
+// set), so the smaller shapes stay with the mma.sync kernel.
+static bool decode_uses_umma(int M, int N, int K) {
+  if (g_decode_kernel == MP_DECODE_KERNEL_UMMA) return true;
+  if (g_decode_kernel != MP_DECODE_KERNEL_AUTO) return false;
+  return M > 8 && (size_t)N * (size_t)K / 2 >= (size_t)64 << 20;
+}
 
 constexpr int kWarpsK = 4;        // warps along K inside a block
 constexpr int kRowGroups = 4;     // 8-row groups per warp -> 32 rows per warp
@@ -487,7 +509,8 @@ using namespace mp;
 
 extern "C" size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split) {
   if (M <= 0 || M > 64 || N <= 0 || K <= 0 || K % kChunk != 0) return 0;
-  if (M <= 16 && k_split <= 0) return 0;     // cluster kernel: reduces through distributed shared memory
+  if (M <= 16 && k_split <= 0)               // stream-K tiles of the tcgen05 kernel; the mma.sync kernels need none
+    return decode_uses_umma(M, N, K) ? decode_umma_workspace_bytes() : 0;
   const DecodePlan pl = plan_decode(M, N, K, k_split);
   return kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
 }
@@ -513,7 +536,12 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   p.chunks = K / kChunk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M <= 16 && k_split <= 0) {
-    // preferred: the TMA-fed ring kernel; shapes it does not take fall through to the register-streaming one
+    if (decode_uses_umma(M, N, K)) {
+      const int rc_umma = launch_decode_umma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
+                                             workspace_bytes, st, decode_programmatic_launch());
+      if (rc_umma != MP_ERR_UNSUPPORTED) return rc_umma;
+    }
+    // the TMA-fed mma.sync ring kernel; shapes it does not take fall through to the register-streaming one
     const int rc_tma = launch_decode_tma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, st);
     if (rc_tma != MP_ERR_UNSUPPORTED) return rc_tma;
     // cluster split-K: the smallest power of two (<= 8, the portable limit) that puts about two
@@ -672,6 +700,14 @@ extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32,
                                       void* workspace, size_t workspace_bytes, mp_stream_t stream) {
   return mp_w4a16_linear_decode_ex(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
                                    workspace_bytes, 0, stream);
+}
+
+extern "C" int mp_set_decode_kernel(int kind) {
+  if (kind != MP_DECODE_KERNEL_MMA_SYNC && kind != MP_DECODE_KERNEL_UMMA && kind != MP_DECODE_KERNEL_AUTO)
+    return MP_ERR_INVALID_ARG;
+  const int prev = g_decode_kernel;
+  g_decode_kernel = kind;
+  return prev;
 }
 
 extern "C" int mp_set_programmatic_launch(int enabled) {

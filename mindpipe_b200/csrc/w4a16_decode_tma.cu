@@ -429,6 +429,7 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
 static bool g_decode_pdl = false;
 void set_decode_programmatic_launch(bool on) { g_decode_pdl = on; }
+bool decode_programmatic_launch() { return g_decode_pdl; }
 
 // Set to a non-zero value by a decode kernel whose bounded wait gave up.
 static __device__ int g_decode_error = 0;
@@ -442,6 +443,28 @@ int read_and_clear_decode_error(int* value) {
   }
   *value = v;
   return MP_OK;
+}
+
+// Device address of g_decode_error on the current device (looked up once per thread and device).
+int* decode_error_word_ptr(int* out_rc) {
+  static thread_local int* err_ptr = nullptr;
+  static thread_local int err_device = -1;
+  *out_rc = MP_OK;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e == cudaSuccess && err_device != device) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_error);
+    if (e == cudaSuccess) {
+      err_ptr = static_cast<int*>(ptr);
+      err_device = device;
+    }
+  }
+  if (e != cudaSuccess) {
+    *out_rc = cuda_fail(e);
+    return nullptr;
+  }
+  return err_ptr;
 }
 
 template <bool HALF, bool FOLD, bool PUSH>
@@ -506,17 +529,9 @@ int launch_decode_tma(const void* x, const void* packed, const void* sz, const v
   p.stages_total = (K + dt::kStageK - 1) / dt::kStageK;
   p.groups_per_stage = gps;
   {
-    static thread_local int* err_ptr = nullptr;          // device address of g_decode_error, looked up once
-    static thread_local int err_device = -1;
-    int device = 0;
-    MP_CUDA_TRY(cudaGetDevice(&device));
-    if (err_device != device) {
-      void* ptr = nullptr;
-      MP_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_error));
-      err_ptr = static_cast<int*>(ptr);
-      err_device = device;
-    }
-    p.error_word = err_ptr;
+    int rc_err = MP_OK;
+    p.error_word = decode_error_word_ptr(&rc_err);
+    if (rc_err != MP_OK) return rc_err;
   }
   const int row_blocks = (N + dt::kRows - 1) / dt::kRows;
   // the smallest power-of-two cluster (<= 8, the portable limit) that puts about two blocks on every SM

@@ -283,6 +283,24 @@ def act_quant_per_token(x, *, want_codes: bool = True, want_fake: bool = False):
     return q, s, f
 
 
+_DECODE_KERNELS = {"mma_sync": 0, "umma": 1, "auto": 2}
+
+
+def set_decode_kernel(kind: str) -> str:
+    """Choose the kernel behind the decode linears for M <= 16; returns the previous choice.
+
+    ``"umma"``: tcgen05.mma with the dequantised weights as the tensor-memory operand;
+    ``"mma_sync"``: the mma.sync ring kernel; ``"auto"`` (the default): by shape.  Shapes the
+    chosen kernel does not take fall through to the other ones.
+    """
+    if kind not in _DECODE_KERNELS:
+        raise ValueError(f"unknown decode kernel {kind!r}; expected one of {sorted(_DECODE_KERNELS)}")
+    prev = _lib.load().mp_set_decode_kernel(_DECODE_KERNELS[kind])
+    if prev < 0:
+        _lib.check(prev, "set_decode_kernel", kind=kind)
+    return next(k for k, v in _DECODE_KERNELS.items() if v == prev)
+
+
 def _error_word(device: torch.device) -> torch.Tensor:
     """Per-device int32 the tensor-core kernels set when a bounded wait gives up."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
