@@ -626,7 +626,7 @@ def run_suite(args, local_rank):
                 packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
                 mods.append((packed, ops.w4a16_prepare(scale, zero, k)))
                 del w
-            for m in (1, 16):
+            for m in [int(v) for v in args.decode_m.split(",")]:
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
                 ws_dec = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, n, k), dev)
@@ -755,6 +755,7 @@ def main():
     ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
     ap.add_argument("--decode-kernel", default="default", choices=["default", "auto", "umma", "mma_sync"],
                     help="kernel behind the M <= 16 decode linears (default: the library's default)")
+    ap.add_argument("--decode-m", default="1,16", help="token counts of the decode suite")
     ap.add_argument("--decode-shapes", default="", help="restrict the decode suite, e.g. 8192x28672,4096x4096 (NxK)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -303,7 +303,10 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       const int u = 2 * i + kh, q = u % du::kASlots;
       const uint32_t aphase = ((u / du::kASlots) & 1) ^ 1;
       const uint32_t a_tmem = tmem_base + lane_field + du::kASlot0 + q * du::kASlotCols;
-      bool slot_ok = true;
+      // (waiting for the slot here, before the expansion, measured 8 % faster at 16 tokens than waiting
+      // just before the first store)
+      if (!__all_sync(0xffffffffu, mbar_wait(aempty0 + 8 * q, aphase, abort_flag))) break;
+      tcgen05_fence_after();
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (j > 0 && short_groups && ((j * 32) & (p.group - 1)) == 0) {   // groups of 32 or 64 columns: next (scale, zero)
@@ -321,16 +324,8 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
           for (int e = 0; e < 4; ++e) r[4 * c + e] = h2_as_u32(v[e]);
         }
-        if (j == 0) {
-          // the first 32 weights are expanded before the slot is needed: the MMAs that still read it
-          // (three units back) get that much more time
-          slot_ok = __all_sync(0xffffffffu, mbar_wait(aempty0 + 8 * q, aphase, abort_flag));
-          if (!slot_ok) break;
-          tcgen05_fence_after();
-        }
         tmem_st_32x32_x16(a_tmem + j * 16, r);
       }
-      if (!slot_ok) break;
       tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
