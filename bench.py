@@ -482,9 +482,14 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
 
     # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
+    # Every linear of the set gets its own stream (forward_host only enqueues and returns), so one linear's
+    # copies overlap another's kernel; the step ends when all results are back in host memory.
+    e2e_streams = [torch.cuda.Stream(device=dev) for _ in layer_shapes()]
+
     def e2e_step(layer):
-        for name, mod in layer:
-            mod.forward_host(x_host[name], y_host[name])      # H2D of X, kernel, D2H of Y on one stream
+        for s_, (name, mod) in zip(e2e_streams, layer):
+            with torch.cuda.stream(s_):
+                mod.forward_host(x_host[name], y_host[name])  # H2D of X, kernel, D2H of Y on this stream
         torch.cuda.synchronize()
 
     e2e_s = float("nan")

@@ -8,12 +8,12 @@ library and raises if it is missing.
 """
 from . import synth  # noqa: F401
 
-__all__ = ["synth", "ops", "modules", "build"]
+__all__ = ["synth", "ops", "modules", "install", "build"]
 __version__ = "0.1.0"
 
 
 def __getattr__(name):
-    if name in ("ops", "modules", "build", "_lib"):
+    if name in ("ops", "modules", "install", "build", "_lib"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)
