@@ -488,8 +488,7 @@ def run_ours(args, rank, world, local_rank):
 
     def e2e_step(layer):
         for s_, (name, mod) in zip(e2e_streams, layer):
-            with torch.cuda.stream(s_):
-                mod.forward_host(x_host[name], y_host[name])  # H2D of X, kernel, D2H of Y on this stream
+            mod.forward_host(x_host[name], y_host[name], stream=s_)   # H2D of X, kernel, D2H of Y on this stream
         torch.cuda.synchronize()
 
     e2e_s = float("nan")

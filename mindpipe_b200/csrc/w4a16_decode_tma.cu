@@ -511,17 +511,47 @@ int launch_decode_tma(const void* x, const void* packed, const void* sz, const v
   if (!aligned(x, 16) || !aligned(packed, 16) || !aligned(sz, 16)) return MP_ERR_UNSUPPORTED;
   const bool half = M <= 8;
   const int mrows = half ? 8 : 16;
-  CUtensorMap tw, tx, tsz;
-  int rc = encode_tensor_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, packed, (uint64_t)K / 2, (uint64_t)N,
-                                (uint64_t)K / 2, 128, dt::kRows, true);
-  if (rc != MP_OK) return rc;
-  rc = encode_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64,
-                            mrows, true);
-  if (rc != MP_OK) return rc;
   const int gps = group < dt::kStageK ? dt::kStageK / group : 1;
-  rc = encode_tensor_map_2d(&tsz, CU_TENSOR_MAP_DATA_TYPE_UINT32, sz, (uint64_t)N, (uint64_t)(K / group),
-                            (uint64_t)N * 4, dt::kRows, gps, false);
-  if (rc != MP_OK) return rc;
+  // The three tensor maps depend on addresses and shapes only; a serving loop calls with the same handful of
+  // (x, W, scales) triples over and over, so the encoded maps are kept in a small per-thread cache.
+  struct MapEntry {
+    const void *x, *packed, *sz;
+    int M, N, K, group, device;
+    CUtensorMap tw, tx, tsz;
+  };
+  constexpr int kMapCache = 32;
+  static thread_local MapEntry cache[kMapCache];
+  static thread_local int cache_used = 0, cache_next = 0;
+  int device = 0;
+  MP_CUDA_TRY(cudaGetDevice(&device));
+  const MapEntry* hit = nullptr;
+  for (int i = 0; i < cache_used; ++i) {
+    const MapEntry& e = cache[i];
+    if (e.x == x && e.packed == packed && e.sz == sz && e.M == M && e.N == N && e.K == K && e.group == group &&
+        e.device == device) {
+      hit = &e;
+      break;
+    }
+  }
+  if (!hit) {
+    MapEntry e{};
+    e.x = x; e.packed = packed; e.sz = sz; e.M = M; e.N = N; e.K = K; e.group = group; e.device = device;
+    int rc = encode_tensor_map_2d(&e.tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, packed, (uint64_t)K / 2, (uint64_t)N,
+                                  (uint64_t)K / 2, 128, dt::kRows, true);
+    if (rc != MP_OK) return rc;
+    rc = encode_tensor_map_2d(&e.tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64,
+                              mrows, true);
+    if (rc != MP_OK) return rc;
+    rc = encode_tensor_map_2d(&e.tsz, CU_TENSOR_MAP_DATA_TYPE_UINT32, sz, (uint64_t)N, (uint64_t)(K / group),
+                              (uint64_t)N * 4, dt::kRows, gps, false);
+    if (rc != MP_OK) return rc;
+    const int slot = cache_used < kMapCache ? cache_used++ : (cache_next++ % kMapCache);
+    cache[slot] = e;
+    hit = &cache[slot];
+  }
+  const CUtensorMap& tw = hit->tw;
+  const CUtensorMap& tx = hit->tx;
+  const CUtensorMap& tsz = hit->tsz;
   DecodeTmaParams p{};
   p.bias = static_cast<const __half*>(bias);
   p.y = static_cast<__half*>(y);

@@ -56,6 +56,7 @@ class VllmPackedInt4Linear(nn.Module):
         self.group_size = self.in_features // int(self.weight_scale.shape[1])
         self._scale_zero = None   # kernel-side layout, built on first use
         self._host_stage = {}     # row count -> (x, y) device staging buffers of forward_host
+        self._host_plans = {}     # (x_host ptr, y_host ptr, shape) -> validated raw call of forward_host
 
     # -- construction -------------------------------------------------------
     @staticmethod
@@ -79,6 +80,7 @@ class VllmPackedInt4Linear(nn.Module):
     def process_weights_after_loading(self) -> None:
         """Build the group-major (scale, zero) buffer the GEMM kernels read."""
         self._scale_zero = ops.w4a16_prepare(self.weight_scale, self.weight_zero_point, self.in_features)
+        self._host_plans = {}            # they hold the old buffer's address
 
     def dequantize(self) -> torch.Tensor:
         """fp16 ``[N, K]`` weights, bit-identical to the reference's fake-quant weight."""
@@ -87,6 +89,8 @@ class VllmPackedInt4Linear(nn.Module):
 
     def _apply(self, fn, *args, **kwargs):
         self._scale_zero = None          # moved/cast: rebuild lazily on the new device
+        self._host_stage = {}
+        self._host_plans = {}
         return super()._apply(fn, *args, **kwargs)
 
     # -- forward ------------------------------------------------------------
@@ -101,12 +105,25 @@ class VllmPackedInt4Linear(nn.Module):
         y = ops.w4a16_linear(x2, self.weight_packed, self._scale_zero, self.bias)
         return y.reshape(*shape[:-1], self.out_features)
 
-    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, stream=None) -> torch.Tensor:
         """Decode (<= 16 rows) on a CPU fp16 tensor, as the reference's CPU forward takes it: the H2D
-        copy, the kernel and the D2H copy are enqueued on the current stream and the call returns at
-        once; read ``y_host`` after synchronising.  Staging buffers are kept per row count."""
+        copy, the kernel and the D2H copy are enqueued on ``stream`` (default: the current stream) and
+        the call returns at once; read ``y_host`` after synchronising.  Staging buffers are kept per row
+        count, and a call that repeats an earlier one's buffers (same ``x_host`` / ``y_host`` storage, as
+        a serving loop with fixed pinned buffers does) skips the argument checks and goes straight to the
+        library."""
         if self._scale_zero is None:
             self.process_weights_after_loading()
+        st = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
+        key = (x_host.data_ptr(), None if y_host is None else y_host.data_ptr(), tuple(x_host.shape))
+        plan = self._host_plans.get(key)
+        if plan is not None:
+            call, args, y_keep, shapes, _keep = plan
+            status = call(*args, st)
+            if status != 0:
+                from . import _lib
+                _lib.check(status, "w4a16_linear_decode_host", **shapes)
+            return y_keep
         m = x_host.shape[0]
         stage = self._host_stage.get(m)
         if stage is None:
@@ -114,8 +131,25 @@ class VllmPackedInt4Linear(nn.Module):
             stage = (torch.empty((m, self.in_features), dtype=torch.float16, device=dev),
                      torch.empty((m, self.out_features), dtype=torch.float16, device=dev))
             self._host_stage[m] = stage
-        return ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias, y_host=y_host,
-                                            x_stage=stage[0], y_stage=stage[1])
+        if stream is None:
+            y = ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias, y_host=y_host,
+                                             x_stage=stage[0], y_stage=stage[1])
+        else:
+            with torch.cuda.stream(stream):
+                y = ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias,
+                                                 y_host=y_host, x_stage=stage[0], y_stage=stage[1])
+        if y_host is not None and x_host.is_pinned() and y_host.is_pinned():
+            # validated once: remember the raw call (the tensors are kept alive by the plan)
+            from . import _lib
+            args = (x_host.data_ptr(), stage[0].data_ptr(), self.weight_packed.data_ptr(), self._scale_zero.data_ptr(),
+                    None if self.bias is None else self.bias.data_ptr(), stage[1].data_ptr(), y_host.data_ptr(),
+                    m, self.out_features, self.in_features, self.group_size)
+            if len(self._host_plans) >= 64:
+                self._host_plans.clear()
+            self._host_plans[key] = (_lib.load().mp_w4a16_linear_decode_host, args, y_host,
+                                     dict(M=m, N=self.out_features, K=self.in_features, group=self.group_size),
+                                     (x_host, stage, self._scale_zero))
+        return y
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "

@@ -176,9 +176,10 @@ def test_host_buffer_entry_matches_device_entry(m):
     mod = VllmPackedInt4Linear.from_float(lin)
     x_host = synth.normal_activation(m, k, seed=3, index=m).pin_memory()
     y_host = torch.empty((m, n), dtype=torch.float16).pin_memory()
-    for _ in range(2):                                   # second call reuses the staging buffers
+    side = torch.cuda.Stream()
+    for it in range(4):               # 2nd call: staging buffers reused; 3rd, 4th: the validated raw call, own stream
         y_host.zero_()
-        out = mod.forward_host(x_host, y_host)
+        out = mod.forward_host(x_host, y_host, stream=side if it == 3 else None)
         torch.cuda.synchronize()
         assert out is y_host
         assert torch.equal(y_host, mod(x_host.cuda()).cpu())
