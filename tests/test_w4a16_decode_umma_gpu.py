@@ -85,3 +85,41 @@ def test_umma_decode_linearity_70b_shape(umma):
     wdq = umma.w4a16_dequant(packed, scale, zero, n, k)[rows].float()
     ref = (x.float() @ wdq.T).cpu().numpy()
     assert O.rel_frobenius(y1[:, rows].float().cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("kind", ["umma", "mma_sync"])
+def test_back_to_back_launches_under_programmatic_dependent_launch(kind):
+    """A chain of decode launches sharing one workspace, each allowed to start fetching its weights while the
+    previous one finishes (mp_set_programmatic_launch): same bits as the serialised chain."""
+    from mindpipe_b200 import _lib, ops
+    prev_kind = ops.set_decode_kernel(kind)
+    lib = _lib.load()
+    try:
+        shapes = [(1024, 2048), (512, 4096), (2048, 1024)]
+        x = {k: synth.normal_activation(16, k, seed=9, index=k).cuda() for k in {k for _, k in shapes}}
+        mods = []
+        for i, (n, k) in enumerate(shapes):
+            w = synth.normal_weight(n, k, seed=9, index=i).cuda()
+            packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+            mods.append((packed, ops.w4a16_prepare(scale, zero, k), k))
+        ws = ops.new_workspace(max(ops.w4a16_decode_workspace_bytes(16, n, k) for n, k in shapes), "cuda")
+
+        def chain():
+            outs = []
+            for _ in range(3):
+                for packed, sz, k in mods:
+                    outs.append(ops.w4a16_linear_decode(x[k], packed, sz, workspace=ws))
+            torch.cuda.synchronize()
+            return outs
+
+        base = chain()
+        before = lib.mp_set_programmatic_launch(1)
+        try:
+            overlapped = chain()
+        finally:
+            lib.mp_set_programmatic_launch(before)
+        ops.check_device_errors()
+        for a, b in zip(base, overlapped):
+            assert torch.equal(a, b)
+    finally:
+        ops.set_decode_kernel(prev_kind)
