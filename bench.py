@@ -571,7 +571,7 @@ def run_ours(args, rank, world, local_rank):
 def run_suite(args, local_rank):
     """Per-kernel numbers for the other configs (one JSON line each, after the headline line)."""
     import torch
-    from mindpipe_b200 import ops, synth
+    from mindpipe_b200 import _lib, ops, synth
     from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
 
     torch.cuda.set_device(local_rank)
@@ -630,6 +630,7 @@ def run_suite(args, local_rank):
                 packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
                 mods.append((packed, ops.w4a16_prepare(scale, zero, k)))
                 del w
+            _lib.load().mp_set_programmatic_launch(1 if args.suite_pdl else 0)
             for m in [int(v) for v in args.decode_m.split(",")]:
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
@@ -644,7 +645,8 @@ def run_suite(args, local_rank):
                 t = timed(g.replay, 20) / copies
                 b = w4a16_bytes(n, k, m)
                 emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
-                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"])
+                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"], **({"pdl": 1} if args.suite_pdl else {}))
+            _lib.load().mp_set_programmatic_launch(0)
             del mods
     if "prefill" in want or "all" in want:
         for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
@@ -760,6 +762,8 @@ def main():
     ap.add_argument("--decode-kernel", default="default", choices=["default", "auto", "umma", "mma_sync"],
                     help="kernel behind the M <= 16 decode linears (default: the library's default)")
     ap.add_argument("--decode-m", default="1,16", help="token counts of the decode suite")
+    ap.add_argument("--suite-pdl", type=int, default=0,
+                    help="decode suite: launch the chain with programmatic dependent launch (adds \"pdl\": 1 to the line)")
     ap.add_argument("--decode-shapes", default="", help="restrict the decode suite, e.g. 8192x28672,4096x4096 (NxK)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
