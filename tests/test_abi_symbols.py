@@ -61,3 +61,30 @@ def test_ops_reject_cpu_tensors():
         ops.act_quant_per_token(torch.zeros(2, 64, dtype=torch.float16))
     with pytest.raises(TypeError):
         ops.act_quant_per_token([1, 2, 3])
+
+
+def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
+    """mp_set_decode_kernel is host state: it returns the previous choice, rejects unknown kinds, and decides
+    whether a decode call of at most 16 rows wants scratch (the tcgen05 kernel's stream-K tiles)."""
+    from mindpipe_b200 import _lib, ops
+    lib = _lib.load()
+    MMA_SYNC, UMMA, AUTO = 0, 1, 2
+    first = lib.mp_set_decode_kernel(AUTO)
+    try:
+        assert first in (MMA_SYNC, UMMA, AUTO)
+        assert lib.mp_set_decode_kernel(7) == -1                       # invalid argument, choice unchanged
+        assert lib.mp_set_decode_kernel(AUTO) == AUTO
+        # AUTO: 9..16 rows on at least 64 MiB of packed weights
+        assert lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672) > 0
+        assert lib.mp_w4a16_decode_workspace_bytes(8, 8192, 28672) == 0
+        assert lib.mp_w4a16_decode_workspace_bytes(16, 22016, 4096) == 0
+        assert lib.mp_set_decode_kernel(UMMA) == AUTO
+        need = lib.mp_w4a16_decode_workspace_bytes(1, 4096, 4096)
+        assert need > 0 and need == lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672)   # shape-independent bound
+        assert lib.mp_set_decode_kernel(MMA_SYNC) == UMMA
+        assert lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672) == 0
+        assert ops.set_decode_kernel("auto") == "mma_sync"
+        with pytest.raises(ValueError, match="unknown decode kernel"):
+            ops.set_decode_kernel("wgmma")
+    finally:
+        lib.mp_set_decode_kernel(first)
