@@ -564,9 +564,18 @@ int launch_decode_tma(const void* x, const void* packed, const void* sz, const v
     if (rc_err != MP_OK) return rc_err;
   }
   const int row_blocks = (N + dt::kRows - 1) / dt::kRows;
-  // the smallest power-of-two cluster (<= 8, the portable limit) that puts about two blocks on every SM
+  // K is cut over a cluster of ck blocks: the smallest power of two (<= 8, the portable limit) that puts
+  // about two blocks on every SM ...
+  constexpr int kSlots = 2 * kSmCount;
   int ck = 1;
-  while (ck < 8 && row_blocks * ck < 2 * kSmCount && p.stages_total >= 2 * ck) ck <<= 1;
+  while (ck < 8 && row_blocks * ck < kSlots && p.stages_total >= 2 * ck) ck <<= 1;
+  // ... unless that grid needs more than one and a half waves: the second wave pays the launch ramp (first
+  // TMA round trip) and the cluster reduction again, which costs more than the idle slots of one wave
+  // filled to three quarters (8192x28672, M = 1: 512 blocks 35.9 us, 256 blocks 31.4 us; 8192x8192:
+  // 15.7 -> 12.1 us; 28672x8192: 37.4 -> 35.0 us).  Grids of up to 1.5 waves keep the finer split: in a
+  // back-to-back sequence of 7B-sized linears it measured better (12288x4096 as 384 rather than 192
+  // blocks: 69.0 vs 72.2 us per layer set).
+  if (ck > 1 && row_blocks * ck * 2 > kSlots * 3) ck >>= 1;
   p.stages_per_block = (p.stages_total + ck - 1) / ck;
   // Folded scales need each warp's 128-column half of a stage to lie inside one group.  They pay for
   // M <= 8 (measured 10-15 % faster on the 70B shapes, neutral on the 7B ones); with 9..16 tokens the
