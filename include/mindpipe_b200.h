@@ -211,7 +211,7 @@ int mp_set_programmatic_launch(int enabled);
  *   MP_DECODE_KERNEL_MMA_SYNC  the mma.sync ring kernel (also the one behind
  *                              the row-parallel entry points)
  *   MP_DECODE_KERNEL_AUTO      (default) the tcgen05 kernel for 9..16 tokens on
- *                              weights of at least 64 MiB packed with at least
+ *                              weights of at least 40 MiB packed with at least
  *                              16384 output rows, the mma.sync kernel otherwise
  * The tcgen05 kernel divides the (row block, K stage) pairs evenly over a
  * persistent grid and needs the workspace of mp_w4a16_decode_workspace_bytes

@@ -45,16 +45,16 @@ size_t decode_umma_workspace_bytes();
 static int g_decode_kernel = MP_DECODE_KERNEL_AUTO;
 
 // AUTO: the tcgen05 kernel for 9 to 16 tokens (below that the mma.sync kernel's folded scales are cheaper
-// still) on weights of at least 64 MiB packed with at least 128 row blocks -- the shapes where the mma.sync
+// still) on weights of at least 40 MiB packed with at least 128 row blocks -- the shapes where the mma.sync
 // kernel cannot cut K without a second wave and stream-K's even split pays (28672x8192, M = 16: 43.9 vs
-// 52.2 us).  With fewer row blocks the mma.sync kernel's one-wave cluster split is as fast or faster
-// (8192x28672: 45.1 vs 46.3 us; 8192x8192: 16.2 vs 21.9 us), and inside a back-to-back sequence of 7B-sized
-// linears under programmatic dependent launch the persistent grid overlaps its neighbours less than the
-// mma.sync kernel's short blocks do (71.1 vs 69.5 us per layer set).
+// 52.2 us; 22016x4096: 23.4 vs 26.3 us, and 66.1 vs 69.4 us per 7B layer set when the fused gate/up
+// projection alone takes it).  With fewer row blocks the mma.sync kernel's one-wave cluster split is as
+// fast or faster (8192x28672: 45.1 vs 46.3 us; 8192x8192: 16.2 vs 21.9 us; 12288x4096 inside the layer
+// set: 71.1 us per set when it also goes to the tcgen05 kernel).
 static bool decode_uses_umma(int M, int N, int K) {
   if (g_decode_kernel == MP_DECODE_KERNEL_UMMA) return true;
   if (g_decode_kernel != MP_DECODE_KERNEL_AUTO) return false;
-  return M > 8 && N >= 16384 && (size_t)N * (size_t)K / 2 >= (size_t)64 << 20;
+  return M > 8 && N >= 16384 && (size_t)N * (size_t)K / 2 >= (size_t)40 << 20;
 }
 
 constexpr int kWarpsK = 4;        // warps along K inside a block

@@ -74,11 +74,12 @@ def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
         assert first in (MMA_SYNC, UMMA, AUTO)
         assert lib.mp_set_decode_kernel(7) == -1                       # invalid argument, choice unchanged
         assert lib.mp_set_decode_kernel(AUTO) == AUTO
-        # AUTO: 9..16 rows on at least 64 MiB of packed weights with at least 16384 output rows
+        # AUTO: 9..16 rows on at least 40 MiB of packed weights with at least 16384 output rows
         assert lib.mp_w4a16_decode_workspace_bytes(16, 28672, 8192) > 0
+        assert lib.mp_w4a16_decode_workspace_bytes(16, 22016, 4096) > 0
         assert lib.mp_w4a16_decode_workspace_bytes(8, 28672, 8192) == 0
         assert lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672) == 0
-        assert lib.mp_w4a16_decode_workspace_bytes(16, 22016, 4096) == 0
+        assert lib.mp_w4a16_decode_workspace_bytes(16, 12288, 4096) == 0
         assert lib.mp_set_decode_kernel(UMMA) == AUTO
         need = lib.mp_w4a16_decode_workspace_bytes(1, 4096, 4096)
         assert need > 0 and need == lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672)   # shape-independent bound
