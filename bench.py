@@ -635,17 +635,19 @@ def run_suite(args, local_rank):
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
                 ws_dec = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, n, k), dev)
+                opt = 0
                 g = torch.cuda.CUDAGraph()
                 for pk, sz in mods:
-                    ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
+                    ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y, options=opt)
                 torch.cuda.synchronize()
                 with torch.cuda.graph(g):
                     for pk, sz in mods:
-                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
+                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y, options=opt)
                 t = timed(g.replay, 20) / copies
                 b = w4a16_bytes(n, k, m)
                 emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
-                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"], **({"pdl": 1} if args.suite_pdl else {}))
+                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"], kernel=args.decode_kernel,
+                     **({"pdl": 1} if args.suite_pdl else {}))
             _lib.load().mp_set_programmatic_launch(0)
             del mods
     if "prefill" in want or "all" in want:

@@ -202,8 +202,10 @@ int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, con
 int mp_set_programmatic_launch(int enabled);
 
 /*
- * Chooses the kernel behind the decode linears for M <= 16 (returns the
- * previous choice, or MP_ERR_INVALID_ARG).  Both compute F.linear(x, Wdq) of
+ * The process-wide DEFAULT kernel behind the decode linears for M <= 16 (returns
+ * the previous choice, or MP_ERR_INVALID_ARG); a call that must not depend on
+ * what another host in the process has set passes its choice in the options of
+ * mp_w4a16_linear_decode_opts instead.  Both compute F.linear(x, Wdq) of
  * awq/quantize/quantizer.py:109-130 with fp32 accumulation:
  *   MP_DECODE_KERNEL_UMMA      tcgen05.mma with the dequantised weights as the
  *                              tensor-memory operand (a thread expands one
@@ -212,17 +214,39 @@ int mp_set_programmatic_launch(int enabled);
  *                              the row-parallel entry points)
  *   MP_DECODE_KERNEL_AUTO      (default) the tcgen05 kernel for 9..16 tokens on
  *                              weights of at least 40 MiB packed with at least
- *                              16384 output rows, the mma.sync kernel otherwise
+ *                              16384 output rows when a workspace was passed,
+ *                              the mma.sync kernel otherwise
  * The tcgen05 kernel divides the (row block, K stage) pairs evenly over a
  * persistent grid and needs the workspace of mp_w4a16_decode_workspace_bytes
  * (zero-filled when created, left ready for the next call, not shared by calls
- * that overlap); without a workspace, and for shapes the chosen kernel does not
- * take, the call falls through to the other kernels.
+ * that overlap; re-zero it after a device-side wait has given up); without a
+ * workspace, and for shapes the chosen kernel does not take, the call falls
+ * through to the other kernels.
  */
 #define MP_DECODE_KERNEL_MMA_SYNC 0
 #define MP_DECODE_KERNEL_UMMA 1
 #define MP_DECODE_KERNEL_AUTO 2
 int mp_set_decode_kernel(int kind);
+
+/*
+ * mp_w4a16_linear_decode for M <= 16 with the kernel and programmatic dependent
+ * launch chosen by THIS call (no process-wide state is read for what the
+ * options name; 0 leaves everything at the process defaults):
+ *   MP_DECODE_OPT_KERNEL_*     the kernel, as above
+ *   MP_DECODE_OPT_PDL_ON/_OFF  programmatic dependent launch for this call (see
+ *                              mp_set_programmatic_launch for what it allows)
+ */
+#define MP_DECODE_OPT_KERNEL_MASK 0x7u
+#define MP_DECODE_OPT_KERNEL_MMA_SYNC 0x1u
+#define MP_DECODE_OPT_KERNEL_UMMA 0x2u
+#define MP_DECODE_OPT_KERNEL_AUTO 0x4u
+#define MP_DECODE_OPT_PDL_MASK 0x30u
+#define MP_DECODE_OPT_PDL_ON 0x10u
+#define MP_DECODE_OPT_PDL_OFF 0x20u
+int mp_w4a16_linear_decode_opts(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                void* workspace, size_t workspace_bytes, unsigned int options,
+                                mp_stream_t stream);
 
 /*
  * Synchronously reads (and clears) the flag a decode kernel sets when one of

@@ -31,6 +31,7 @@ SIGNATURES = {
     "mp_w4a16_decode_workspace_bytes_ex": (_Z, [_I, _I, _I, _I]),
     "mp_w4a16_linear_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "mp_w4a16_linear_decode_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _I, _P]),
+    "mp_w4a16_linear_decode_opts": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _U, _P]),
     "mp_w4a16_rowparallel_push": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_w4a16_linear_decode_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),

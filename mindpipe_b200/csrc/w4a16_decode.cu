@@ -29,8 +29,9 @@
 namespace mp {
 
 // TMA-fed kernel for M <= 16 (w4a16_decode_tma.cu)
+// pdl_choice: -1 = the process-wide setting, 0 / 1 = programmatic dependent launch off / on for this call
 int launch_decode_tma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
-                      int group, cudaStream_t st, const DecodePush* push = nullptr);
+                      int group, cudaStream_t st, const DecodePush* push = nullptr, int pdl_choice = -1);
 void set_decode_programmatic_launch(bool on);
 bool decode_programmatic_launch();
 int read_and_clear_decode_error(int* value);
@@ -38,10 +39,8 @@ int read_and_clear_decode_error(int* value);
 int launch_decode_umma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
                        int group, void* workspace, size_t workspace_bytes, cudaStream_t st, bool pdl);
 size_t decode_umma_workspace_bytes();
-
-// Which kernel serves M <= 16: MP_DECODE_KERNEL_UMMA (tcgen05, weights through tensor memory),
-// MP_DECODE_KERNEL_MMA_SYNC (the mma.sync ring kernel) or MP_DECODE_KERNEL_AUTO (by shape).  Shapes the
-// chosen one does not take fall through.
+// Which kernel serves M <= 16 when a call does not say: one of the MP_DECODE_KERNEL_* values.  Shapes the
+// chosen one does not take fall through to the next.
 static int g_decode_kernel = MP_DECODE_KERNEL_AUTO;
 
 // AUTO: the tcgen05 kernel for 9 to 16 tokens (below that the mma.sync kernel's folded scales are cheaper
@@ -51,10 +50,10 @@ static int g_decode_kernel = MP_DECODE_KERNEL_AUTO;
 // projection alone takes it).  With fewer row blocks the mma.sync kernel's one-wave cluster split is as
 // fast or faster (8192x28672: 45.1 vs 46.3 us; 8192x8192: 16.2 vs 21.9 us; 12288x4096 inside the layer
 // set: 71.1 us per set when it also goes to the tcgen05 kernel).
-static bool decode_uses_umma(int M, int N, int K) {
-  if (g_decode_kernel == MP_DECODE_KERNEL_UMMA) return true;
-  if (g_decode_kernel != MP_DECODE_KERNEL_AUTO) return false;
-  return M > 8 && N >= 16384 && (size_t)N * (size_t)K / 2 >= (size_t)40 << 20;
+static int decode_kernel_for(int kind, int M, int N, int K, bool have_workspace) {
+  if (kind != MP_DECODE_KERNEL_AUTO) return kind;
+  if (have_workspace && M > 8 && N >= 16384 && (size_t)N * (size_t)K / 2 >= (size_t)40 << 20) return MP_DECODE_KERNEL_UMMA;
+  return MP_DECODE_KERNEL_MMA_SYNC;
 }
 
 constexpr int kWarpsK = 4;        // warps along K inside a block
@@ -510,8 +509,9 @@ using namespace mp;
 
 extern "C" size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split) {
   if (M <= 0 || M > 64 || N <= 0 || K <= 0 || K % kChunk != 0) return 0;
-  if (M <= 16 && k_split <= 0)               // stream-K tiles of the tcgen05 kernel; the mma.sync kernels need none
-    return decode_uses_umma(M, N, K) ? decode_umma_workspace_bytes() : 0;
+  if (M <= 16 && k_split <= 0) {             // partial tiles of the persistent tcgen05 kernels; the mma.sync kernels need none
+    return g_decode_kernel == MP_DECODE_KERNEL_MMA_SYNC ? 0 : decode_umma_workspace_bytes();
+  }
   const DecodePlan pl = plan_decode(M, N, K, k_split);
   return kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
 }
@@ -520,10 +520,39 @@ extern "C" size_t mp_w4a16_decode_workspace_bytes(int M, int N, int K) {
   return mp_w4a16_decode_workspace_bytes_ex(M, N, K, 0);
 }
 
+static int decode_linear(const void* x_f16, const void* packed_i32, const void* sz_f16x2, const void* bias_f16,
+                         void* y_f16, int M, int N, int K, int group, void* workspace, size_t workspace_bytes,
+                         int k_split, int kind, int pdl_choice, mp_stream_t stream);
+
 extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
                                          const void* bias_f16, void* y_f16, int M, int N, int K, int group,
                                          void* workspace, size_t workspace_bytes, int k_split,
                                          mp_stream_t stream) {
+  return decode_linear(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace, workspace_bytes,
+                       k_split, g_decode_kernel, -1, stream);
+}
+
+extern "C" int mp_w4a16_linear_decode_opts(const void* x_f16, const void* packed_i32, const void* sz_f16x2,
+                                           const void* bias_f16, void* y_f16, int M, int N, int K, int group,
+                                           void* workspace, size_t workspace_bytes, unsigned int options,
+                                           mp_stream_t stream) {
+  const unsigned int k = options & MP_DECODE_OPT_KERNEL_MASK;
+  int kind = g_decode_kernel;
+  if (k == MP_DECODE_OPT_KERNEL_MMA_SYNC) kind = MP_DECODE_KERNEL_MMA_SYNC;
+  else if (k == MP_DECODE_OPT_KERNEL_UMMA) kind = MP_DECODE_KERNEL_UMMA;
+  else if (k == MP_DECODE_OPT_KERNEL_AUTO) kind = MP_DECODE_KERNEL_AUTO;
+  else if (k != 0) return MP_ERR_INVALID_ARG;
+  const unsigned int pd = options & MP_DECODE_OPT_PDL_MASK;
+  if (pd == MP_DECODE_OPT_PDL_MASK) return MP_ERR_INVALID_ARG;
+  const int pdl_choice = pd == MP_DECODE_OPT_PDL_ON ? 1 : pd == MP_DECODE_OPT_PDL_OFF ? 0 : -1;
+  if (M > 16) return MP_ERR_UNSUPPORTED;
+  return decode_linear(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace, workspace_bytes, 0,
+                       kind, pdl_choice, stream);
+}
+
+static int decode_linear(const void* x_f16, const void* packed_i32, const void* sz_f16x2, const void* bias_f16,
+                         void* y_f16, int M, int N, int K, int group, void* workspace, size_t workspace_bytes,
+                         int k_split, int kind, int pdl_choice, mp_stream_t stream) {
   if (!x_f16 || !packed_i32 || !sz_f16x2 || !y_f16 || M <= 0 || N <= 0 || K <= 0 || group <= 0) return MP_ERR_INVALID_ARG;
   if (M > 64 || K % kChunk != 0 || group % 32 != 0 || K % group != 0 || N % 8 != 0) return MP_ERR_UNSUPPORTED;
   if (!aligned(x_f16, 16) || !aligned(packed_i32, 16) || !aligned(sz_f16x2, 4) || !aligned(y_f16, 2)) return MP_ERR_ALIGNMENT;
@@ -537,13 +566,16 @@ extern "C" int mp_w4a16_linear_decode_ex(const void* x_f16, const void* packed_i
   p.chunks = K / kChunk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M <= 16 && k_split <= 0) {
-    if (decode_uses_umma(M, N, K)) {
+    const bool pdl = pdl_choice < 0 ? decode_programmatic_launch() : pdl_choice != 0;
+    const int chosen = decode_kernel_for(kind, M, N, K, workspace != nullptr && workspace_bytes > 0);
+    if (chosen == MP_DECODE_KERNEL_UMMA) {
       const int rc_umma = launch_decode_umma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
-                                             workspace_bytes, st, decode_programmatic_launch());
+                                             workspace_bytes, st, pdl);
       if (rc_umma != MP_ERR_UNSUPPORTED) return rc_umma;
     }
     // the TMA-fed mma.sync ring kernel; shapes it does not take fall through to the register-streaming one
-    const int rc_tma = launch_decode_tma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, st);
+    const int rc_tma = launch_decode_tma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, st, nullptr,
+                                         pdl ? 1 : 0);
     if (rc_tma != MP_ERR_UNSUPPORTED) return rc_tma;
     // cluster split-K: the smallest power of two (<= 8, the portable limit) that puts about two
     // 16-warp blocks on every SM, as long as every block keeps at least one chunk per K-warp

@@ -469,7 +469,7 @@ int* decode_error_word_ptr(int* out_rc) {
 
 template <bool HALF, bool FOLD, bool PUSH>
 static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tsz, const DecodeTmaParams& p,
-                      int row_blocks, int ck, cudaStream_t st) {
+                      int row_blocks, int ck, cudaStream_t st, bool pdl) {
   using C = dt::Cfg<HALF>;
   auto kern = w4a16_decode_tma_kernel<HALF, FOLD, PUSH>;
   static thread_local int configured_device = -1;
@@ -490,7 +490,7 @@ static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtens
   attrs[0].val.clusterDim.y = ck;
   attrs[0].val.clusterDim.z = 1;
   int n_attrs = 1;
-  if (g_decode_pdl && !PUSH) {      // a push launch shares its block counter with the previous one: no early start
+  if (pdl && !PUSH) {      // a push launch shares its block counter with the previous one: no early start
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     n_attrs = 2;
@@ -505,7 +505,8 @@ static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtens
 // register-streaming kernel): M > 16, K % 64 != 0, N % 4 != 0, group sizes that neither divide nor
 // are a multiple of 256.
 int launch_decode_tma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
-                      int group, cudaStream_t st, const DecodePush* push) {
+                      int group, cudaStream_t st, const DecodePush* push, int pdl_choice) {
+  const bool pdl = pdl_choice < 0 ? g_decode_pdl : pdl_choice != 0;
   if (M > 16 || K % 64 != 0 || N % 4 != 0) return MP_ERR_UNSUPPORTED;
   if (!((group <= dt::kStageK && dt::kStageK % group == 0) || group % dt::kStageK == 0)) return MP_ERR_UNSUPPORTED;
   if (!aligned(x, 16) || !aligned(packed, 16) || !aligned(sz, 16)) return MP_ERR_UNSUPPORTED;
@@ -583,13 +584,13 @@ int launch_decode_tma(const void* x, const void* packed, const void* sz, const v
   // exact per-weight form.
   if (push) {
     p.push = *push;
-    if (half && group % 128 == 0) return launch_tma<true, true, true>(tw, tx, tsz, p, row_blocks, ck, st);
-    return half ? launch_tma<true, false, true>(tw, tx, tsz, p, row_blocks, ck, st)
-                : launch_tma<false, false, true>(tw, tx, tsz, p, row_blocks, ck, st);
+    if (half && group % 128 == 0) return launch_tma<true, true, true>(tw, tx, tsz, p, row_blocks, ck, st, pdl);
+    return half ? launch_tma<true, false, true>(tw, tx, tsz, p, row_blocks, ck, st, pdl)
+                : launch_tma<false, false, true>(tw, tx, tsz, p, row_blocks, ck, st, pdl);
   }
-  if (half && group % 128 == 0) return launch_tma<true, true, false>(tw, tx, tsz, p, row_blocks, ck, st);
-  return half ? launch_tma<true, false, false>(tw, tx, tsz, p, row_blocks, ck, st)
-              : launch_tma<false, false, false>(tw, tx, tsz, p, row_blocks, ck, st);
+  if (half && group % 128 == 0) return launch_tma<true, true, false>(tw, tx, tsz, p, row_blocks, ck, st, pdl);
+  return half ? launch_tma<true, false, false>(tw, tx, tsz, p, row_blocks, ck, st, pdl)
+              : launch_tma<false, false, false>(tw, tx, tsz, p, row_blocks, ck, st, pdl);
 }
 
 }  // namespace mp

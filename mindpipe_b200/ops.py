@@ -122,12 +122,30 @@ def w4a16_prepare(weight_scale, weight_zero_point, in_features: int):
     return sz
 
 
-def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int = 0, workspace=None, out=None):
+_DECODE_OPT_KERNEL = {"mma_sync": 0x1, "umma": 0x2, "auto": 0x4}
+
+
+def decode_options(kernel: str | None = None, pdl: bool | None = None) -> int:
+    """The ``options`` word of ``mp_w4a16_linear_decode_opts``: kernel and programmatic dependent launch
+    chosen for one call; ``None`` keeps the process default."""
+    opt = 0
+    if kernel is not None:
+        if kernel not in _DECODE_OPT_KERNEL:
+            raise ValueError(f"unknown decode kernel {kernel!r}; expected one of {sorted(_DECODE_OPT_KERNEL)}")
+        opt |= _DECODE_OPT_KERNEL[kernel]
+    if pdl is not None:
+        opt |= 0x10 if pdl else 0x20
+    return opt
+
+
+def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int = 0, workspace=None, out=None,
+                        options: int = 0):
     """``y[M,N] = x[M,K] @ dequant(W)^T (+bias)`` with the weight-streaming kernels (M <= 64; meant for
     M <= 16 -- above that ``w4a16_linear`` prefers the split-K tensor-core GEMM).
 
     ``workspace`` (uint8, zero-filled when created, not shared by calls that
-    may overlap) defaults to a cached buffer per device and stream.
+    may overlap) defaults to a cached buffer per device and stream.  ``options``
+    (see :func:`decode_options`, M <= 16 only) fixes kernel / launch mode for this call.
     """
     x2 = _req(x, "x", torch.float16, 2)
     p = _req(weight_packed, "weight_packed", torch.int32, 2)
@@ -147,9 +165,16 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
     y = torch.empty((m, n), dtype=torch.float16, device=x2.device) if out is None else _req(out, "out", torch.float16, 2)
     if y.shape != (m, n):
         raise ValueError(f"out must be [{m}, {n}]")
-    st = lib.mp_w4a16_linear_decode_ex(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
-                                       m, n, k, k // groups, _ptr(ws), 0 if ws is None else ws.numel(), k_split,
-                                       _stream())
+    if options:
+        if k_split:
+            raise ValueError("options and k_split cannot be combined")
+        st = lib.mp_w4a16_linear_decode_opts(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
+                                             m, n, k, k // groups, _ptr(ws), 0 if ws is None else ws.numel(),
+                                             int(options), _stream())
+    else:
+        st = lib.mp_w4a16_linear_decode_ex(x2.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), y.data_ptr(),
+                                           m, n, k, k // groups, _ptr(ws), 0 if ws is None else ws.numel(), k_split,
+                                           _stream())
     _lib.check(st, "w4a16_linear_decode", M=m, N=n, K=k, group=k // groups)
     return y
 
@@ -291,7 +316,8 @@ def set_decode_kernel(kind: str) -> str:
 
     ``"umma"``: tcgen05.mma with the dequantised weights as the tensor-memory operand;
     ``"mma_sync"``: the mma.sync ring kernel; ``"auto"`` (the default): by shape.  Shapes the
-    chosen kernel does not take fall through to the other ones.
+    chosen kernel does not take fall through to the other ones.  This is the process-wide default;
+    a single call chooses with ``options=decode_options(kernel=...)``.
     """
     if kind not in _DECODE_KERNELS:
         raise ValueError(f"unknown decode kernel {kind!r}; expected one of {sorted(_DECODE_KERNELS)}")

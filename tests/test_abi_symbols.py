@@ -45,7 +45,7 @@ def test_argument_validation_needs_no_gpu(built_lib):
     lib = _lib.load()
     assert lib.mp_w4a16_quantize(None, 8, 128, 128, None, None, None, None) == -1
     assert lib.mp_act_quant_per_token(None, 4, 64, None, None, None, None) == -1
-    assert lib.mp_w4a16_decode_workspace_bytes(16, 4096, 4096) == 0      # M <= 16: no scratch at all
+    assert lib.mp_w4a16_decode_workspace_bytes(16, 4096, 4096) > 0       # partial tiles of the persistent kernels
     assert lib.mp_w4a16_decode_workspace_bytes(32, 4096, 4096) > 0
     assert lib.mp_w4a16_decode_workspace_bytes_ex(16, 4096, 4096, 4) > 0
     assert lib.mp_w4a16_decode_workspace_bytes(128, 4096, 4096) == 0     # decode kernel is M <= 64
@@ -64,8 +64,9 @@ def test_ops_reject_cpu_tensors():
 
 
 def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
-    """mp_set_decode_kernel is host state: it returns the previous choice, rejects unknown kinds, and decides
-    whether a decode call of at most 16 rows wants scratch (the tcgen05 kernel's stream-K tiles)."""
+    """mp_set_decode_kernel is host state (the default for calls that do not choose): it returns the previous
+    choice, rejects unknown kinds, and decides whether a decode call of at most 16 rows wants scratch (the
+    partial tiles of the persistent tcgen05 kernels)."""
     from mindpipe_b200 import _lib, ops
     lib = _lib.load()
     MMA_SYNC, UMMA, AUTO = 0, 1, 2
@@ -74,19 +75,26 @@ def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
         assert first in (MMA_SYNC, UMMA, AUTO)
         assert lib.mp_set_decode_kernel(7) == -1                       # invalid argument, choice unchanged
         assert lib.mp_set_decode_kernel(AUTO) == AUTO
-        # AUTO: 9..16 rows on at least 40 MiB of packed weights with at least 16384 output rows
-        assert lib.mp_w4a16_decode_workspace_bytes(16, 28672, 8192) > 0
-        assert lib.mp_w4a16_decode_workspace_bytes(16, 22016, 4096) > 0
-        assert lib.mp_w4a16_decode_workspace_bytes(8, 28672, 8192) == 0
-        assert lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672) == 0
-        assert lib.mp_w4a16_decode_workspace_bytes(16, 12288, 4096) == 0
+        # every kernel choice but the mma.sync ring kernel may cut row blocks between blocks of a persistent
+        # grid and then wants the same, shape-independent scratch
+        need = lib.mp_w4a16_decode_workspace_bytes(16, 28672, 8192)
+        assert need > 0
+        for m, n, k in [(16, 22016, 4096), (8, 28672, 8192), (1, 4096, 4096), (16, 8192, 28672)]:
+            assert lib.mp_w4a16_decode_workspace_bytes(m, n, k) == need
         assert lib.mp_set_decode_kernel(UMMA) == AUTO
-        need = lib.mp_w4a16_decode_workspace_bytes(1, 4096, 4096)
-        assert need > 0 and need == lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672)   # shape-independent bound
+        assert lib.mp_w4a16_decode_workspace_bytes(1, 4096, 4096) == need
         assert lib.mp_set_decode_kernel(MMA_SYNC) == UMMA
         assert lib.mp_w4a16_decode_workspace_bytes(16, 8192, 28672) == 0
         assert ops.set_decode_kernel("auto") == "mma_sync"
         with pytest.raises(ValueError, match="unknown decode kernel"):
             ops.set_decode_kernel("wgmma")
+        assert ops.decode_options() == 0
+        assert ops.decode_options(kernel="umma", pdl=True) == 0x2 | 0x10
+        assert ops.decode_options(kernel="mma_sync", pdl=False) == 0x1 | 0x20
+        with pytest.raises(ValueError):
+            ops.decode_options(kernel="wgmma")
+        # per-call options are validated before anything touches a device
+        assert lib.mp_w4a16_linear_decode_opts(None, None, None, None, None, 1, 8, 128, 128, None, 0, 0x3, None) == -1
+        assert lib.mp_w4a16_linear_decode_opts(None, None, None, None, None, 1, 8, 128, 128, None, 0, 0x30, None) == -1
     finally:
         lib.mp_set_decode_kernel(first)
