@@ -170,14 +170,20 @@ def build_cpu_sets(n_sets, m):
 
 
 def run_reference(args, rank, world):
+    """The reference's CPU forward of the same linears on this box's host cores.  Under torchrun rank 0 alone
+    runs it (the launcher pins every rank to one thread; that is undone here), and the line describes ONE
+    replica of the workload whatever --gpus says."""
     import torch
     if rank != 0:
         return
+    if world > 1 or os.environ.get("OMP_NUM_THREADS") == "1":
+        torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     sets, xs = build_cpu_sets(2, M_DECODE)
     for _ in range(max(args.warmup, 1)):
         cpu_reference_pass(sets, xs, 1)
-    dt = cpu_reference_pass(sets, xs, args.steps)
+    runs = sorted(cpu_reference_pass(sets, xs, args.steps) for _ in range(5))
+    dt = runs[len(runs) // 2]                                # median of five passes of `steps` steps
     gbs = step_bytes(M_DECODE) * args.steps / dt / 1e9
     line = {
         "impl": "reference", "metric": "w4a16_decode_linear_algorithmic_hbm_gbs", "value": gbs, "unit": "GB/s",
@@ -185,32 +191,24 @@ def run_reference(args, rank, world):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": workload_config(),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{args.steps} steps of the 7-linear set at M={M_DECODE}: torch CPU F.linear on "
-                                   "fp16 weights dequantised by the oracle, 2 layer sets alternating"},
+                         "sample": f"median of 5 runs of {args.steps} steps of the 7-linear set at M={M_DECODE}: torch CPU "
+                                   "F.linear on fp16 weights dequantised by the oracle, 2 layer sets alternating"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "replicas_timed": 1,
+        "note": "one replica of the workload on the host cores; with --gpus N the GPU arm reports N replicas",
     }
     print(json.dumps(line), flush=True)
 
 
-def measure_row_parallel(world, rank, dev, dist, iters=50):
-    """Llama-2-70B down_proj (8192 x 28672, W4A16 g128) at decode M=16 with the input features sharded
-    over the ranks: the decode kernel pushes its partial sums to every peer, a finish kernel adds them."""
+def _timed_pair(dist, dev, iters=50):
+    """(eager, graph) timers for a multi-rank callable: device time per call, max over ranks, in us."""
     import torch
-    from mindpipe_b200 import ops, synth
-    from mindpipe_b200.modules import VllmPackedInt4Linear
-    from mindpipe_b200.row_parallel import RowParallelW4A16Linear
-    n, k = 8192, 28672
-    if k % (world * 256):
-        return {"skipped": f"{k} input features do not split into 256-column stages over {world} ranks"}
-    k_loc = k // world
-    w = synth.normal_weight(n, k_loc, seed=7, index=rank).to(dev)             # this rank's column slice
-    packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
-    del w
-    local = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k_loc, out_features=n,
-                                 zero_point=zero)
-    layer = RowParallelW4A16Linear(local, None, max_rows=M_DECODE)
-    x = synth.normal_activation(M_DECODE, k_loc, seed=7, index=100 + rank).to(dev)
+
+    def reduce_max(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3
 
     def timed(fn):
         for _ in range(5):
@@ -223,13 +221,10 @@ def measure_row_parallel(world, rank, dev, dist, iters=50):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e3
+        return reduce_max(e0.elapsed_time(e1) / iters)
 
     def timed_graph(fn):
-        """`iters` calls captured in one graph and replayed ONCE (every call carries its own epoch, so
-        the graph must not be replayed twice); removes the host launch path from the measurement."""
+        """`iters` calls captured in one graph and replayed once: removes the host launch path."""
         for _ in range(5):
             fn()
         dist.barrier()
@@ -248,20 +243,91 @@ def measure_row_parallel(world, rank, dev, dist, iters=50):
             graph.replay()
             e1.record(side)
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e3
+        return reduce_max(e0.elapsed_time(e1) / iters)
 
-    us_fused_eager = timed(lambda: layer(x))
-    ops.check_device_errors()
-    us_fused = timed_graph(lambda: layer(x))
-    ops.check_device_errors()
-    us_local = timed_graph(lambda: local(x))
-    us_nccl = timed(lambda: layer.forward_nccl(x))
-    return {"config": f"llama2-70b down_proj 8192x28672 W4A16 g128, M={M_DECODE}, K sharded over {world} ranks",
-            "us_fused_push_allreduce": us_fused, "us_fused_eager_launches": us_fused_eager,
-            "us_local_gemm_only": us_local, "us_local_gemm_plus_nccl_allreduce_eager": us_nccl, "n_gpus": world,
-            "algorithmic_gbs_whole_job": w4a16_bytes(n, k, M_DECODE) / (us_fused * 1e-6) / 1e9}
+    return timed, timed_graph
+
+
+def measure_row_parallel(world, rank, dev, dist, iters=50):
+    """Llama-2-70B down_proj (8192 x 28672, W4A16 g128) at decode M=16 with the input features sharded
+    over the ranks: the decode kernel leaves its partial sums in peer-mapped memory, a finish kernel adds them
+    (one-shot: every rank adds everything; two-phase: every rank its own columns, then fp16 slices are exchanged)."""
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    from mindpipe_b200.row_parallel import RowParallelW4A16Linear
+    n, k = 8192, 28672
+    if k % (world * 256):
+        return {"skipped": f"{k} input features do not split into 256-column stages over {world} ranks"}
+    k_loc = k // world
+    w = synth.normal_weight(n, k_loc, seed=7, index=rank).to(dev)             # this rank's column slice
+    packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+    del w
+    local = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k_loc, out_features=n,
+                                 zero_point=zero)
+    x = synth.normal_activation(M_DECODE, k_loc, seed=7, index=100 + rank).to(dev)
+    timed, timed_graph = _timed_pair(dist, dev, iters)
+    out = {"config": f"llama2-70b down_proj 8192x28672 W4A16 g128, M={M_DECODE}, K sharded over {world} ranks",
+           "n_gpus": world}
+    for name, two_phase in (("one_shot", False), ("two_phase", True)):
+        layer = RowParallelW4A16Linear(local, None, max_rows=M_DECODE, two_phase=two_phase)
+        if two_phase and not layer.two_phase:
+            continue
+        out[f"us_fused_{name}_eager_launches"] = timed(lambda: layer(x))
+        ops.check_device_errors()
+        out[f"us_fused_{name}"] = timed_graph(lambda: layer(x))
+        ops.check_device_errors()
+    layer = RowParallelW4A16Linear(local, None, max_rows=M_DECODE)            # default choice for this world size
+    out["default_exchange"] = "two_phase" if layer.two_phase else "one_shot"
+    out["us_fused_push_allreduce"] = out[f"us_fused_{out['default_exchange']}"]
+    out["us_local_gemm_only"] = timed_graph(lambda: local(x))
+    out["us_local_gemm_plus_nccl_allreduce_eager"] = timed(lambda: layer.forward_nccl(x))
+    out["algorithmic_gbs_whole_job"] = w4a16_bytes(n, k, M_DECODE) / (out["us_fused_push_allreduce"] * 1e-6) / 1e9
+    return out
+
+
+def measure_column_parallel(world, rank, dev, dist, iters=50):
+    """The split BASELINE config 5 names: Llama-2-70B-shaped W4A16 linears with the OUTPUT rows sharded over
+    the ranks, decode M in {1, 8, 64}, all-gather of the output slices.  Local kernel and gather are timed
+    separately; the gather both as the device-driven peer-store exchange and as NCCL all_gather_into_tensor."""
+    import torch
+    from mindpipe_b200 import ops, synth
+    from mindpipe_b200.column_parallel import ColumnParallelW4A16Linear
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    hbm = json.loads(peaks_path.read_text())["hbm_gbs"] if peaks_path.exists() else 6650.0
+    timed, timed_graph = _timed_pair(dist, dev, iters)
+    rows = []
+    for name, (n, k) in (("gate_up_proj", (28672, 8192)), ("attn_proj", (8192, 8192))):
+        if n % world or ((n // world) * 2) % 16:
+            rows.append({"linear": name, "skipped": f"{n} rows do not split over {world} ranks"})
+            continue
+        n_loc = n // world
+        w = synth.normal_weight(n_loc, k, seed=11, index=rank).to(dev)        # this rank's row slice
+        packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
+        del w
+        local = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k, out_features=n_loc,
+                                     zero_point=zero)
+        layer = ColumnParallelW4A16Linear(local, n, max_rows=64)
+        for m in (1, 8, 64):
+            x = synth.normal_activation(m, k, seed=11, index=200).to(dev)      # replicated activations
+            same = bool(torch.equal(layer(x), layer.forward_nccl(x)))
+            ops.check_device_errors()
+            us_local = timed_graph(lambda: local(x))
+            us_fused = timed_graph(lambda: layer(x))
+            ops.check_device_errors()
+            us_nccl = timed(lambda: layer.forward_nccl(x))
+            y_loc = local(x).contiguous()
+            us_gather_nccl = timed(lambda: layer._gather_nccl(y_loc))
+            gbs = w4a16_bytes(n, k, m) / (us_fused * 1e-6) / 1e9
+            rows.append({"linear": name, "N": n, "K": k, "M": m, "us_local_kernel": us_local,
+                         "us_local_plus_peer_gather": us_fused, "us_peer_gather": max(us_fused - us_local, 0.0),
+                         "us_local_plus_nccl_all_gather_eager": us_nccl, "us_nccl_all_gather_eager": us_gather_nccl,
+                         "algorithmic_gbs_whole_job": gbs, "frac_of_n_x_measured_hbm": gbs / (world * hbm),
+                         "gathers_agree_bitwise": same})
+    return {"config": f"llama2-70b-shaped W4A16 g128 linears, output rows sharded over {world} ranks, all-gather of "
+                      "the output slices", "n_gpus": world, "rows": rows,
+            "parity": all(r.get("gathers_agree_bitwise", True) for r in rows)}
 
 
 def measure_moe(world, rank, dev, dist, iters=10):
@@ -447,38 +513,53 @@ def run_ours(args, rank, world, local_rank):
         parallel(["gate_proj", "up_proj"])
         launch("down_proj", mods["down_proj"])
 
-    # ---- one CUDA graph per layer set: the kernels, without host launch gaps ----
+    # ---- multi-rank parity first: the sharded paths against the single-GPU modules, inside this very job ----
+    parity = None
+    if dist is not None:
+        try:
+            from mindpipe_b200.verify import all_ranks_agree, verify_multi_gpu
+            parity = all_ranks_agree(verify_multi_gpu(rank, world, dev), dev)
+        except Exception as err:
+            parity = {"error": f"{type(err).__name__}: {err}"[:200]}
+
+    # ---- the timed steps as ONE CUDA graph (K steps back to back, as a serving runtime captures a whole
+    # decode pass: no host launch gaps, and under programmatic dependent launch a linear's prologue runs under
+    # its predecessor's tail across step boundaries too) ----
     for layer in pool[:2]:
         step(layer)
     torch.cuda.synchronize()
-    graphs = []
-    for layer in pool:
+    launches_per_step = len(layer_shapes())
+
+    def capture(first, count):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            step(layer)
-        graphs.append((g, None))
-    launches_per_step = len(layer_shapes())
+            for i in range(count):
+                step(pool[(first + i) % POOL_SETS])
+        return g
+
+    warm_graph = capture(0, args.warmup)
+    timed_graph = capture(args.warmup, args.steps)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        graphs[i % POOL_SETS][0].replay()
+    warm_graph.replay()
+    timed_graph.replay()                    # one untimed replay of the timed graph itself (first-replay set-up)
+    warm_graph.replay()
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
         ev0.record()
-        for i in range(args.steps):
-            graphs[(args.warmup + i) % POOL_SETS][0].replay()
+        timed_graph.replay()
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
         if ms < 200:                       # keep the sampler alive long enough to see clocks under load
             t_end = time.time() + 0.4
             while time.time() < t_end:
-                graphs[0][0].replay()
+                warm_graph.replay()
             torch.cuda.synchronize()
 
     # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
@@ -491,34 +572,53 @@ def run_ours(args, rank, world, local_rank):
             mod.forward_host(x_host[name], y_host[name], stream=s_)   # H2D of X, kernel, D2H of Y on this stream
         torch.cuda.synchronize()
 
-    e2e_s = float("nan")
+    def e2e_run(count):
+        t0 = time.perf_counter()
+        for i in range(count):
+            e2e_step(pool[(args.warmup + i) % POOL_SETS])
+        return time.perf_counter() - t0
+
+    e2e_s, e2e_detail = float("nan"), None
     if not args.no_e2e:
+        # every (layer set, linear) pair is called once before the clock starts, whatever --warmup says: the
+        # first forward_host of a module allocates its staging buffers and encodes its tensor maps
+        for layer in pool:
+            e2e_step(layer)
         for i in range(args.warmup):
             e2e_step(pool[i % POOL_SETS])
+        # `steps` steps take a few milliseconds: repeat the run until at least 0.1 s has been timed per sample,
+        # take five samples and report the median per-step time
+        probe = e2e_run(args.steps)
+        inner = max(1, int(0.1 / max(probe, 1e-6)) + 1)
         barrier()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            e2e_step(pool[(args.warmup + i) % POOL_SETS])
+        samples = []
+        for _ in range(5):
+            samples.append(e2e_run(args.steps * inner) / inner)
         barrier()
-        e2e_s = time.perf_counter() - t0
+        samples.sort()
+        e2e_s = samples[len(samples) // 2]
+        e2e_detail = {"samples_ms_per_step": [round(v / args.steps * 1e3, 4) for v in samples],
+                      "steps_per_sample": args.steps * inner, "statistic": "median of 5"}
 
     t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
 
-    moe_extra = None
-    if args.moe:
+    def extra(fn, *a):
         try:
-            moe_extra = measure_moe(world, rank, dev, dist)
-        except Exception as err:          # the headline number must not depend on the extra
-            moe_extra = {"error": f"{type(err).__name__}: {err}"[:200]}
-    tp_extra = None
-    if args.moe and world > 1:            # the sharded 70B down_proj: decode kernel fused with its all-reduce
-        try:
-            tp_extra = measure_row_parallel(world, rank, dev, dist)
-        except Exception as err:
-            tp_extra = {"error": f"{type(err).__name__}: {err}"[:200]}
+            return fn(*a)
+        except Exception as err:          # the headline number must not depend on an extra
+            return {"error": f"{type(err).__name__}: {err}"[:200]}
+
+    moe_extra = extra(measure_moe, world, rank, dev, dist) if args.moe else None
+    tp_extra = col_extra = None
+    if args.moe and world > 1:            # the sharded 70B linears
+        tp_extra = extra(measure_row_parallel, world, rank, dev, dist)
+        col_extra = extra(measure_column_parallel, world, rank, dev, dist)
+    configs_extra = None
+    if args.moe and world == 1 and rank == 0:
+        configs_extra = extra(measure_other_configs, args, local_rank)
 
     if rank == 0:
         bytes_step = step_bytes(M_DECODE)
@@ -545,14 +645,21 @@ def run_ours(args, rank, world, local_rank):
                          "launch_us_avg": ms * 1e3 / (args.steps * launches_per_step)},
             "e2e": {"value": e2e_val, "unit": "GB/s",
                     "h2d_bytes_per_step": sum(t.numel() * 2 for t in x_host.values()),
-                    "d2h_bytes_per_step": sum(t.numel() * 2 for t in y_host.values())},
+                    "d2h_bytes_per_step": sum(t.numel() * 2 for t in y_host.values()),
+                    "timing": e2e_detail},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "tflops": world * step_flops(M_DECODE) * args.steps / (ms * 1e-3) / 1e12,
             "moe_w8a8": moe_extra,
         }
+        if parity is not None:
+            line["multi_gpu_parity"] = parity
         if tp_extra is not None:
             line["tp_row_parallel"] = tp_extra
+        if col_extra is not None:
+            line["tp_column_parallel"] = col_extra
+        if configs_extra is not None:
+            line["configs"] = configs_extra
         if world == 1 and not args.no_cpu_baseline:
             cores = torch.get_num_threads()
             sets, xs = build_cpu_sets(2, M_DECODE)
@@ -567,9 +674,34 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def measure_other_configs(args, local_rank):
+    """The other BASELINE configs at their full sizes, one compact record each (kernel-level timings, graph
+    replay, operands rotated through more than twice the L2): config 2 prefill M=2048, config 3 W8A8 M=4096,
+    config 5 decode M in {1, 8, 64}."""
+    rows = []
+    sub = argparse.Namespace(**vars(args))
+    sub.suite, sub.decode_shapes, sub.decode_m, sub.suite_pdl = "decode,prefill,w8a8", "8192x8192,1024x8192,28672x8192,8192x28672", "1,8,64", 1
+    sub.fast_weights = True
+    run_suite(sub, local_rank, collect=rows)
+    out = {"w4a16_decode_llama2_70b": [], "w4a16_prefill_llama2_7b": [], "w8a8_llama3_8b": []}
+    for r in rows:
+        if r["suite"] == "w4a16_decode":
+            out["w4a16_decode_llama2_70b"].append({k: r[k] for k in ("N", "K", "M", "us", "gbs", "frac_of_measured_hbm")})
+        elif r["suite"] == "w4a16_prefill":
+            out["w4a16_prefill_llama2_7b"].append({k: r[k] for k in ("N", "K", "M", "us", "tflops", "frac_of_measured_bf16_burst")})
+        elif r["suite"] == "w8a8":
+            out["w8a8_llama3_8b"].append({k: r[k] for k in ("N", "K", "M", "act_quant_us", "act_quant_gbs", "gemm_us", "gemm_tops",
+                                                          "linear_tops", "library_int8_gemm_tops")})
+    out["note"] = ("decode: chains of launches under programmatic dependent launch, weights rotated; M=64 goes through the "
+                   "dispatching entry (split-K tensor-core GEMM); library_int8_gemm_tops is torch._int_mm on the same box, "
+                   "a timing yardstick only (MEASURED_PEAKS.json has no int8 figure)")
+    return out
+
+
 # ----------------------------------------------------------------------------
-def run_suite(args, local_rank):
-    """Per-kernel numbers for the other configs (one JSON line each, after the headline line)."""
+def run_suite(args, local_rank, collect=None):
+    """Per-kernel numbers for the other configs (one JSON line each, after the headline line; appended to
+    `collect` instead when a list is given)."""
     import torch
     from mindpipe_b200 import _lib, ops, synth
     from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
@@ -615,7 +747,19 @@ def run_suite(args, local_rank):
         return e0.elapsed_time(e1) / (rounds * len(fns)) * 1e-3
 
     def emit(**kw):
-        print(json.dumps(kw), flush=True)
+        if collect is not None:
+            collect.append(kw)
+        else:
+            print(json.dumps(kw), flush=True)
+
+    def weight(n, k, seed, index=0):
+        """N(0, 0.02) fp16 weights: seeded on the CPU (reproducible bits), or drawn on the device when only
+        timings are wanted (a 28672 x 8192 matrix takes seconds on the host)."""
+        if getattr(args, "fast_weights", False):
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed * 1000003 + index)
+            return (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.float16)
+        return synth.normal_weight(n, k, seed=seed, index=index).to(dev)
 
     want = set(args.suite.split(","))
     if "decode" in want or "all" in want:
@@ -626,7 +770,7 @@ def run_suite(args, local_rank):
             copies = max(2, int(300e6 // (n * k // 2)) + 1)           # rotate > 2x L2 of packed weights
             mods = []
             for c in range(copies):
-                w = synth.normal_weight(n, k, seed=c, index=0).to(dev)
+                w = weight(n, k, c)
                 packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
                 mods.append((packed, ops.w4a16_prepare(scale, zero, k)))
                 del w
@@ -635,14 +779,19 @@ def run_suite(args, local_rank):
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
                 ws_dec = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, n, k), dev)
-                opt = 0
+
+                def call(pk, sz):
+                    if m <= 16:
+                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
+                    else:                       # above 16 rows the dispatching entry takes the split-K tensor-core GEMM
+                        ops.w4a16_linear(x, pk, sz)
                 g = torch.cuda.CUDAGraph()
                 for pk, sz in mods:
-                    ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y, options=opt)
+                    call(pk, sz)
                 torch.cuda.synchronize()
                 with torch.cuda.graph(g):
                     for pk, sz in mods:
-                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y, options=opt)
+                        call(pk, sz)
                 t = timed(g.replay, 20) / copies
                 b = w4a16_bytes(n, k, m)
                 emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
@@ -652,7 +801,7 @@ def run_suite(args, local_rank):
             del mods
     if "prefill" in want or "all" in want:
         for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
-            w = synth.normal_weight(n, k, seed=0, index=0).to(dev)
+            w = weight(n, k, 0)
             packed, scale, zero, _ = ops.w4a16_quantize(w, GROUP)
             sz = ops.w4a16_prepare(scale, zero, k)
             x = synth.normal_activation(2048, k, seed=0).to(dev)
@@ -699,7 +848,7 @@ def run_suite(args, local_rank):
     if "w8a8" in want or "all" in want:
         for (n, k) in [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]:
             m = 4096
-            w = synth.normal_weight(n, k, seed=0, index=0).to(dev)
+            w = weight(n, k, 0)
             qw, sw, _ = ops.act_quant_per_token(w)
             x = synth.outlier_activation(m, k, seed=0).to(dev)
             qx, sx, _ = ops.act_quant_per_token(x)

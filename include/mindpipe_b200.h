@@ -479,6 +479,55 @@ int mp_w8a8_rowparallel_finish(const void* const* peer_acc_i32, const void* cons
                                const void* flags_u32, int world, const void* epoch_counter_u32, int M,
                                int N, const void* w_scale_f32, const void* bias_f16, void* y_f16,
                                int* error_word, mp_stream_t stream);
+/*
+ * mp_peer_publish                    copies up to two local ranges (A: 16-byte units, B: 4-byte units) to byte
+ *                                    offsets offset_a / offset_b of this rank's receive slot -- slot0 or slot1 by
+ *                                    the parity of the call number, which the kernel reads from epoch_counter_u32,
+ *                                    advances and raises on every peer (block_counter: device int, zero between
+ *                                    calls).  It replaces mp_peer_signal where the slot must alternate from call to
+ *                                    call even inside a replayed CUDA graph: the producers write to ordinary local
+ *                                    buffers and the slot is chosen on the device.
+ * mp_w8a8_rowparallel_finish_parity  mp_w8a8_rowparallel_finish reading the slot of the call number's parity
+ *                                    (entry [r] of the *0 / *1 arrays = rank r's slot 0 / slot 1).
+ */
+int mp_peer_publish(const void* src_a, int bytes_a, int offset_a, const void* src_b, int bytes_b, int offset_b,
+                    void* slot0, void* slot1, void* const* peer_flags_u32, void* epoch_counter_u32,
+                    int* block_counter, int world, int rank, mp_stream_t stream);
+int mp_w8a8_rowparallel_finish_parity(const void* const* peer_acc0_i32, const void* const* peer_acc1_i32,
+                                      const void* const* peer_xscale0_f32, const void* const* peer_xscale1_f32,
+                                      const void* flags_u32, int world, const void* epoch_counter_u32, int M,
+                                      int N, const void* w_scale_f32, const void* bias_f16, void* y_f16,
+                                      int* error_word, mp_stream_t stream);
+
+/*
+ * All-gather of output slices for the column-parallel linear (output rows of the weight split over `world`
+ * GPUs; the role of the runtime's tensor-parallel all-gather after a column-parallel linear,
+ * acceleration/runtime_patches/vllm_ascend.patch:3260-3305): src [rows][slice_bytes] holds this rank's columns;
+ * they are stored into every rank's gathered buffer [rows][world * slice_bytes] (peer_gather0 / peer_gather1,
+ * used alternately by call parity; entry [r] = rank r's buffer) at column offset rank * slice_bytes, the call
+ * number in epoch_counter_u32 is advanced and raised on every peer, and once all ranks' slices have arrived
+ * (bounded wait, 2 s -> error word 7) this rank's gathered buffer is copied to out [rows][world * slice_bytes].
+ * slice_bytes % 16 == 0.  No argument changes between calls (graph-replayable).
+ */
+int mp_peer_allgather_push(const void* src, int rows, int slice_bytes, void* const* peer_gather0,
+                           void* const* peer_gather1, void* const* peer_flags_u32, void* epoch_counter_u32,
+                           int* block_counter, int world, int rank, void* out, int* error_word,
+                           mp_stream_t stream);
+
+/*
+ * Two-phase form of mp_w4a16_rowparallel_finish: after the arrival words have reached the call number, this
+ * rank adds the `world` partial sums of ITS N / world output columns in rank order (+ bias), rounds to fp16 and
+ * stores that slice into every rank's gathered buffer [M][N] (peer_gather0 / peer_gather1 by call parity); a
+ * second round of arrival words (peer_flags2_u32) then tells every rank that its buffer is complete, and it is
+ * copied to y.  Every element is computed once, by its owner: identical bits on all ranks, and 1 / world of the
+ * NVLink reads of the one-shot form.  N % (4 * world) == 0.
+ */
+int mp_w4a16_rowparallel_finish2(void* const* peer_partial0_f32, void* const* peer_partial1_f32,
+                                 const void* arrival_flags_u32, void* const* peer_gather0_f16,
+                                 void* const* peer_gather1_f16, void* const* peer_flags2_u32,
+                                 int* block_counter, int world, int rank, const void* epoch_counter_u32, int M,
+                                 int N, const void* bias_f16, void* y_f16, int* error_word,
+                                 mp_stream_t stream);
 size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
 int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
                    int capacity_rows, void* xplan_i32, mp_stream_t stream);

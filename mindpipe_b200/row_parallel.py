@@ -8,10 +8,13 @@ the unsharded ``nn.Linear``, algorithm/quantization/ptq/awq/source/awq/quantize/
 
 The exchange is driven from the device: the decode kernel leaves its fp32 partial sums in a peer-mapped
 buffer (``torch.distributed._symmetric_memory``) and its last block raises an arrival word on every
-peer; a small second kernel waits for all arrival words, reads the ``P`` buffers over NVLink and adds
-them in rank order -- so all ranks end with bit-identical fp16 outputs, and no NCCL call, barrier
-kernel or host synchronisation sits on the path.  ``forward_nccl`` is the plain fallback (local linear +
-``all_reduce``) for process groups without peer mappings.
+peer; a small second kernel waits for all arrival words and adds the ``P`` buffers in rank order --
+either everything on every rank (one-shot: each rank reads ``4 M N (P-1)`` bytes over NVLink), or, in
+the two-phase form used from four ranks up, each rank only its ``N / P`` columns, whose fp16 result it
+stores to every peer (``1 / P`` of the reads, one more round of arrival words).  Either way all ranks
+end with bit-identical fp16 outputs, and no NCCL call, barrier kernel or host synchronisation sits on
+the path.  ``forward_nccl`` is the plain fallback (local linear + ``all_reduce``) for process groups
+without peer mappings.
 """
 from __future__ import annotations
 
@@ -66,7 +69,8 @@ class RowParallelW4A16Linear(torch.nn.Module):
     """``VllmPackedInt4Linear`` sharded by input features; ``forward(x_local)`` takes this rank's slice
     ``x[:, K_r]`` (<= ``max_rows`` rows) and returns the full ``y[M, N]`` on every rank."""
 
-    def __init__(self, local_linear, bias=None, group=None, max_rows: int = 16, symmetric: bool = True):
+    def __init__(self, local_linear, bias=None, group=None, max_rows: int = 16, symmetric: bool = True,
+                 two_phase: bool | None = None):
         super().__init__()
         self.local = local_linear
         self.group = dist.group.WORLD if group is None else group
@@ -78,6 +82,10 @@ class RowParallelW4A16Linear(torch.nn.Module):
             raise ValueError("the local shard must not carry the bias (it would be added once per rank)")
         self.bias = bias
         self.symmetric = bool(symmetric)
+        # two-phase (reduce own columns, then exchange fp16 slices) pays once the one-shot reads outweigh a
+        # second round of arrival words; it needs N to split into 4-column units per rank
+        can_split = self.out_features % (4 * self.world) == 0
+        self.two_phase = (self.world >= 4 if two_phase is None else bool(two_phase)) and can_split
         if self.symmetric:
             self._setup_symmetric()
 
@@ -86,7 +94,9 @@ class RowParallelW4A16Linear(torch.nn.Module):
         dev = self.local.weight_packed.device
         self.slot_bytes = self.max_rows * self.out_features * 4                      # one [m_cap][N] fp32 buffer
         self.off_partial = 256                                                        # arrival words first
-        total = self.off_partial + 2 * self.slot_bytes
+        self.gather_bytes = (self.max_rows * self.out_features * 2 + 255) // 256 * 256   # one [m_cap][N] fp16 buffer
+        self.off_gather = self.off_partial + 2 * self.slot_bytes
+        total = self.off_gather + 2 * self.gather_bytes
         self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
         self.buf.zero_()
         torch.cuda.synchronize(dev)
@@ -96,7 +106,11 @@ class RowParallelW4A16Linear(torch.nn.Module):
         self.p_flags = (ctypes.c_void_p * self.world)(*bases)
         self.p_partial = [(ctypes.c_void_p * self.world)(*[b + self.off_partial + par * self.slot_bytes for b in bases])
                           for par in range(2)]
+        self.p_flags2 = (ctypes.c_void_p * self.world)(*[b + 128 for b in bases])    # second round of arrival words
+        self.p_gather = [(ctypes.c_void_p * self.world)(*[b + self.off_gather + par * self.gather_bytes for b in bases])
+                         for par in range(2)]
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)     # blocks of the running call that have stored
+        self.counter2 = torch.zeros(1, dtype=torch.int32, device=dev)    # same, for the two-phase finish kernel
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)       # calls completed (advanced by the kernel)
 
     @staticmethod
@@ -130,10 +144,17 @@ class RowParallelW4A16Linear(torch.nn.Module):
                                            self.p_flags, self.counter.data_ptr(), self.epoch.data_ptr(), self.world,
                                            self.rank, m, self.out_features, k_loc, self.local.group_size, stream)
         _lib.check(st, "w4a16_rowparallel_push", M=m, N=self.out_features, K_local=k_loc)
-        st = lib.mp_w4a16_rowparallel_finish(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(), self.world,
-                                             self.epoch.data_ptr(), m, self.out_features,
-                                             None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
-                                             ops._error_word(x2.device).data_ptr(), stream)
+        bias = None if self.bias is None else self.bias.data_ptr()
+        err = ops._error_word(x2.device).data_ptr()
+        if self.two_phase and (m * self.out_features * 2) % 16 == 0:
+            st = lib.mp_w4a16_rowparallel_finish2(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(),
+                                                  self.p_gather[0], self.p_gather[1], self.p_flags2,
+                                                  self.counter2.data_ptr(), self.world, self.rank, self.epoch.data_ptr(),
+                                                  m, self.out_features, bias, y.data_ptr(), err, stream)
+        else:
+            st = lib.mp_w4a16_rowparallel_finish(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(), self.world,
+                                                 self.epoch.data_ptr(), m, self.out_features, bias, y.data_ptr(), err,
+                                                 stream)
         _lib.check(st, "w4a16_rowparallel_finish", M=m, N=self.out_features)
         return y.reshape(*x_local.shape[:-1], self.out_features)
 
@@ -159,6 +180,11 @@ class RowParallelW8A8Linear(torch.nn.Module):
     in peer-mapped memory, raises an arrival word on the peers, and a finish kernel on every rank reads all
     accumulators and token scales over NVLink and adds the dequantised partial products in rank order:
     bit-identical outputs on all ranks, no NCCL call or host synchronisation on the path.
+
+    The quantiser and the GEMM write to ordinary local buffers; a publish kernel copies them into the
+    receive slot of the call number's parity (the number lives in device memory), so the two slots
+    alternate from call to call however the launches were issued -- eagerly, or from a captured graph
+    with any number of forwards in it.
     """
 
     def __init__(self, weight_i8, weight_scale, bias=None, group=None, max_rows: int = 256):
@@ -193,7 +219,9 @@ class RowParallelW8A8Linear(torch.nn.Module):
         self.p_acc = [mk(o) for o in self.off_acc]
         self.p_scale = [mk(o) for o in self.off_scale]
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)     # calls completed (advanced on the device)
-        self.calls = 0
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)   # blocks of the publish kernel that have copied
+        self.acc_local = torch.empty(self.max_rows * self.out_features, dtype=torch.int32, device=dev)
+        self.scale_local = torch.empty(self.max_rows, dtype=torch.float32, device=dev)
 
     @staticmethod
     def from_float(linear: torch.nn.Linear, group=None, **kw):
@@ -218,24 +246,28 @@ class RowParallelW8A8Linear(torch.nn.Module):
         m, k_loc = x2.shape
         if m > self.max_rows or k_loc != self.in_features or x2.dtype != torch.float16:
             raise ValueError(f"x_local must be fp16 [<= {self.max_rows}, {self.in_features}], got {tuple(x2.shape)}")
-        par = self.calls & 1                         # a peer may still read call n while this rank computes call n+1
-        self.calls += 1
         stream = torch.cuda.current_stream().cuda_stream
         base = self.buf.data_ptr()
-        acc_ptr, scale_ptr = base + self.off_acc[par], base + self.off_scale[par]
         qx = torch.empty((m, k_loc), dtype=torch.int8, device=x2.device)
         y = torch.empty((m, self.out_features), dtype=torch.float16, device=x2.device)
         err = ops._error_word(x2.device).data_ptr()
-        _lib.check(lib.mp_act_quant_per_token(x2.data_ptr(), m, k_loc, qx.data_ptr(), scale_ptr, None, stream),
-                   "act_quant_per_token", M=m, K=k_loc)
-        _lib.check(lib.mp_w8a8_gemm_i32(qx.data_ptr(), self.weight.data_ptr(), acc_ptr, m, self.out_features, k_loc, err,
-                                        stream), "w8a8_gemm_i32", M=m, N=self.out_features, K=k_loc)
-        _lib.check(lib.mp_peer_signal(self.p_flags, self.world, self.rank, self.epoch.data_ptr(), stream), "peer_signal")
-        _lib.check(lib.mp_w8a8_rowparallel_finish(self.p_acc[par], self.p_scale[par], base, self.world,
-                                                  self.epoch.data_ptr(), m, self.out_features,
-                                                  self.weight_scale.data_ptr(),
-                                                  None if self.bias is None else self.bias.data_ptr(), y.data_ptr(), err,
-                                                  stream), "w8a8_rowparallel_finish", M=m, N=self.out_features)
+        _lib.check(lib.mp_act_quant_per_token(x2.data_ptr(), m, k_loc, qx.data_ptr(), self.scale_local.data_ptr(), None,
+                                              stream), "act_quant_per_token", M=m, K=k_loc)
+        _lib.check(lib.mp_w8a8_gemm_i32(qx.data_ptr(), self.weight.data_ptr(), self.acc_local.data_ptr(), m,
+                                        self.out_features, k_loc, err, stream),
+                   "w8a8_gemm_i32", M=m, N=self.out_features, K=k_loc)
+        # a peer may still read call n while this rank computes call n+1: two slots, chosen on the device
+        _lib.check(lib.mp_peer_publish(self.acc_local.data_ptr(), m * self.out_features * 4, 0,
+                                       self.scale_local.data_ptr(), m * 4, self.acc_bytes,
+                                       base + self.off_acc[0], base + self.off_acc[1], self.p_flags,
+                                       self.epoch.data_ptr(), self.counter.data_ptr(), self.world, self.rank, stream),
+                   "peer_publish", M=m, N=self.out_features)
+        _lib.check(lib.mp_w8a8_rowparallel_finish_parity(self.p_acc[0], self.p_acc[1], self.p_scale[0], self.p_scale[1],
+                                                         base, self.world, self.epoch.data_ptr(), m, self.out_features,
+                                                         self.weight_scale.data_ptr(),
+                                                         None if self.bias is None else self.bias.data_ptr(),
+                                                         y.data_ptr(), err, stream),
+                   "w8a8_rowparallel_finish", M=m, N=self.out_features)
         return y.reshape(*x_local.shape[:-1], self.out_features)
 
     @torch.no_grad()
