@@ -417,6 +417,30 @@ int mp_moe_expert_stage_scatter(const void* routed_q_i8, const void* routed_scal
                                 int* error_word, mp_stream_t stream);
 
 /*
+ * Dense chunked gate/up projection with SwiGLU and per-token re-quantisation:
+ * for every chunk c of the intermediate size,
+ *   h_c = silu(x W_gate_c^T) * (x W_up_c^T),  (q_c, s_c) = int8 quant of h_c per token.
+ * Replaces the reference's native op grouped_swiglu_loop_out
+ * (acceleration/custom_ops/qwen2_5_vl/aclnn_grouped_swiglu_out_bridge.cpp:157-273;
+ * its callers acceleration/runtime_patches/vllm.patch:114-170 and :959-1001),
+ * which loops aclnnGroupedMatmulSwigluQuant over the chunks; here all chunks
+ * are the groups of one grouped tcgen05 GEMM launch.
+ *   x_i8        [T, H] int8 codes,       x_scale_f32 [T]
+ *   w_i8        [chunks, 2C, H] int8: per chunk the C gate rows, then the C up
+ *               rows (the reference's [1, H, 2C] per-chunk weight, transposed)
+ *   w_scale_f32 [chunks, 2C]
+ *   q_out_i8    [chunks, T, C],          scale_out_f32 [chunks, T]
+ * Dequantisation, SiLU and the product round to fp16 as the expert path does
+ * (smoothquant/fake_quant.py:184-186); scale = f16(max(|h|max, 1e-5) / 127).
+ * H % 16 == 0, C % 16 == 0, chunks <= 256.
+ */
+size_t mp_w8a8_gate_up_swiglu_requant_workspace_bytes(int T, int H, int C, int chunks);
+int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_scale_f32, const void* w_i8,
+                                   const void* w_scale_f32, int T, int H, int C, int chunks,
+                                   void* q_out_i8, void* scale_out_f32, void* workspace,
+                                   size_t workspace_bytes, int* error_word, mp_stream_t stream);
+
+/*
  * out[t] = sum_j f16(d[dest_row(t,j)] * w[t,j]) in fp16, experts in ascending
  * order: npu_moe_token_unpermute (vllm_ascend.patch:2415-2419), i.e.
  * fake_quant.py:188-189.  Entries with dest_row < 0 are skipped.

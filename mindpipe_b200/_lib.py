@@ -59,6 +59,8 @@ SIGNATURES = {
     "mp_moe_expert_stage": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
     "mp_moe_expert_stage_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
     "mp_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_w8a8_gate_up_swiglu_requant_workspace_bytes": (_Z, [_I, _I, _I, _I]),
+    "mp_w8a8_gate_up_swiglu_requant": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P, _P]),
     "mp_gather_rows": (_I, [_P, _P, _I, _I, _P, _P]),
     "mp_peer_barrier": (_I, [_P, _I, _I, ctypes.c_uint, _P, _P]),
     "mp_peer_barrier_counted": (_I, [_P, _I, _I, _P, _P, _P]),

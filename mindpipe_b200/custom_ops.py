@@ -13,13 +13,16 @@ shared library (raising if it is missing) and defines
 * ``mindpipe_b200::w8a8_linear(x, weight, weight_scale, bias?) -> y``
 * ``mindpipe_b200::w8a8_gemm(qx, x_scale, weight, weight_scale, bias?) -> y``
 * ``mindpipe_b200::moe_w8a8_experts(hidden, top_k_index, top_k_weights, w13, w13_scale, w2, w2_scale) -> out``
+* ``mindpipe_b200::grouped_swiglu_loop_out(x, weights, batched_weight, group_list, weight_scales,
+  batched_weight_scale, x_scale, min_tokens, layer_idx) -> (codes, scales)`` -- the reference's own op name and
+  argument list (vllm.patch:114-208)
 
 Each fake implementation only computes output shapes and dtypes.
 """
 from __future__ import annotations
 
 import threading
-from typing import Optional
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -96,6 +99,26 @@ def load_and_register():
         @moe_w8a8_experts.register_fake
         def _(hidden, top_k_index, top_k_weights, w13, w13_scale, w2, w2_scale):
             return torch.empty_like(hidden)
+
+        @torch.library.custom_op(f"{NAMESPACE}::grouped_swiglu_loop_out", mutates_args=())
+        def grouped_swiglu_loop_out(x: torch.Tensor, weights: List[torch.Tensor], batched_weight: torch.Tensor,
+                                    group_list: torch.Tensor, weight_scales: List[torch.Tensor],
+                                    batched_weight_scale: torch.Tensor, x_scale: torch.Tensor, min_tokens: int,
+                                    layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
+            return ops.grouped_swiglu_loop_out(x, weights, batched_weight, group_list, weight_scales,
+                                               batched_weight_scale, x_scale, min_tokens, layer_idx)
+
+        @grouped_swiglu_loop_out.register_fake
+        def _(x, weights, batched_weight, group_list, weight_scales, batched_weight_scale, x_scale, min_tokens,
+              layer_idx):
+            if not weights or len(weights) != len(weight_scales):
+                raise RuntimeError("loop-out requires equal non-empty weight lists")
+            chunks = len(weights)
+            if batched_weight.shape[0] != chunks or batched_weight_scale.shape[0] != chunks:
+                raise RuntimeError("loop-out batched weight has an invalid chunk count")
+            width = batched_weight_scale.shape[-1] // 2
+            return (x.new_empty((chunks, x.shape[0], width), dtype=torch.int8),
+                    x.new_empty((chunks, x.shape[0]), dtype=torch.float32))
 
         _registered = True
     return getattr(torch.ops, NAMESPACE)

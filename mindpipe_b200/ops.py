@@ -487,6 +487,83 @@ def moe_expert_stage(routed_q, routed_scale, plan, num_local_experts: int, w13_q
     return d
 
 
+def w8a8_gate_up_swiglu_requant(x_q, x_scale, w_q, w_scale):
+    """Chunked gate/up projection + SwiGLU + per-token re-quant on int8 rows, all chunks in one grouped launch.
+
+    ``x_q`` int8 ``[T, H]``, ``x_scale`` fp32 ``[T]``, ``w_q`` int8 ``[chunks, 2C, H]`` (per chunk: gate rows, then up
+    rows), ``w_scale`` fp32 ``[chunks, 2C]`` -> (int8 ``[chunks, T, C]``, fp32 ``[chunks, T]``)."""
+    xq = _req(x_q, "x", torch.int8, 2)
+    xs = _req(x_scale, "x_scale", torch.float32, 1)
+    w = _req(w_q, "weight", torch.int8, 3)
+    s = _req(w_scale, "weight_scale", torch.float32, 2)
+    t, h = xq.shape
+    chunks, two_c, h2 = w.shape
+    c = two_c // 2
+    if h2 != h or two_c % 2 or tuple(s.shape) != (chunks, two_c) or xs.numel() != t:
+        raise ValueError("gate/up weight, scale and activation shapes are inconsistent")
+    q = torch.empty((chunks, t, c), dtype=torch.int8, device=xq.device)
+    qs = torch.empty((chunks, t), dtype=torch.float32, device=xq.device)
+    if t == 0:
+        return q, qs
+    lib = _lib.load()
+    nbytes = lib.mp_w8a8_gate_up_swiglu_requant_workspace_bytes(t, h, c, chunks)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=xq.device)
+    st = lib.mp_w8a8_gate_up_swiglu_requant(xq.data_ptr(), xs.data_ptr(), w.data_ptr(), s.data_ptr(), t, h, c, chunks,
+                                            q.data_ptr(), qs.data_ptr(), ws.data_ptr(), nbytes,
+                                            _error_word(xq.device).data_ptr(), _stream())
+    _lib.check(st, "w8a8_gate_up_swiglu_requant", T=t, H=h, C=c, chunks=chunks)
+    return q, qs
+
+
+_LOOP_OUT_WEIGHTS: dict = {}
+
+
+def loop_out_weights(batched_weight, batched_weight_scale):
+    """The reference's ``[chunks, H, 2C]`` gate/up weight and ``[chunks, 2C]`` scale in the layout the kernel
+    streams (``[chunks, 2C, H]``, fp32 scales).  Made once per weight tensor and kept: weights are static while
+    serving (the cache is keyed by storage address and version, so an in-place update makes a new copy)."""
+    key = (batched_weight.data_ptr(), batched_weight._version, batched_weight_scale.data_ptr(),
+           batched_weight_scale._version, tuple(batched_weight.shape))
+    hit = _LOOP_OUT_WEIGHTS.get(key)
+    if hit is None:
+        if batched_weight.dtype != torch.int8 or batched_weight.dim() != 3:
+            raise ValueError("batched_weight must be int8 [chunks, H, 2C]")
+        chunks = batched_weight.shape[0]
+        w = batched_weight.transpose(1, 2).contiguous()
+        s = batched_weight_scale.reshape(chunks, -1).to(torch.float32).contiguous()
+        _LOOP_OUT_WEIGHTS.clear()                       # one layer set resident per call site is the common case
+        hit = _LOOP_OUT_WEIGHTS[key] = (w, s)
+    return hit
+
+
+def grouped_swiglu_loop_out(x, weights, batched_weight, group_list, weight_scales, batched_weight_scale, x_scale,
+                            min_tokens: int = 0, layer_idx: int = -1):
+    """The reference's loop-out op with its argument list (acceleration/runtime_patches/vllm.patch:114-170):
+    ``x`` int8 ``[T, H]``; ``weights`` the per-chunk ``[1, H, 2C]`` views of ``batched_weight``
+    ``[chunks, H, 2C]``; ``group_list`` int64 ``[1]`` (= T); ``weight_scales`` the per-chunk ``[1, 2C]`` views of
+    ``batched_weight_scale``; ``x_scale`` fp32 ``[T]``.  Returns (int8 ``[chunks, T, C]``, fp32 ``[chunks, T]``).
+    The reference switches between a per-chunk loop and one batched call at ``min_tokens``; here every size
+    takes the single grouped launch, so ``min_tokens`` and ``layer_idx`` (a logging tag) only keep the
+    signature.  Argument checks as the bridge's (aclnn_grouped_swiglu_out_bridge.cpp:166-199)."""
+    if not weights or len(weights) != len(weight_scales):
+        raise RuntimeError("loop-out requires equal non-empty weight lists")
+    chunks = len(weights)
+    if batched_weight.shape[0] != chunks or batched_weight_scale.shape[0] != chunks:
+        raise RuntimeError("loop-out batched weight has an invalid chunk count")
+    if x.dim() != 2 or x.dtype != torch.int8:
+        raise RuntimeError("x must be a 2-D int8 tensor")
+    if x_scale.dim() != 1 or x_scale.shape[0] != x.shape[0]:
+        raise RuntimeError("x_scale must be [tokens]")
+    if group_list.dim() != 1 or group_list.numel() != 1 or group_list.dtype != torch.int64:
+        raise RuntimeError("group_list must be int64 [1]")
+    width = batched_weight_scale.shape[-1]
+    for wv, sv in zip(weights, weight_scales):
+        if wv.shape[-1] != width or sv.shape[-1] != width or wv.shape[-2] != x.shape[1]:
+            raise RuntimeError("loop-out weight view shapes differ")
+    w, s = loop_out_weights(batched_weight, batched_weight_scale)
+    return w8a8_gate_up_swiglu_requant(x.contiguous(), x_scale.to(torch.float32).contiguous(), w, s)
+
+
 def moe_combine(d, dest_row, top_k_index, top_k_weights, num_tokens: int):
     """``out[t] = sum_j f16(d[dest(t,j)] * w[t,j])`` (fp16 adds, experts ascending)."""
     dd = _req(d, "d", torch.float16, 2)

@@ -16,10 +16,13 @@ import torch.distributed as dist
 
 
 def _graph_replays(fn, out_of, dev, replays=3):
-    """Capture ``fn`` once, replay it ``replays`` times, return the captured call's output tensor."""
+    """Run ``fn`` once on a side stream, capture it there, replay ``replays`` times; returns the captured call's
+    output tensor."""
     side = torch.cuda.Stream(device=dev)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
+        fn()                                       # per-stream scratch is created outside the capture
+        torch.cuda.synchronize(dev)
         with torch.cuda.graph(graph, stream=side):
             out = fn()
         for _ in range(replays):

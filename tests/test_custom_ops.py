@@ -24,6 +24,11 @@ def test_registration_is_idempotent_and_fake_impls_give_shapes():
                                   torch.empty(4, 512, 128, dtype=torch.int8), torch.empty(4, 512),
                                   torch.empty(4, 128, 256, dtype=torch.int8), torch.empty(4, 128))
         assert out.shape == h.shape
+        bw, bs = torch.empty(4, 128, 96, dtype=torch.int8), torch.empty(4, 96)
+        q, s = ns.grouped_swiglu_loop_out(torch.empty(9, 128, dtype=torch.int8), [bw[i:i + 1] for i in range(4)], bw,
+                                          torch.empty(1, dtype=torch.int64), [bs[i:i + 1] for i in range(4)], bs,
+                                          torch.empty(9), 64, 0)
+        assert q.shape == (4, 9, 48) and q.dtype == torch.int8 and s.shape == (4, 9) and s.dtype == torch.float32
 
 
 @pytest.mark.gpu
