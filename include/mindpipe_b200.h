@@ -526,32 +526,38 @@ int mp_w8a8_rowparallel_finish_parity(const void* const* peer_acc0_i32, const vo
 /*
  * All-gather of output slices for the column-parallel linear (output rows of the weight split over `world`
  * GPUs; the role of the runtime's tensor-parallel all-gather after a column-parallel linear,
- * acceleration/runtime_patches/vllm_ascend.patch:3260-3305): src [rows][slice_bytes] holds this rank's columns;
- * they are stored into every rank's gathered buffer [rows][world * slice_bytes] (peer_gather0 / peer_gather1,
- * used alternately by call parity; entry [r] = rank r's buffer) at column offset rank * slice_bytes, the call
- * number in epoch_counter_u32 is advanced and raised on every peer, and once all ranks' slices have arrived
- * (bounded wait, 2 s -> error word 7) this rank's gathered buffer is copied to out [rows][world * slice_bytes].
- * slice_bytes % 16 == 0.  No argument changes between calls (graph-replayable).
+ * acceleration/runtime_patches/vllm_ascend.patch:3260-3305): src [rows][slice_bytes] holds this rank's columns.
+ * They are stored into every peer's receive buffer (peer_recv0 / peer_recv1, used alternately by call parity;
+ * entry [r] = rank r's buffer, mp_peer_allgather_recv_bytes bytes each, zero before the first call) in a
+ * flag-in-data form -- every 8 bytes on the wire are 4 bytes of payload and the call number -- so the receiver
+ * polls the words it needs and neither a fence nor an arrival word is on the path; out [rows][world * slice_bytes]
+ * receives this rank's slice directly and the peers' slices as they arrive (bounded wait, 2 s -> error word 7).
+ * The call number lives in epoch_counter_u32 (device, zero at start; block_counter: device int, zero between
+ * calls), so no argument changes between calls (graph-replayable).  slice_bytes % 16 == 0.
  */
-int mp_peer_allgather_push(const void* src, int rows, int slice_bytes, void* const* peer_gather0,
-                           void* const* peer_gather1, void* const* peer_flags_u32, void* epoch_counter_u32,
-                           int* block_counter, int world, int rank, void* out, int* error_word,
-                           mp_stream_t stream);
+size_t mp_peer_allgather_recv_bytes(int rows, int slice_bytes, int world);
+int mp_peer_allgather_push(const void* src, int rows, int slice_bytes, void* const* peer_recv0,
+                           void* const* peer_recv1, void* epoch_counter_u32, int* block_counter, int world,
+                           int rank, void* out, int* error_word, mp_stream_t stream);
 
 /*
- * Two-phase form of mp_w4a16_rowparallel_finish: after the arrival words have reached the call number, this
- * rank adds the `world` partial sums of ITS N / world output columns in rank order (+ bias), rounds to fp16 and
- * stores that slice into every rank's gathered buffer [M][N] (peer_gather0 / peer_gather1 by call parity); a
- * second round of arrival words (peer_flags2_u32) then tells every rank that its buffer is complete, and it is
- * copied to y.  Every element is computed once, by its owner: identical bits on all ranks, and 1 / world of the
- * NVLink reads of the one-shot form.  N % (4 * world) == 0.
+ * Reduce-scatter + all-gather form of mp_w4a16_rowparallel_finish (the all-reduce after a row-parallel linear,
+ * acceleration/runtime_patches/vllm_ascend.patch:3260-3305), for use after mp_w4a16_rowparallel_push on the same
+ * stream: partial0_f32 / partial1_f32 are this rank's two partial-sum slots [M][N] (the push kernel wrote the
+ * one of the call number's parity).  The columns rank q owns (N / world of them) are sent to q, which adds the
+ * `world` partial sums in rank order (+ bias), rounds to fp16 and sends the result to everyone; both transfers use
+ * the flag-in-data form of mp_peer_allgather_push (receive buffers peer_recv1_* of
+ * mp_w4a16_rowparallel_recv_bytes(M_max, N, 1) bytes and peer_recv2_* of (M_max, N, 2) bytes, by call parity,
+ * zero before the first call).  Every element is computed once, by its owner: identical bits on all ranks;
+ * a rank sends 12 M N (world-1)/world bytes instead of reading 4 M N (world-1).  Bounded waits (2 s -> error
+ * word 5).  N % (4 * world) == 0.
  */
-int mp_w4a16_rowparallel_finish2(void* const* peer_partial0_f32, void* const* peer_partial1_f32,
-                                 const void* arrival_flags_u32, void* const* peer_gather0_f16,
-                                 void* const* peer_gather1_f16, void* const* peer_flags2_u32,
-                                 int* block_counter, int world, int rank, const void* epoch_counter_u32, int M,
-                                 int N, const void* bias_f16, void* y_f16, int* error_word,
-                                 mp_stream_t stream);
+size_t mp_w4a16_rowparallel_recv_bytes(int M, int N, int which);
+int mp_w4a16_rowparallel_finish_ll(const void* partial0_f32, const void* partial1_f32,
+                                   void* const* peer_recv1_0, void* const* peer_recv1_1,
+                                   void* const* peer_recv2_0, void* const* peer_recv2_1, int world, int rank,
+                                   const void* epoch_counter_u32, int M, int N, const void* bias_f16,
+                                   void* y_f16, int* error_word, mp_stream_t stream);
 size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
 int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
                    int capacity_rows, void* xplan_i32, mp_stream_t stream);

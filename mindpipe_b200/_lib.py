@@ -68,8 +68,10 @@ SIGNATURES = {
     "mp_w8a8_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P]),
     "mp_peer_publish": (_I, [_P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P]),
     "mp_w8a8_rowparallel_finish_parity": (_I, [_P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P]),
-    "mp_peer_allgather_push": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P]),
-    "mp_w4a16_rowparallel_finish2": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P]),
+    "mp_peer_allgather_recv_bytes": (_Z, [_I, _I, _I]),
+    "mp_peer_allgather_push": (_I, [_P, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P]),
+    "mp_w4a16_rowparallel_recv_bytes": (_Z, [_I, _I, _I]),
+    "mp_w4a16_rowparallel_finish_ll": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_moe_ep_plan_ints": (_Z, [_I, _I, _I]),
     "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),

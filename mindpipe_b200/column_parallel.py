@@ -10,9 +10,10 @@ Per GPU the weight stream shrinks by ``P``; the collective moves ``2*M*N`` bytes
 
 At decode sizes the gather is a few hundred kilobytes and a library collective is all latency, so the
 default exchange is a device-driven one over peer-mapped memory (``torch.distributed._symmetric_memory``):
-one kernel stores this rank's slice into every rank's gathered buffer with plain peer stores, raises an
-arrival word on the peers, waits (bounded) for theirs and copies the assembled ``y[M, N]`` out -- no NCCL
-call, no host synchronisation, replayable from a CUDA graph.  ``forward_nccl`` is the plain form
+one kernel stores this rank's slice into every peer's receive buffer with plain peer stores whose every
+8 bytes carry 4 bytes of payload and the call number, and polls (bounded) its own receive buffer for the
+peers' slices while it assembles ``y[M, N]`` -- one one-way NVLink flight, no fence, arrival word, NCCL
+call or host synchronisation, replayable from a CUDA graph.  ``forward_nccl`` is the plain form
 (``all_gather_into_tensor``), used for batches above ``max_rows`` and without peer mappings.
 """
 from __future__ import annotations
@@ -66,18 +67,19 @@ class ColumnParallelW4A16Linear(torch.nn.Module):
 
     def _setup_symmetric(self):
         import torch.distributed._symmetric_memory as symm
+        from . import _lib
         dev = self.local.weight_packed.device
-        self.gather_bytes = (self.max_rows * self.out_features * 2 + 255) // 256 * 256   # one [m_cap][N] fp16 buffer
-        self.buf = symm.empty(256 + 2 * self.gather_bytes, dtype=torch.uint8, device=dev)   # arrival words first
-        self.buf.zero_()
+        n_loc = self.out_features // self.world
+        # one receive buffer per call parity, in the flag-in-data wire form (twice the payload)
+        self.recv_bytes = (_lib.load().mp_peer_allgather_recv_bytes(self.max_rows, n_loc * 2, self.world) + 255) // 256 * 256
+        self.buf = symm.empty(2 * self.recv_bytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()                                                              # call numbers start at 1
         torch.cuda.synchronize(dev)
         self.handle = symm.rendezvous(self.buf, self.group)
-        dist.barrier(self.group)                                                      # every rank zeroed its words
+        dist.barrier(self.group)                                                      # every rank zeroed its buffer
         bases = [int(p) for p in self.handle.buffer_ptrs]
-        self.p_flags = (ctypes.c_void_p * self.world)(*bases)
-        self.p_gather = [(ctypes.c_void_p * self.world)(*[b + 256 + par * self.gather_bytes for b in bases])
-                         for par in range(2)]
-        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)     # blocks of the running call that have stored
+        self.p_recv = [(ctypes.c_void_p * self.world)(*[b + par * self.recv_bytes for b in bases]) for par in range(2)]
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)     # blocks of the running call that are done
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)       # calls completed (advanced by the kernel)
 
     @staticmethod
@@ -102,8 +104,8 @@ class ColumnParallelW4A16Linear(torch.nn.Module):
             return self._gather_nccl(y2).reshape(*lead, self.out_features)
         from . import _lib, ops
         out = torch.empty((m, self.out_features), dtype=y2.dtype, device=y2.device)
-        st = _lib.load().mp_peer_allgather_push(y2.data_ptr(), m, n_loc * 2, self.p_gather[0], self.p_gather[1],
-                                                self.p_flags, self.epoch.data_ptr(), self.counter.data_ptr(), self.world,
+        st = _lib.load().mp_peer_allgather_push(y2.data_ptr(), m, n_loc * 2, self.p_recv[0], self.p_recv[1],
+                                                self.epoch.data_ptr(), self.counter.data_ptr(), self.world,
                                                 self.rank, out.data_ptr(), ops._error_word(y2.device).data_ptr(),
                                                 torch.cuda.current_stream().cuda_stream)
         _lib.check(st, "peer_allgather_push", M=m, N=self.out_features)

@@ -1,6 +1,6 @@
 // Small device-driven collectives over NVLink peer memory for the tensor-parallel linears: an all-gather
-// of output slices (column-parallel W4A16) and a two-phase all-reduce of fp32 partial sums (row-parallel
-// W4A16).  They stand in for the runtime's tensor-parallel all-gather / all-reduce around its linear
+// of output slices (column-parallel W4A16), a reduce-scatter + all-gather of fp32 partial sums (row-parallel
+// W4A16), and the slot publication of the row-parallel W8A8 linear.  They stand in for the runtime's tensor-parallel all-gather / all-reduce around its linear
 // methods (acceleration/runtime_patches/vllm_ascend.patch:3260-3305) at decode sizes, where a library
 // collective is all launch latency.
 //
@@ -73,85 +73,162 @@ __device__ __forceinline__ void pc_publish_when_grid_done(int* block_counter, co
   }
 }
 
-__device__ __forceinline__ uint4 pc_ld_l2(const void* p) {        // peers wrote it: read from L2, not a stale L1 line
-  uint4 r;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-  return r;
+// ---- flag-in-data transfers ------------------------------------------------------------------------------
+// A message that is announced by a separate arrival word costs a full NVLink round trip before the word may
+// be stored (the system-scope fence waits for the data stores to be acknowledged) plus the word's own flight.
+// At decode sizes that is most of the collective.  Here every 8 bytes on the wire carry 4 bytes of payload and
+// the call number (the low-latency form of a library collective's wire protocol): a 16-byte store holds
+// {w0, epoch, w1, epoch}; the receiver polls the very words it needs until both numbers match and no fence,
+// arrival word or grid-wide step is needed.  8-byte halves of a store are never torn, and a slot is reused
+// only two calls later with a different number, so a stale word cannot be mistaken for a fresh one.
+__device__ __forceinline__ void ll_store(void* p, uint32_t w0, uint32_t w1, uint32_t epoch) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(w0), "r"(epoch), "r"(w1), "r"(epoch)
+               : "memory");
+}
+
+struct LlWait {
+  uint64_t t0;
+  bool ok;
+};
+
+// Polls one 16-byte unit until both call numbers equal `epoch` (bounded); false after a timeout.
+__device__ __forceinline__ bool ll_load(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1, LlWait& w) {
+  if (!w.ok) { w0 = w1 = 0; return false; }
+  for (unsigned int it = 0;; ++it) {
+    uint32_t e0, e1;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(e0), "=r"(w1), "=r"(e1) : "l"(p) : "memory");
+    if (e0 == epoch && e1 == epoch) return true;
+    if ((it & 0x3FF) == 0x3FF && pc_timer_ns() - w.t0 > kPcWaitNs) {
+      w.ok = false;
+      w0 = w1 = 0;
+      return false;
+    }
+  }
+}
+
+// The grid's last block (by the arrival counter, which it re-arms) stores the new call number.
+__device__ __forceinline__ void pc_count_call(int* block_counter, unsigned int* epoch_counter, unsigned int epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(block_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+    atomicExch(block_counter, 0);
+    *epoch_counter = epoch;
+  }
 }
 
 // ---- all-gather of row slices -----------------------------------------------------------------------------
-// src [rows][slice_bytes] (this rank's columns) -> every peer's gather[parity][rows][world * slice_bytes] at column
-// offset rank * slice_bytes; then wait for all ranks and copy this rank's gathered buffer to `out`.
+// src [rows][slice_bytes] (this rank's columns) -> every peer's receive buffer of the call's parity,
+// [rows][world][slice_bytes * 2] in the flag-in-data form; this rank's own slice goes straight to `out`
+// [rows][world * slice_bytes], the others are polled out of the local receive buffer.
 __global__ void __launch_bounds__(256)
-peer_allgather_push_kernel(const unsigned char* __restrict__ src, int rows, int slice_bytes, PcPeers gather0,
-                           PcPeers gather1, PcPeers peer_flags, unsigned int* epoch_counter, int* block_counter,
-                           int world, int rank, unsigned char* __restrict__ out, int* error_word) {
-  __shared__ int s_ok;
+peer_allgather_push_kernel(const unsigned char* __restrict__ src, int rows, int slice_bytes, PcPeers recv0,
+                           PcPeers recv1, unsigned int* epoch_counter, int* block_counter, int world, int rank,
+                           unsigned char* __restrict__ out, int* error_word) {
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(epoch_counter) + 1u;
-  const PcPeers& gather = (epoch & 1u) ? gather1 : gather0;
-  const int cpr = slice_bytes >> 4;                          // 16-byte chunks per slice row
-  const size_t pitch = (size_t)world * slice_bytes;
-  const int stride = gridDim.x * blockDim.x;
-  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < rows * cpr; c += stride) {
+  const PcPeers& recv = (epoch & 1u) ? recv1 : recv0;
+  const int cpr = slice_bytes >> 4;                          // 16-byte payload chunks per slice row
+  const size_t out_pitch = (size_t)world * slice_bytes;
+  const int stride = gridDim.x * blockDim.x, tid = blockIdx.x * blockDim.x + threadIdx.x;
+  for (int c = tid; c < rows * cpr; c += stride) {
     const int m = c / cpr, j = c - m * cpr;
     const uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)c * 16);
-    const size_t off = (size_t)m * pitch + (size_t)rank * slice_bytes + (size_t)j * 16;
-    for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(gather.p[q]) + off) = v;
+    const size_t off = (((size_t)m * world + rank) * cpr + j) * 32;      // 32 wire bytes per payload chunk
+    for (int q = 0; q < world; ++q) {
+      if (q == rank) continue;
+      unsigned char* dst = static_cast<unsigned char*>(recv.p[q]) + off;
+      ll_store(dst, v.x, v.y, epoch);
+      ll_store(dst + 16, v.z, v.w, epoch);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)m * out_pitch + (size_t)rank * slice_bytes + (size_t)j * 16) = v;
   }
-  pc_publish_when_grid_done(block_counter, peer_flags, world, rank, epoch, epoch_counter);
-  if (!pc_wait_all(static_cast<const unsigned int*>(peer_flags.p[rank]), world, epoch, error_word, 7, &s_ok)) return;
-  const unsigned char* mine = static_cast<const unsigned char*>(gather.p[rank]);
-  const int total = static_cast<int>((size_t)rows * pitch >> 4);
-  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < total; c += stride)
-    *reinterpret_cast<uint4*>(out + (size_t)c * 16) = pc_ld_l2(mine + (size_t)c * 16);
+  LlWait w{pc_timer_ns(), true};
+  const unsigned char* mine = static_cast<const unsigned char*>(recv.p[rank]);
+  const int others = world - 1;
+  for (int c = tid; c < rows * others * cpr; c += stride) {
+    const int m = c / (others * cpr), rem = c - m * (others * cpr);
+    int r = rem / cpr;
+    const int j = rem - r * cpr;
+    r += (r >= rank);                                        // skip this rank's own slice
+    const unsigned char* p = mine + (((size_t)m * world + r) * cpr + j) * 32;
+    uint4 v;
+    ll_load(p, epoch, v.x, v.y, w);
+    ll_load(p + 16, epoch, v.z, v.w, w);
+    if (w.ok) *reinterpret_cast<uint4*>(out + (size_t)m * out_pitch + (size_t)r * slice_bytes + (size_t)j * 16) = v;
+  }
+  if (!w.ok && error_word) atomicExch(error_word, 7);
+  pc_count_call(block_counter, epoch_counter, epoch);
 }
 
-// ---- two-phase all-reduce of the row-parallel decode linear ---------------------------------------------
-// partial[parity][r]: rank r's fp32 partial sums [M][N] (announced by the decode kernel through `arrival`).
-// Phase 1: this rank adds the P partials of ITS N/P columns in rank order (+ bias), rounds to fp16 and stores
-// the slice into every rank's gather[parity][M][N].  Phase 2: wait for all slices, copy to y.  Every output
-// element is computed once, by its owner, so all ranks hold the same bits; a rank reads 4 M N (P-1)/P bytes
-// over NVLink instead of 4 M N (P-1).
-struct PcPartials {
-  const float* p[2][kPcMaxRanks];
-};
-
+// ---- all-reduce of the row-parallel decode linear: reduce-scatter, then all-gather, both flag-in-data -------
+// partial: this rank's fp32 partial sums [M][N] (written by the decode kernel that ran before on the stream).
+// Step 1: the columns that rank q owns (N / P of them) are sent to q's receive buffer
+//         recv1[parity][this rank][M][N / P] (8 wire bytes per sum).
+// Step 2: for its own columns this rank polls the P - 1 peers' sums, adds all P in rank order (+ bias), rounds
+//         to fp16, writes y and sends the fp16 pairs to every peer's recv2[parity][M][N] (8 wire bytes per pair).
+// Step 3: the other ranks' columns are polled out of recv2 into y.
+// Every output element is computed once, by its owner, in a fixed order: the same bits on all ranks.  A rank
+// sends 4 M N (P-1)/P * 2 bytes in step 1 and 2 M N (P-1)/P * 2 bytes in step 2, and waits twice for one
+// one-way flight -- no acknowledged fence, no arrival words.
 __global__ void __launch_bounds__(256)
-rowparallel_finish2_kernel(PcPartials partial, const unsigned int* __restrict__ arrival, PcPeers gather0, PcPeers gather1,
-                           PcPeers peer_flags2, const unsigned int* __restrict__ epoch_counter, int* block_counter,
-                           int world, int rank, int M, int N, const __half* __restrict__ bias, __half* __restrict__ y,
-                           int* error_word) {
-  __shared__ int s_ok;
+rowparallel_finish_ll_kernel(const float* __restrict__ partial0, const float* __restrict__ partial1, PcPeers recv1_0,
+                             PcPeers recv1_1, PcPeers recv2_0, PcPeers recv2_1,
+                             const unsigned int* __restrict__ epoch_counter, int world, int rank, int M, int N,
+                             const __half* __restrict__ bias, __half* __restrict__ y, int* error_word) {
   const unsigned int epoch = *epoch_counter;                 // advanced by the decode kernel that ran before this one
-  const float* const* src = partial.p[epoch & 1u];
-  const PcPeers& gather = (epoch & 1u) ? gather1 : gather0;
-  if (!pc_wait_all(arrival, world, epoch, error_word, 5, &s_ok)) return;
-  const int n_loc = N / world, quads = n_loc >> 2, n0 = rank * n_loc;
-  const int stride = gridDim.x * blockDim.x;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += stride) {
-    const int m = i / quads, n = n0 + ((i - m * quads) << 2);
-    float4 v[kPcMaxRanks];
-#pragma unroll
-    for (int r = 0; r < kPcMaxRanks; ++r)                    // all loads in flight before the first add
-      if (r < world) v[r] = *reinterpret_cast<const float4*>(src[r] + (size_t)m * N + n);
+  const float* partial = (epoch & 1u) ? partial1 : partial0;
+  const PcPeers& recv1 = (epoch & 1u) ? recv1_1 : recv1_0;
+  const PcPeers& recv2 = (epoch & 1u) ? recv2_1 : recv2_0;
+  const int n_loc = N / world, quads_loc = n_loc >> 2, quads = N >> 2;
+  const int stride = gridDim.x * blockDim.x, tid = blockIdx.x * blockDim.x + threadIdx.x;
+  // step 1: scatter the peers' columns
+  for (int i = tid; i < M * quads; i += stride) {
+    const int m = i / quads, n = (i - m * quads) << 2;
+    const int q = n / n_loc;
+    if (q == rank) continue;
+    const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)m * N + n);
+    unsigned char* dst = static_cast<unsigned char*>(recv1.p[q]) +
+                         (((size_t)rank * M + m) * n_loc + (n - q * n_loc)) * 8;
+    ll_store(dst, __float_as_uint(v.x), __float_as_uint(v.y), epoch);
+    ll_store(dst + 16, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
+  }
+  LlWait w{pc_timer_ns(), true};
+  // step 2: reduce this rank's columns
+  const unsigned char* in1 = static_cast<const unsigned char*>(recv1.p[rank]);
+  for (int i = tid; i < M * quads_loc; i += stride) {
+    const int m = i / quads_loc, nl = (i - m * quads_loc) << 2, n = rank * n_loc + nl;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int r = 0; r < kPcMaxRanks; ++r)
-      if (r < world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+    for (int r = 0; r < world; ++r) {
+      float4 v;
+      if (r == rank) {
+        v = *reinterpret_cast<const float4*>(partial + (size_t)m * N + n);
+      } else {
+        const unsigned char* p = in1 + (((size_t)r * M + m) * n_loc + nl) * 8;
+        uint32_t a, b, c, d;
+        ll_load(p, epoch, a, b, w);
+        ll_load(p + 16, epoch, c, d, w);
+        v = make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c), __uint_as_float(d));
+      }
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
     if (bias) {
       acc.x += h2f(bias[n]); acc.y += h2f(bias[n + 1]); acc.z += h2f(bias[n + 2]); acc.w += h2f(bias[n + 3]);
     }
-    const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
-    const uint2 o = make_uint2(h2_as_u32(lo), h2_as_u32(hi));
+    const uint32_t lo = h2_as_u32(__floats2half2_rn(acc.x, acc.y)), hi = h2_as_u32(__floats2half2_rn(acc.z, acc.w));
+    if (!w.ok) continue;                                     // a peer never showed up: send nothing half-made
+    *reinterpret_cast<uint2*>(y + (size_t)m * N + n) = make_uint2(lo, hi);
+    const size_t off = ((size_t)m * N + n) * 4;             // 8 wire bytes per fp16 pair
     for (int q = 0; q < world; ++q)
-      *reinterpret_cast<uint2*>(static_cast<__half*>(gather.p[q]) + (size_t)m * N + n) = o;
+      if (q != rank) ll_store(static_cast<unsigned char*>(recv2.p[q]) + off, lo, hi, epoch);
   }
-  pc_publish_when_grid_done(block_counter, peer_flags2, world, rank, epoch, nullptr);
-  if (!pc_wait_all(static_cast<const unsigned int*>(peer_flags2.p[rank]), world, epoch, error_word, 5, &s_ok)) return;
-  const unsigned char* mine = static_cast<const unsigned char*>(gather.p[rank]);
-  const int total = static_cast<int>((size_t)M * N * 2 >> 4);
-  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < total; c += stride)
-    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(y) + (size_t)c * 16) = pc_ld_l2(mine + (size_t)c * 16);
+  // step 3: collect the other ranks' columns
+  const unsigned char* in2 = static_cast<const unsigned char*>(recv2.p[rank]);
+  for (int i = tid; i < M * quads; i += stride) {
+    const int m = i / quads, n = (i - m * quads) << 2;
+    if (n / n_loc == rank) continue;
+    uint32_t lo, hi;
+    if (ll_load(in2 + ((size_t)m * N + n) * 4, epoch, lo, hi, w))
+      *reinterpret_cast<uint2*>(y + (size_t)m * N + n) = make_uint2(lo, hi);
+  }
+  if (!w.ok && error_word) atomicExch(error_word, 5);
 }
 
 // ---- publish: copy up to two local ranges into this rank's receive slot of the call's parity, then announce ---
@@ -230,10 +307,10 @@ int pc_fill(PcPeers& dst, const void* const* src, int world) {
   return MP_OK;
 }
 
-// few blocks: the waits inside the kernels assume the whole grid is resident
+// at most one block per SM: peers wait on what every block of the grid stores, so the whole grid is resident
 int pc_grid(int work_items) {
   int blocks = (work_items + 255) / 256;
-  return blocks < 1 ? 1 : (blocks > 32 ? 32 : blocks);
+  return blocks < 1 ? 1 : (blocks > kSmCount ? kSmCount : blocks);
 }
 
 }  // namespace
@@ -241,54 +318,56 @@ int pc_grid(int work_items) {
 
 using namespace mp;
 
-extern "C" int mp_peer_allgather_push(const void* src, int rows, int slice_bytes, void* const* peer_gather0,
-                                      void* const* peer_gather1, void* const* peer_flags_u32, void* epoch_counter_u32,
-                                      int* block_counter, int world, int rank, void* out, int* error_word,
-                                      mp_stream_t stream) {
+extern "C" size_t mp_peer_allgather_recv_bytes(int rows, int slice_bytes, int world) {
+  if (rows <= 0 || slice_bytes <= 0 || world <= 0) return 0;
+  return (size_t)rows * world * slice_bytes * 2;
+}
+
+extern "C" int mp_peer_allgather_push(const void* src, int rows, int slice_bytes, void* const* peer_recv0,
+                                      void* const* peer_recv1, void* epoch_counter_u32, int* block_counter, int world,
+                                      int rank, void* out, int* error_word, mp_stream_t stream) {
   if (!src || !out || !epoch_counter_u32 || !block_counter || rows <= 0 || slice_bytes <= 0) return MP_ERR_INVALID_ARG;
   if (rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
   if (slice_bytes % 16 != 0) return MP_ERR_UNSUPPORTED;
   if (!aligned(src, 16) || !aligned(out, 16)) return MP_ERR_ALIGNMENT;
-  PcPeers g0, g1, pf;
-  int rc = pc_fill(g0, peer_gather0, world);
+  PcPeers r0, r1;
+  int rc = pc_fill(r0, peer_recv0, world);
   if (rc != MP_OK) return rc;
-  if ((rc = pc_fill(g1, peer_gather1, world)) != MP_OK) return rc;
-  if ((rc = pc_fill(pf, peer_flags_u32, world)) != MP_OK) return rc;
-  const int grid = pc_grid(rows * (slice_bytes / 16) * world);
+  if ((rc = pc_fill(r1, peer_recv1, world)) != MP_OK) return rc;
+  const int grid = pc_grid(rows * (slice_bytes / 16) * (world > 1 ? world - 1 : 1));
   peer_allgather_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const unsigned char*>(src), rows, slice_bytes, g0, g1, pf, static_cast<unsigned int*>(epoch_counter_u32),
+      static_cast<const unsigned char*>(src), rows, slice_bytes, r0, r1, static_cast<unsigned int*>(epoch_counter_u32),
       block_counter, world, rank, static_cast<unsigned char*>(out), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }
 
-extern "C" int mp_w4a16_rowparallel_finish2(void* const* peer_partial0_f32, void* const* peer_partial1_f32,
-                                            const void* arrival_flags_u32, void* const* peer_gather0_f16,
-                                            void* const* peer_gather1_f16, void* const* peer_flags2_u32,
-                                            int* block_counter, int world, int rank, const void* epoch_counter_u32, int M,
-                                            int N, const void* bias_f16, void* y_f16, int* error_word,
-                                            mp_stream_t stream) {
-  if (!arrival_flags_u32 || !epoch_counter_u32 || !block_counter || !y_f16 || M <= 0 || N <= 0) return MP_ERR_INVALID_ARG;
+extern "C" size_t mp_w4a16_rowparallel_recv_bytes(int M, int N, int which) {
+  if (M <= 0 || N <= 0) return 0;
+  return which == 1 ? (size_t)M * N * 8 : (size_t)M * N * 4;
+}
+
+extern "C" int mp_w4a16_rowparallel_finish_ll(const void* partial0_f32, const void* partial1_f32,
+                                              void* const* peer_recv1_0, void* const* peer_recv1_1,
+                                              void* const* peer_recv2_0, void* const* peer_recv2_1, int world, int rank,
+                                              const void* epoch_counter_u32, int M, int N, const void* bias_f16,
+                                              void* y_f16, int* error_word, mp_stream_t stream) {
+  if (!partial0_f32 || !partial1_f32 || !epoch_counter_u32 || !y_f16 || M <= 0 || N <= 0) return MP_ERR_INVALID_ARG;
   if (rank < 0 || rank >= world) return MP_ERR_INVALID_ARG;
-  if (world > kPcMaxRanks || N % world != 0 || (N / world) % 4 != 0 || ((size_t)M * N * 2) % 16 != 0) return MP_ERR_UNSUPPORTED;
-  if (!aligned(y_f16, 16)) return MP_ERR_ALIGNMENT;
-  PcPeers p0, p1, g0, g1, pf2;
-  int rc = pc_fill(p0, peer_partial0_f32, world);
+  if (world > kPcMaxRanks || N % world != 0 || (N / world) % 4 != 0) return MP_ERR_UNSUPPORTED;
+  if (!aligned(y_f16, 8) || !aligned(partial0_f32, 16) || !aligned(partial1_f32, 16)) return MP_ERR_ALIGNMENT;
+  PcPeers a0, a1, b0, b1;
+  int rc = pc_fill(a0, peer_recv1_0, world);
   if (rc != MP_OK) return rc;
-  if ((rc = pc_fill(p1, peer_partial1_f32, world)) != MP_OK) return rc;
-  if ((rc = pc_fill(g0, peer_gather0_f16, world)) != MP_OK) return rc;
-  if ((rc = pc_fill(g1, peer_gather1_f16, world)) != MP_OK) return rc;
-  if ((rc = pc_fill(pf2, peer_flags2_u32, world)) != MP_OK) return rc;
-  PcPartials pp{};
-  for (int r = 0; r < world; ++r) {
-    pp.p[0][r] = static_cast<const float*>(p0.p[r]);
-    pp.p[1][r] = static_cast<const float*>(p1.p[r]);
-  }
-  const int grid = pc_grid(M * N / 8);
-  rowparallel_finish2_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      pp, static_cast<const unsigned int*>(arrival_flags_u32), g0, g1, pf2,
-      static_cast<const unsigned int*>(epoch_counter_u32), block_counter, world, rank, M, N,
-      static_cast<const __half*>(bias_f16), static_cast<__half*>(y_f16), error_word);
+  if ((rc = pc_fill(a1, peer_recv1_1, world)) != MP_OK) return rc;
+  if ((rc = pc_fill(b0, peer_recv2_0, world)) != MP_OK) return rc;
+  if ((rc = pc_fill(b1, peer_recv2_1, world)) != MP_OK) return rc;
+  int grid = (M * (N / 4) + 255) / 256;
+  if (grid > kSmCount) grid = kSmCount;                      // one resident wave: peers wait on every block's stores
+  rowparallel_finish_ll_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(partial0_f32), static_cast<const float*>(partial1_f32), a0, a1, b0, b1,
+      static_cast<const unsigned int*>(epoch_counter_u32), world, rank, M, N, static_cast<const __half*>(bias_f16),
+      static_cast<__half*>(y_f16), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

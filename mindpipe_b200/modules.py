@@ -55,8 +55,10 @@ class VllmPackedInt4Linear(nn.Module):
             raise ValueError(f"scale shape {tuple(self.weight_scale.shape)} does not divide in_features")
         self.group_size = self.in_features // int(self.weight_scale.shape[1])
         self._scale_zero = None   # kernel-side layout, built on first use
-        self._host_stage = {}     # row count -> (x, y) device staging buffers of forward_host
-        self._host_plans = {}     # (x_host ptr, y_host ptr, shape) -> validated raw call of forward_host
+        self._host_stage = {}     # (row count, stream) -> (x, y) device staging buffers of forward_host
+        self._host_plans = {}     # (x_host ptr, y_host ptr, shape, stream, weight-side ptrs) -> raw call of forward_host
+        self._derived_from = None  # (address, version) of every tensor _scale_zero was built from
+        self._register_load_state_dict_post_hook(VllmPackedInt4Linear._state_loaded)
 
     # -- construction -------------------------------------------------------
     @staticmethod
@@ -77,10 +79,26 @@ class VllmPackedInt4Linear(nn.Module):
                                     zero_point=zeros)
 
     # -- weights ------------------------------------------------------------
+    def _weight_side_state(self):
+        return tuple((t.data_ptr(), t._version) for t in (self.weight_scale, self.weight_zero_point) if t is not None)
+
     def process_weights_after_loading(self) -> None:
         """Build the group-major (scale, zero) buffer the GEMM kernels read."""
         self._scale_zero = ops.w4a16_prepare(self.weight_scale, self.weight_zero_point, self.in_features)
+        self._derived_from = self._weight_side_state()
         self._host_plans = {}            # they hold the old buffer's address
+
+    @staticmethod
+    def _state_loaded(module, incompatible_keys) -> None:
+        """``load_state_dict`` copied new scales / zero points into the buffers: the derived layout is stale."""
+        module._scale_zero = None
+        module._host_plans = {}
+
+    def _ensure_prepared(self) -> None:
+        """(Re)build the derived buffer when it is missing or when scales / zero points were replaced or
+        written in place since it was built (tensor version counters catch ``copy_`` and friends)."""
+        if self._scale_zero is None or self._derived_from != self._weight_side_state():
+            self.process_weights_after_loading()
 
     def dequantize(self) -> torch.Tensor:
         """fp16 ``[N, K]`` weights, bit-identical to the reference's fake-quant weight."""
@@ -96,8 +114,7 @@ class VllmPackedInt4Linear(nn.Module):
     # -- forward ------------------------------------------------------------
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self._scale_zero is None:
-            self.process_weights_after_loading()
+        self._ensure_prepared()
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         if not x2.is_contiguous():
@@ -109,13 +126,15 @@ class VllmPackedInt4Linear(nn.Module):
         """Decode (<= 16 rows) on a CPU fp16 tensor, as the reference's CPU forward takes it: the H2D
         copy, the kernel and the D2H copy are enqueued on ``stream`` (default: the current stream) and
         the call returns at once; read ``y_host`` after synchronising.  Staging buffers are kept per row
-        count, and a call that repeats an earlier one's buffers (same ``x_host`` / ``y_host`` storage, as
-        a serving loop with fixed pinned buffers does) skips the argument checks and goes straight to the
-        library."""
-        if self._scale_zero is None:
-            self.process_weights_after_loading()
+        count and stream (calls on different streams may overlap, so they do not share staging), and a call
+        that repeats an earlier one's buffers (same ``x_host`` / ``y_host`` storage, stream and weight-side
+        tensors, as a serving loop with fixed pinned buffers does) skips the argument checks and goes
+        straight to the library."""
+        self._ensure_prepared()
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
-        key = (x_host.data_ptr(), None if y_host is None else y_host.data_ptr(), tuple(x_host.shape))
+        key = (x_host.data_ptr(), None if y_host is None else y_host.data_ptr(), tuple(x_host.shape), st,
+               self.weight_packed.data_ptr(), self._scale_zero.data_ptr(),
+               None if self.bias is None else self.bias.data_ptr())
         plan = self._host_plans.get(key)
         if plan is not None:
             call, args, y_keep, shapes, _keep = plan
@@ -125,12 +144,12 @@ class VllmPackedInt4Linear(nn.Module):
                 _lib.check(status, "w4a16_linear_decode_host", **shapes)
             return y_keep
         m = x_host.shape[0]
-        stage = self._host_stage.get(m)
+        stage = self._host_stage.get((m, st))
         if stage is None:
             dev = self.weight_packed.device
             stage = (torch.empty((m, self.in_features), dtype=torch.float16, device=dev),
                      torch.empty((m, self.out_features), dtype=torch.float16, device=dev))
-            self._host_stage[m] = stage
+            self._host_stage[(m, st)] = stage
         if stream is None:
             y = ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias, y_host=y_host,
                                              x_stage=stage[0], y_stage=stage[1])
@@ -216,10 +235,18 @@ class SmoothQuantLinear(nn.Module):
         """fp32 copy of the per-channel scales, as the runtime method keeps
         (acceleration/runtime_patches/vllm_ascend.patch:4029-4031)."""
         self._weight_scale_fp32 = self.weight_scale.detach().flatten().to(torch.float32).contiguous()
+        self._derived_from = (self.weight_scale.data_ptr(), self.weight_scale._version)
 
     def _apply(self, fn, *args, **kwargs):
         self._weight_scale_fp32 = None
         return super()._apply(fn, *args, **kwargs)
+
+    def _ensure_prepared(self) -> None:
+        """Rebuild the fp32 scales when missing or when ``weight_scale`` was replaced, loaded
+        (``load_state_dict`` copies in place) or edited in place since they were derived."""
+        if self._weight_scale_fp32 is None or \
+                getattr(self, "_derived_from", None) != (self.weight_scale.data_ptr(), self.weight_scale._version):
+            self.process_weights_after_loading()
 
     def dequantize(self) -> torch.Tensor:
         """The reference's fake-quantised fp16 weight: ``f16(code * scale)``."""
@@ -229,8 +256,7 @@ class SmoothQuantLinear(nn.Module):
     def forward(self, x):
         """``x`` is an fp16 tensor, or a ``(int8 codes, per-token scale)`` pair produced upstream
         (the tuple input of AscendW8A8DynamicLinearMethod.apply, vllm_ascend.patch:3945-3962)."""
-        if self._weight_scale_fp32 is None:
-            self.process_weights_after_loading()
+        self._ensure_prepared()
         if isinstance(x, tuple):
             q, s = x
             lead = q.shape[:-1]

@@ -340,16 +340,32 @@ def _error_word(device: torch.device) -> torch.Tensor:
 
 
 def check_device_errors(device=None) -> None:
-    """Synchronise and raise if any kernel reported a device-side wait that gave up."""
+    """Synchronise and raise if any kernel reported a device-side wait that gave up.
+
+    A kernel that gave up leaves its arrival counters and partial sums as they were at that moment, so the
+    scratch buffers this module caches are cleared again before the error is raised and later calls start from
+    a clean state.  Scratch owned by the caller (``new_workspace``) must be zeroed by the caller, and the
+    tensor- and expert-parallel modules, whose call numbers and arrival words are spread over the ranks, must
+    be rebuilt on every rank after such an error."""
     torch.cuda.synchronize(device)
     import ctypes
+
+    def rearm(index=None):
+        with _ws_lock:
+            for (dev_index, _stream_id, _kind), ws in _workspaces.items():
+                if index is None or dev_index == index:
+                    ws.zero_()
+        torch.cuda.synchronize(device)
+
     flag = ctypes.c_int(0)
     _lib.check(_lib.load().mp_read_decode_error(ctypes.byref(flag)), "read_decode_error")
     if flag.value != 0:
+        rearm()
         raise _lib.MindPipeKernelError("a bounded wait inside a decode kernel timed out")
     for idx, w in _err_words.items():
         if int(w.item()) != 0:
             w.zero_()
+            rearm(idx)
             raise _lib.MindPipeKernelError(f"device {idx}: a bounded wait inside a tensor-core kernel timed out")
 
 

@@ -6,14 +6,15 @@ Rank ``r`` of ``P`` holds columns ``[r*K/P, (r+1)*K/P)`` of the weight (tensor p
 row-parallel kind, what a serving runtime does for ``down_proj`` / ``o_proj``; the reference computes
 the unsharded ``nn.Linear``, algorithm/quantization/ptq/awq/source/awq/quantize/quantizer.py:109-130).
 
-The exchange is driven from the device: the decode kernel leaves its fp32 partial sums in a peer-mapped
-buffer (``torch.distributed._symmetric_memory``) and its last block raises an arrival word on every
-peer; a small second kernel waits for all arrival words and adds the ``P`` buffers in rank order --
-either everything on every rank (one-shot: each rank reads ``4 M N (P-1)`` bytes over NVLink), or, in
-the two-phase form used from four ranks up, each rank only its ``N / P`` columns, whose fp16 result it
-stores to every peer (``1 / P`` of the reads, one more round of arrival words).  Either way all ranks
-end with bit-identical fp16 outputs, and no NCCL call, barrier kernel or host synchronisation sits on
-the path.  ``forward_nccl`` is the plain fallback (local linear + ``all_reduce``) for process groups
+The exchange is driven from the device, over peer-mapped memory (``torch.distributed._symmetric_memory``).
+The decode kernel leaves its fp32 partial sums in a local buffer; a small second kernel then adds the ``P``
+partial sums in rank order, in one of two forms.  Two-phase (the default): every rank sends each peer the
+partial sums of the columns that peer owns, adds the ``P`` contributions to its own ``N / P`` columns, and
+sends the fp16 result to everyone; every 8 bytes on the wire carry 4 bytes of payload and the call number,
+so receivers poll the data itself and the all-reduce costs two one-way NVLink flights.  One-shot: the
+decode kernel's last block raises an arrival word on every peer and every rank reads all ``P`` buffers
+(``4 M N (P-1)`` bytes over NVLink, after an acknowledged fence).  Either way all ranks end with
+bit-identical fp16 outputs, and no NCCL call, barrier kernel or host synchronisation sits on the path.  ``forward_nccl`` is the plain fallback (local linear + ``all_reduce``) for process groups
 without peer mappings.
 """
 from __future__ import annotations
@@ -82,35 +83,40 @@ class RowParallelW4A16Linear(torch.nn.Module):
             raise ValueError("the local shard must not carry the bias (it would be added once per rank)")
         self.bias = bias
         self.symmetric = bool(symmetric)
-        # two-phase (reduce own columns, then exchange fp16 slices) pays once the one-shot reads outweigh a
-        # second round of arrival words; it needs N to split into 4-column units per rank
+        # two-phase (reduce own columns, then exchange fp16 slices) needs N to split into 4-column units per rank
         can_split = self.out_features % (4 * self.world) == 0
-        self.two_phase = (self.world >= 4 if two_phase is None else bool(two_phase)) and can_split
+        self.two_phase = (True if two_phase is None else bool(two_phase)) and can_split
         if self.symmetric:
             self._setup_symmetric()
 
     def _setup_symmetric(self):
         import torch.distributed._symmetric_memory as symm
+        from . import _lib
         dev = self.local.weight_packed.device
         self.slot_bytes = self.max_rows * self.out_features * 4                      # one [m_cap][N] fp32 buffer
         self.off_partial = 256                                                        # arrival words first
-        self.gather_bytes = (self.max_rows * self.out_features * 2 + 255) // 256 * 256   # one [m_cap][N] fp16 buffer
-        self.off_gather = self.off_partial + 2 * self.slot_bytes
-        total = self.off_gather + 2 * self.gather_bytes
+        lib = _lib.load()
+        up = lambda v: (int(v) + 255) // 256 * 256
+        self.recv1_bytes = up(lib.mp_w4a16_rowparallel_recv_bytes(self.max_rows, self.out_features, 1))
+        self.recv2_bytes = up(lib.mp_w4a16_rowparallel_recv_bytes(self.max_rows, self.out_features, 2))
+        self.off_recv1 = self.off_partial + 2 * self.slot_bytes
+        self.off_recv2 = self.off_recv1 + 2 * self.recv1_bytes
+        total = self.off_recv2 + 2 * self.recv2_bytes
         self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
-        self.buf.zero_()
+        self.buf.zero_()                                                              # call numbers start at 1
         torch.cuda.synchronize(dev)
         self.handle = symm.rendezvous(self.buf, self.group)
         dist.barrier(self.group)                                                      # every rank zeroed its words
         bases = [int(p) for p in self.handle.buffer_ptrs]
         self.p_flags = (ctypes.c_void_p * self.world)(*bases)
+        self.p_flags_self = (ctypes.c_void_p * 1)(bases[self.rank])
         self.p_partial = [(ctypes.c_void_p * self.world)(*[b + self.off_partial + par * self.slot_bytes for b in bases])
                           for par in range(2)]
-        self.p_flags2 = (ctypes.c_void_p * self.world)(*[b + 128 for b in bases])    # second round of arrival words
-        self.p_gather = [(ctypes.c_void_p * self.world)(*[b + self.off_gather + par * self.gather_bytes for b in bases])
-                         for par in range(2)]
+        self.p_recv1 = [(ctypes.c_void_p * self.world)(*[b + self.off_recv1 + par * self.recv1_bytes for b in bases])
+                        for par in range(2)]
+        self.p_recv2 = [(ctypes.c_void_p * self.world)(*[b + self.off_recv2 + par * self.recv2_bytes for b in bases])
+                        for par in range(2)]
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)     # blocks of the running call that have stored
-        self.counter2 = torch.zeros(1, dtype=torch.int32, device=dev)    # same, for the two-phase finish kernel
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)       # calls completed (advanced by the kernel)
 
     @staticmethod
@@ -134,23 +140,24 @@ class RowParallelW4A16Linear(torch.nn.Module):
         m, k_loc = x2.shape
         if m > self.max_rows or k_loc != self.local.in_features:
             raise ValueError(f"x_local must be [<= {self.max_rows}, {self.local.in_features}], got {tuple(x2.shape)}")
-        if self.local._scale_zero is None:
-            self.local.process_weights_after_loading()
+        self.local._ensure_prepared()
         stream = torch.cuda.current_stream().cuda_stream
         y = torch.empty((m, self.out_features), dtype=torch.float16, device=x2.device)
         mine = self.buf.data_ptr() + self.off_partial
+        # the two-phase finish polls the data itself, so the decode kernel announces to nobody but this rank
+        flags, world, rank = (self.p_flags_self, 1, 0) if self.two_phase else (self.p_flags, self.world, self.rank)
         st = lib.mp_w4a16_rowparallel_push(x2.data_ptr(), self.local.weight_packed.data_ptr(),
                                            self.local._scale_zero.data_ptr(), mine, mine + self.slot_bytes,
-                                           self.p_flags, self.counter.data_ptr(), self.epoch.data_ptr(), self.world,
-                                           self.rank, m, self.out_features, k_loc, self.local.group_size, stream)
+                                           flags, self.counter.data_ptr(), self.epoch.data_ptr(), world,
+                                           rank, m, self.out_features, k_loc, self.local.group_size, stream)
         _lib.check(st, "w4a16_rowparallel_push", M=m, N=self.out_features, K_local=k_loc)
         bias = None if self.bias is None else self.bias.data_ptr()
         err = ops._error_word(x2.device).data_ptr()
-        if self.two_phase and (m * self.out_features * 2) % 16 == 0:
-            st = lib.mp_w4a16_rowparallel_finish2(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(),
-                                                  self.p_gather[0], self.p_gather[1], self.p_flags2,
-                                                  self.counter2.data_ptr(), self.world, self.rank, self.epoch.data_ptr(),
-                                                  m, self.out_features, bias, y.data_ptr(), err, stream)
+        if self.two_phase:
+            st = lib.mp_w4a16_rowparallel_finish_ll(mine, mine + self.slot_bytes, self.p_recv1[0], self.p_recv1[1],
+                                                    self.p_recv2[0], self.p_recv2[1], self.world, self.rank,
+                                                    self.epoch.data_ptr(), m, self.out_features, bias, y.data_ptr(), err,
+                                                    stream)
         else:
             st = lib.mp_w4a16_rowparallel_finish(self.p_partial[0], self.p_partial[1], self.buf.data_ptr(), self.world,
                                                  self.epoch.data_ptr(), m, self.out_features, bias, y.data_ptr(), err,

@@ -1,12 +1,12 @@
 """Generate the golden fixtures in this directory from the reference itself.
 
 Run once, in a container where the MindPipe reference checkout is present
-(``MINDPIPE_REFERENCE`` or the default below).  The script imports the
+(its path in ``MINDPIPE_REFERENCE``).  The script imports the
 reference's own functions (nothing is copied), feeds them small seeded
 inputs and stores inputs and outputs as ``.npz`` files.  The fixtures are
 committed, so the tests never need the reference at run time.
 
-    python tests/golden/make_golden.py
+    MINDPIPE_REFERENCE=<path to the reference checkout> python tests/golden/make_golden.py
 """
 from __future__ import annotations
 
@@ -19,7 +19,9 @@ from types import SimpleNamespace
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("MINDPIPE_REFERENCE", "/root/reference"))
+if "MINDPIPE_REFERENCE" not in os.environ:
+    sys.exit("set MINDPIPE_REFERENCE to a checkout of the reference project")
+REF = Path(os.environ["MINDPIPE_REFERENCE"])
 OUT = Path(__file__).resolve().parent
 sys.dont_write_bytecode = True
 for sub in ("", "algorithm/quantization/ptq/awq/source", "algorithm/quantization/ptq/smoothquant/source",

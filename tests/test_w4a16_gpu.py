@@ -2,7 +2,7 @@
 
 Bit-exact: packed codes, scales, zero points, dequantised weights.
 fp16 outputs: relative Frobenius error <= 1e-2 against the oracle's
-``F.linear(x, Wdq)`` (the bound the north star states; observed ~1e-3).
+``F.linear(x, Wdq)`` (observed ~1e-3).
 """
 import numpy as np
 import pytest
@@ -187,6 +187,30 @@ def test_host_buffer_entry_matches_device_entry(m):
         mod.forward_host(x_host.cuda(), y_host)
     with pytest.raises(RuntimeError):
         mod.forward_host(synth.normal_activation(17, k, seed=3).pin_memory())
+
+
+def test_derived_buffers_follow_load_state_dict_and_in_place_updates():
+    """The kernel-side (scale, zero) layout and the remembered host calls are rebuilt when the scales change
+    under the module: through ``load_state_dict`` (copies in place) and through a plain in-place write."""
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    n, k = 256, 512
+    a = VllmPackedInt4Linear.from_float(torch.nn.Linear(k, n, bias=False).half().cuda())
+    b = VllmPackedInt4Linear.from_float(torch.nn.Linear(k, n, bias=False).half().cuda())
+    x = synth.normal_activation(4, k, seed=12).cuda()
+    x_host, y_host = x.cpu().pin_memory(), torch.empty((4, n), dtype=torch.float16).pin_memory()
+    want_b = b(x)
+    assert not torch.equal(a(x), want_b)                   # derived buffer of a's own weights now exists
+    a.forward_host(x_host, y_host)
+    a.forward_host(x_host, y_host)                         # the remembered raw call
+    a.load_state_dict(b.state_dict())
+    assert torch.equal(a(x), want_b)
+    a.forward_host(x_host, y_host)
+    torch.cuda.synchronize()
+    assert torch.equal(y_host.cuda(), want_b)
+    a.weight_scale.mul_(2)                                 # in place: scales doubled, zero points kept
+    assert torch.equal(a(x), VllmPackedInt4Linear(packed_weight=b.weight_packed, scale=b.weight_scale * 2, bias=None,
+                                                  in_features=k, out_features=n,
+                                                  zero_point=b.weight_zero_point)(x))
 
 
 def test_errors_are_loud():
