@@ -58,7 +58,7 @@ class VllmPackedInt4Linear(nn.Module):
         self._host_stage = {}     # (row count, stream) -> (x, y) device staging buffers of forward_host
         self._host_plans = {}     # (x_host ptr, y_host ptr, shape, stream, weight-side ptrs) -> raw call of forward_host
         self._derived_from = None  # (address, version) of every tensor _scale_zero was built from
-        self._register_load_state_dict_post_hook(VllmPackedInt4Linear._state_loaded)
+        self.register_load_state_dict_post_hook(VllmPackedInt4Linear._state_loaded)
 
     # -- construction -------------------------------------------------------
     @staticmethod
