@@ -655,11 +655,11 @@ def run_ours(args, rank, world, local_rank):
 
     moe_extra = extra(measure_moe, world, rank, dev, dist) if args.moe else None
     tp_extra = col_extra = None
-    if args.moe and world > 1:            # the sharded 70B linears
+    if args.tp and world > 1:             # the sharded 70B linears
         tp_extra = extra(measure_row_parallel, world, rank, dev, dist)
         col_extra = extra(measure_column_parallel, world, rank, dev, dist)
     configs_extra = None
-    if args.moe and world == 1 and rank == 0:
+    if args.configs and world == 1 and rank == 0:
         configs_extra = extra(measure_other_configs, args, local_rank)
 
     if rank == 0:
@@ -959,6 +959,8 @@ def main():
     ap.add_argument("--concurrent", type=int, default=1,
                     help="run q/k/v and gate/up of a layer on parallel streams inside the captured step")
     ap.add_argument("--moe", type=int, default=1, help="also measure the expert-parallel MoE layer (extra key)")
+    ap.add_argument("--tp", type=int, default=1, help="on N > 1: also measure the tensor-parallel 70B-shaped linears (extra keys)")
+    ap.add_argument("--configs", type=int, default=1, help="on N = 1: also measure the other configs (extra key)")
     ap.add_argument("--suite", default="", help="comma list of extra per-kernel lines: decode,prefill,w8a8,moe,all")
     ap.add_argument("--suite-only", action="store_true", help="skip the headline workload")
     ap.add_argument("--decode-kernel", default="default", choices=["default", "auto", "umma", "mma_sync"],
