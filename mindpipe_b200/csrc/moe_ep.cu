@@ -123,34 +123,97 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
   *num_tiles = tiles;
 }
 
-// Sorted row i <- peer row (int8 codes and fp32 scale).  Blocks stride over the rows in use.
+// The part of the extended plan that ep_locate reads (segment offsets, per-source cumulative counts, source
+// segment starts), copied to shared memory once per block: a row's home is then found without a chain of
+// dependent global loads in front of every row copy.
+constexpr int kEpLocateInts = 2 * 64 + 1 + 64 * (kMaxRanks + 1) + 64 * kMaxRanks;   // up to 64 local experts
+
+struct EpLocator {
+  const int* seg;       // [e_loc + 1]
+  const int* cum;       // [e_loc][world + 1]
+  const int* src_seg;   // [e_loc][world]
+  int world, e_loc;
+  __device__ __forceinline__ bool locate(int i, int& s_out, int& src_row) const {
+    if (i >= seg[e_loc]) return false;
+    int e = 0;
+    while (e + 1 < e_loc && i >= seg[e + 1]) ++e;
+    const int j = i - seg[e];
+    if (j >= cum[e * (world + 1) + world]) return false;
+    int s = 0;
+    while (s + 1 < world && j >= cum[e * (world + 1) + s + 1]) ++s;
+    s_out = s;
+    src_row = src_seg[e * world + s] + (j - cum[e * (world + 1) + s]);
+    return true;
+  }
+};
+
+__device__ __forceinline__ EpLocator ep_cache_plan(const int* __restrict__ xplan, int world, int e_loc, int ext, int* s_buf) {
+  int* s_seg = s_buf;
+  int* s_cum = s_seg + e_loc + 1;
+  int* s_src = s_cum + e_loc * (world + 1);
+  for (int i = threadIdx.x; i <= e_loc; i += blockDim.x) s_seg[i] = xplan[2 * e_loc + i];
+  for (int i = threadIdx.x; i < e_loc * (world + 1); i += blockDim.x) s_cum[i] = xplan[ext + i];
+  for (int i = threadIdx.x; i < e_loc * world; i += blockDim.x) s_src[i] = xplan[ext + e_loc * (world + 1) + i];
+  __syncthreads();
+  return EpLocator{s_seg, s_cum, s_src, world, e_loc};
+}
+
+// Sorted row i <- peer row (int8 codes and fp32 scale).  One warp per row: a lane requests all its 16-byte
+// pieces of the row before it stores the first, so a row costs one NVLink round trip; warps stride over the
+// rows in use.  VPL = 16-byte pieces per lane.
+template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xplan, int world, int e_loc, int ext,
                int vec_per_row, uint4* __restrict__ q_sorted, float* __restrict__ s_sorted) {
-  const int rows = xplan[2 * e_loc + e_loc];                        // seg[e_loc]: padded rows in use
-  for (int i = blockIdx.x; i < rows; i += gridDim.x) {
+  __shared__ int s_plan[kEpLocateInts];
+  const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
+  const int rows = loc.seg[e_loc];                                  // padded rows in use
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
     int s, src;
-    const bool real = ep_locate(xplan, world, e_loc, ext, i, s, src);
-    if (!real) {
-      if (threadIdx.x == 0) s_sorted[i] = 0.0f;                     // padding row: neutralised by a zero scale
+    if (!loc.locate(i, s, src)) {
+      if (lane == 0) s_sorted[i] = 0.0f;                            // padding row: neutralised by a zero scale
       continue;
     }
     const uint4* from = static_cast<const uint4*>(peer_q.p[s]) + (size_t)src * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += 256) q_sorted[(size_t)i * vec_per_row + v] = from[v];
-    if (threadIdx.x == 0) s_sorted[i] = static_cast<const float*>(peer_scale.p[s])[src];
+    uint4* to = q_sorted + (size_t)i * vec_per_row;
+    if (VPL > 0) {
+      uint4 v[VPL > 0 ? VPL : 1];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) v[j] = from[lane + 32 * j];
+      if (lane == 0) s_sorted[i] = static_cast<const float*>(peer_scale.p[s])[src];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) to[lane + 32 * j] = v[j];
+    } else {
+      for (int v = lane; v < vec_per_row; v += 32) to[v] = from[v];
+      if (lane == 0) s_sorted[i] = static_cast<const float*>(peer_scale.p[s])[src];
+    }
   }
 }
 
-// Result row i -> the source rank's result buffer, at the row's original position.
+// Result row i -> the source rank's result buffer, at the row's original position; one warp per row.
+template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const uint4* __restrict__ d_sorted, const int* __restrict__ xplan, int world, int e_loc, int ext,
                int vec_per_row, PeerPtrs peer_back) {
-  const int rows = xplan[2 * e_loc + e_loc];
-  for (int i = blockIdx.x; i < rows; i += gridDim.x) {
+  __shared__ int s_plan[kEpLocateInts];
+  const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
+  const int rows = loc.seg[e_loc];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
     int s, src;
-    if (!ep_locate(xplan, world, e_loc, ext, i, s, src)) continue;
+    if (!loc.locate(i, s, src)) continue;
+    const uint4* from = d_sorted + (size_t)i * vec_per_row;
     uint4* to = static_cast<uint4*>(peer_back.p[s]) + (size_t)src * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += 256) to[v] = d_sorted[(size_t)i * vec_per_row + v];
+    if (VPL > 0) {
+      uint4 v[VPL > 0 ? VPL : 1];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) v[j] = from[lane + 32 * j];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) to[lane + 32 * j] = v[j];
+    } else {
+      for (int v = lane; v < vec_per_row; v += 32) to[v] = from[v];
+    }
   }
 }
 
@@ -344,10 +407,18 @@ extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const*
   rc = fill_peers(ps, peer_scale_ptrs, world);
   if (rc != MP_OK) return rc;
   if (!xplan_i32 || !q_sorted_i8 || !scale_sorted_f32 || H <= 0 || H % 16 != 0) return MP_ERR_INVALID_ARG;
+  if (num_local_experts > 64) return MP_ERR_UNSUPPORTED;           // the locate tables are staged in shared memory
   const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
-  ep_pull_kernel<<<16 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      pq, ps, static_cast<const int*>(xplan_i32), world, num_local_experts, ext, H / 16,
-      static_cast<uint4*>(q_sorted_i8), static_cast<float*>(scale_sorted_f32));
+  const int vec = H / 16;
+  int grid = (capacity_rows + 7) / 8;                               // one warp per row, at most four blocks per SM
+  if (grid > 4 * kSmCount) grid = 4 * kSmCount;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int* xp = static_cast<const int*>(xplan_i32);
+  uint4* qd = static_cast<uint4*>(q_sorted_i8);
+  float* sd = static_cast<float*>(scale_sorted_f32);
+  if (vec == 256) ep_pull_kernel<8><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
+  else if (vec == 128) ep_pull_kernel<4><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
+  else ep_pull_kernel<0><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }
@@ -358,10 +429,17 @@ extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, i
   int rc = fill_peers(pb, peer_back_ptrs, world);
   if (rc != MP_OK) return rc;
   if (!d_sorted_f16 || !xplan_i32 || H <= 0 || H % 8 != 0) return MP_ERR_INVALID_ARG;
+  if (num_local_experts > 64) return MP_ERR_UNSUPPORTED;
   const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
-  ep_push_kernel<<<16 * kSmCount, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(d_sorted_f16), static_cast<const int*>(xplan_i32), world, num_local_experts, ext,
-      H / 8, pb);
+  const int vec = H / 8;
+  int grid = (capacity_rows + 7) / 8;
+  if (grid > 4 * kSmCount) grid = 4 * kSmCount;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint4* dd = static_cast<const uint4*>(d_sorted_f16);
+  const int* xp = static_cast<const int*>(xplan_i32);
+  if (vec == 512) ep_push_kernel<16><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
+  else if (vec == 256) ep_push_kernel<8><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
+  else ep_push_kernel<0><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

@@ -15,6 +15,8 @@
 
 namespace mp {
 
+bool decode_programmatic_launch();   // w4a16_decode_tma.cu: the process-wide programmatic-dependent-launch switch
+
 namespace {
 
 constexpr int kPcMaxRanks = 16;
@@ -123,6 +125,10 @@ __global__ void __launch_bounds__(256)
 peer_allgather_push_kernel(const unsigned char* __restrict__ src, int rows, int slice_bytes, PcPeers recv0,
                            PcPeers recv1, unsigned int* epoch_counter, int* block_counter, int world, int rank,
                            unsigned char* __restrict__ out, int* error_word) {
+  // under programmatic dependent launch: wait for the producer of `src`, then let the next kernel of the stream
+  // begin its own prologue (e.g. a decode linear's weight fetch) while this one is on the wire
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(epoch_counter) + 1u;
   const PcPeers& recv = (epoch & 1u) ? recv1 : recv0;
   const int cpr = slice_bytes >> 4;                          // 16-byte payload chunks per slice row
@@ -173,6 +179,8 @@ rowparallel_finish_ll_kernel(const float* __restrict__ partial0, const float* __
                              PcPeers recv1_1, PcPeers recv2_0, PcPeers recv2_1,
                              const unsigned int* __restrict__ epoch_counter, int world, int rank, int M, int N,
                              const __half* __restrict__ bias, __half* __restrict__ y, int* error_word) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");         // the decode kernel's partial sums and call number
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const unsigned int epoch = *epoch_counter;                 // advanced by the decode kernel that ran before this one
   const float* partial = (epoch & 1u) ? partial1 : partial0;
   const PcPeers& recv1 = (epoch & 1u) ? recv1_1 : recv1_0;
@@ -307,6 +315,26 @@ int pc_fill(PcPeers& dst, const void* const* src, int world) {
   return MP_OK;
 }
 
+
+
+// Launch with the programmatic-stream-serialization attribute when the switch is on: the kernel may then be
+// scheduled while the previous kernel of the stream drains (it waits for it with griddepcontrol.wait).
+template <typename... KArgs, typename... Args>
+int pc_launch(void (*kernel)(KArgs...), int grid, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = decode_programmatic_launch() ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+  return MP_OK;
+}
+
 // at most one block per SM: peers wait on what every block of the grid stores, so the whole grid is resident
 int pc_grid(int work_items) {
   int blocks = (work_items + 255) / 256;
@@ -335,11 +363,10 @@ extern "C" int mp_peer_allgather_push(const void* src, int rows, int slice_bytes
   if (rc != MP_OK) return rc;
   if ((rc = pc_fill(r1, peer_recv1, world)) != MP_OK) return rc;
   const int grid = pc_grid(rows * (slice_bytes / 16) * (world > 1 ? world - 1 : 1));
-  peer_allgather_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const unsigned char*>(src), rows, slice_bytes, r0, r1, static_cast<unsigned int*>(epoch_counter_u32),
-      block_counter, world, rank, static_cast<unsigned char*>(out), error_word);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return pc_launch(peer_allgather_push_kernel, grid, static_cast<cudaStream_t>(stream),
+                   static_cast<const unsigned char*>(src), rows, slice_bytes, r0, r1,
+                   static_cast<unsigned int*>(epoch_counter_u32), block_counter, world, rank,
+                   static_cast<unsigned char*>(out), error_word);
 }
 
 extern "C" size_t mp_w4a16_rowparallel_recv_bytes(int M, int N, int which) {
@@ -364,12 +391,10 @@ extern "C" int mp_w4a16_rowparallel_finish_ll(const void* partial0_f32, const vo
   if ((rc = pc_fill(b1, peer_recv2_1, world)) != MP_OK) return rc;
   int grid = (M * (N / 4) + 255) / 256;
   if (grid > kSmCount) grid = kSmCount;                      // one resident wave: peers wait on every block's stores
-  rowparallel_finish_ll_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(partial0_f32), static_cast<const float*>(partial1_f32), a0, a1, b0, b1,
-      static_cast<const unsigned int*>(epoch_counter_u32), world, rank, M, N, static_cast<const __half*>(bias_f16),
-      static_cast<__half*>(y_f16), error_word);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return pc_launch(rowparallel_finish_ll_kernel, grid, static_cast<cudaStream_t>(stream),
+                   static_cast<const float*>(partial0_f32), static_cast<const float*>(partial1_f32), a0, a1, b0, b1,
+                   static_cast<const unsigned int*>(epoch_counter_u32), world, rank, M, N,
+                   static_cast<const __half*>(bias_f16), static_cast<__half*>(y_f16), error_word);
 }
 
 extern "C" int mp_peer_publish(const void* src_a, int bytes_a, int offset_a, const void* src_b, int bytes_b, int offset_b,
