@@ -516,7 +516,7 @@ def run_ours(args, rank, world, local_rank):
     ws_bytes = max(ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) for _, (n, k) in layer_shapes())
     # one scratch buffer per linear: with --fuse 0 --concurrent 1 some of them run side by side
     ws = {name: ops.new_workspace(ws_bytes, dev) for name, _ in layer_shapes()}
-    umma_names = [name for name, (n, k) in layer_shapes() if ops.w4a16_decode_workspace_bytes(M_DECODE, n, k) > 0]
+    umma_names = [name for name, (n, k) in layer_shapes() if ops.w4a16_decode_kernel_choice(M_DECODE, n, k) == "umma"]
     tma_names = [name for name, _ in layer_shapes() if name not in umma_names]
     kernel_names = " + ".join(
         f"{kern} ({', '.join(names)})" for kern, names in (("w4a16_decode_umma_kernel", umma_names),

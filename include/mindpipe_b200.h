@@ -227,6 +227,9 @@ int mp_set_programmatic_launch(int enabled);
 #define MP_DECODE_KERNEL_UMMA 1
 #define MP_DECODE_KERNEL_AUTO 2
 int mp_set_decode_kernel(int kind);
+/* Which kernel (MP_DECODE_KERNEL_MMA_SYNC or _UMMA) the process default sends a decode call of this shape to
+ * (1 <= M <= 16), with or without a workspace; shapes the chosen kernel does not take still fall through. */
+int mp_w4a16_decode_kernel_choice(int M, int N, int K, int have_workspace);
 
 /*
  * mp_w4a16_linear_decode for M <= 16 with the kernel and programmatic dependent

@@ -42,6 +42,7 @@ SIGNATURES = {
     "mp_w4a16_linear_decode_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_set_programmatic_launch": (_I, [_I]),
     "mp_set_decode_kernel": (_I, [_I]),
+    "mp_w4a16_decode_kernel_choice": (_I, [_I, _I, _I, _I]),
     "mp_read_decode_error": (_I, [_P]),
     "mp_act_quant_per_token": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "mp_add_rmsnorm_quant": (_I, [_P, _P, _P, ctypes.c_float, _I, _I, _P, _P, _P]),

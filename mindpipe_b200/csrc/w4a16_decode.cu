@@ -735,6 +735,11 @@ extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32,
                                    workspace_bytes, 0, stream);
 }
 
+extern "C" int mp_w4a16_decode_kernel_choice(int M, int N, int K, int have_workspace) {
+  if (M <= 0 || M > 16 || N <= 0 || K <= 0) return MP_ERR_INVALID_ARG;
+  return decode_kernel_for(g_decode_kernel, M, N, K, have_workspace != 0);
+}
+
 extern "C" int mp_set_decode_kernel(int kind) {
   if (kind != MP_DECODE_KERNEL_MMA_SYNC && kind != MP_DECODE_KERNEL_UMMA && kind != MP_DECODE_KERNEL_AUTO)
     return MP_ERR_INVALID_ARG;

@@ -70,6 +70,13 @@ def w4a16_decode_workspace_bytes(m: int, n: int, k: int, k_split: int = 0) -> in
     return int(_lib.load().mp_w4a16_decode_workspace_bytes_ex(m, n, k, k_split))
 
 
+def w4a16_decode_kernel_choice(m: int, n: int, k: int, have_workspace: bool = True) -> str:
+    """Name of the kernel the process default picks for a decode call of this shape (1 <= m <= 16)."""
+    kind = _lib.load().mp_w4a16_decode_kernel_choice(m, n, k, 1 if have_workspace else 0)
+    _lib.check(min(kind, 0), "w4a16_decode_kernel_choice", M=m, N=n, K=k)
+    return {0: "mma_sync", 1: "umma"}[kind]
+
+
 # ------------------------------------------------------------------ W4A16
 def w4a16_quantize(weight: torch.Tensor, group_size: int = 128):
     """Asymmetric int4 group quantisation + packing of ``weight[N,K]`` (fp16).

@@ -88,6 +88,12 @@ def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
         assert ops.set_decode_kernel("auto") == "mma_sync"
         with pytest.raises(ValueError, match="unknown decode kernel"):
             ops.set_decode_kernel("wgmma")
+        # the default rule: the tcgen05 kernel for 9..16 tokens on 70B-sized weights with a workspace, else mma.sync
+        assert ops.w4a16_decode_kernel_choice(16, 22016, 4096) == "umma"
+        assert ops.w4a16_decode_kernel_choice(16, 22016, 4096, have_workspace=False) == "mma_sync"
+        assert ops.w4a16_decode_kernel_choice(8, 22016, 4096) == "mma_sync"
+        assert ops.w4a16_decode_kernel_choice(16, 4096, 4096) == "mma_sync"
+        assert lib.mp_w4a16_decode_kernel_choice(17, 4096, 4096, 1) < 0
         assert ops.decode_options() == 0
         assert ops.decode_options(kernel="umma", pdl=True) == 0x2 | 0x10
         assert ops.decode_options(kernel="mma_sync", pdl=False) == 0x1 | 0x20
