@@ -31,6 +31,27 @@ def test_registration_is_idempotent_and_fake_impls_give_shapes():
         assert q.shape == (4, 9, 48) and q.dtype == torch.int8 and s.shape == (4, 9) and s.dtype == torch.float32
 
 
+def test_loop_out_argument_checks_precede_any_device_work():
+    """The bridge's checks (aclnn_grouped_swiglu_out_bridge.cpp:166-199) fire on the host before a kernel is
+    looked up, so they can be exercised without a GPU."""
+    from mindpipe_b200 import ops
+    bw, bs = torch.zeros(2, 128, 96, dtype=torch.int8), torch.zeros(2, 96)
+    x, xs, gl = torch.zeros(4, 128, dtype=torch.int8), torch.zeros(4), torch.tensor([4], dtype=torch.int64)
+    views, sviews = [bw[i:i + 1] for i in range(2)], [bs[i:i + 1] for i in range(2)]
+    with pytest.raises(RuntimeError, match="non-empty"):
+        ops.grouped_swiglu_loop_out(x, [], bw, gl, [], bs, xs, 64, 0)
+    with pytest.raises(RuntimeError, match="chunk count"):
+        ops.grouped_swiglu_loop_out(x, views[:1], bw, gl, sviews[:1], bs, xs, 64, 0)
+    with pytest.raises(RuntimeError, match="int8"):
+        ops.grouped_swiglu_loop_out(x.float(), views, bw, gl, sviews, bs, xs, 64, 0)
+    with pytest.raises(RuntimeError, match="x_scale"):
+        ops.grouped_swiglu_loop_out(x, views, bw, gl, sviews, bs, xs[:3], 64, 0)
+    with pytest.raises(RuntimeError, match="group_list"):
+        ops.grouped_swiglu_loop_out(x, views, bw, gl.to(torch.int32), sviews, bs, xs, 64, 0)
+    with pytest.raises(ValueError, match="CUDA tensor"):          # everything valid: stops at "there is no CPU path"
+        ops.grouped_swiglu_loop_out(x, views, bw, gl, sviews, bs, xs, 64, 0)
+
+
 @pytest.mark.gpu
 def test_ops_run_eager_and_under_torch_compile():
     from mindpipe_b200 import ops, synth

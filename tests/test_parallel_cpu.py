@@ -188,3 +188,104 @@ def test_expert_parallel_constructor_rejects_wrong_partition():
             ep.ExpertParallelMoE(FakeExperts(), 8)
     finally:
         ep.dist = real
+
+
+# ---- wire layout of the flag-in-data collectives (csrc/peer_collectives.cu), replayed rank by rank in numpy ----
+def _ll_pack(words, epoch):
+    """uint32 words -> the wire form: every word followed by the call number."""
+    out = np.empty(words.size * 2, dtype=np.uint32)
+    out[0::2] = words.ravel()
+    out[1::2] = epoch
+    return out
+
+
+@pytest.mark.parametrize("world,m,n", [(2, 1, 64), (4, 5, 256), (8, 16, 512)])
+def test_row_parallel_two_phase_wire_layout(world, m, n):
+    """rowparallel_finish_ll_kernel's offsets: step 1 sends the fp32 sums of the columns rank q owns to
+    recv1[q][sender][m][n_loc] (8 bytes per sum), step 2 adds the P contributions in rank order and sends fp16
+    pairs to recv2[q][m][N] (8 bytes per pair), step 3 reads the other ranks' columns.  Every wire word must be
+    written exactly once and every rank must end with the rank-ordered sum."""
+    rng = np.random.default_rng(world * 100 + m)
+    epoch = 7
+    partial = rng.standard_normal((world, m, n)).astype(np.float32)
+    n_loc = n // world
+    recv1 = np.zeros((world, world * m * n_loc * 2), dtype=np.uint32)        # per receiving rank, in 4-byte words
+    recv2 = np.zeros((world, m * n), dtype=np.uint32)                         # 4 wire bytes per fp16 element
+    for rank in range(world):                                                 # step 1 on every rank
+        for mm in range(m):
+            for nn in range(0, n, 4):
+                q = nn // n_loc
+                if q == rank:
+                    continue
+                off = ((rank * m + mm) * n_loc + (nn - q * n_loc)) * 8 // 4
+                wire = _ll_pack(partial[rank, mm, nn:nn + 4].view(np.uint32), epoch)
+                assert not recv1[q, off:off + 8].any()
+                recv1[q, off:off + 8] = wire
+    y = np.zeros((world, m, n), dtype=np.float16)
+    for rank in range(world):                                                 # step 2
+        for mm in range(m):
+            for nl in range(0, n_loc, 4):
+                nn = rank * n_loc + nl
+                acc = np.zeros(4, dtype=np.float32)
+                for r in range(world):
+                    if r == rank:
+                        v = partial[rank, mm, nn:nn + 4]
+                    else:
+                        off = ((r * m + mm) * n_loc + nl) * 8 // 4
+                        w = recv1[rank, off:off + 8]
+                        assert (w[1::2] == epoch).all()
+                        v = w[0::2].view(np.float32)
+                    acc = acc + v
+                h = acc.astype(np.float16)
+                y[rank, mm, nn:nn + 4] = h
+                pairs = h.view(np.uint32)                                     # two fp16 per word
+                for q in range(world):
+                    if q != rank:
+                        off = (mm * n + nn) * 4 // 4
+                        assert not recv2[q, off:off + 4].any()
+                        recv2[q, off:off + 4] = _ll_pack(pairs, epoch)
+    for rank in range(world):                                                 # step 3
+        for mm in range(m):
+            for nn in range(0, n, 4):
+                if nn // n_loc == rank:
+                    continue
+                w = recv2[rank, (mm * n + nn):(mm * n + nn) + 4]
+                assert (w[1::2] == epoch).all()
+                y[rank, mm, nn:nn + 4] = np.ascontiguousarray(w[0::2]).view(np.float16)
+    want = np.zeros((m, n), dtype=np.float32)
+    for r in range(world):
+        want = want + partial[r]
+    for rank in range(world):
+        assert np.array_equal(y[rank].view(np.uint16), want.astype(np.float16).view(np.uint16))
+
+
+@pytest.mark.parametrize("world,rows,slice_bytes", [(2, 1, 32), (4, 3, 64), (8, 16, 128)])
+def test_all_gather_wire_layout(world, rows, slice_bytes):
+    """peer_allgather_push_kernel's offsets: rank r's 16-byte chunk j of row m lands at wire byte
+    ((m * world + r) * chunks_per_row + j) * 32 of every peer's receive buffer."""
+    rng = np.random.default_rng(world)
+    cpr = slice_bytes // 16
+    src = rng.integers(0, 2 ** 32, size=(world, rows, slice_bytes // 4), dtype=np.uint64).astype(np.uint32)
+    recv = np.zeros((world, rows * world * slice_bytes * 2 // 4), dtype=np.uint32)
+    epoch = 3
+    for rank in range(world):
+        for mm in range(rows):
+            for j in range(cpr):
+                off = ((mm * world + rank) * cpr + j) * 32 // 4
+                for q in range(world):
+                    if q != rank:
+                        assert not recv[q, off:off + 8].any()
+                        recv[q, off:off + 8] = _ll_pack(src[rank, mm, 4 * j:4 * j + 4], epoch)
+    for rank in range(world):
+        out = np.zeros((rows, world, slice_bytes // 4), dtype=np.uint32)
+        out[:, rank] = src[rank]
+        for mm in range(rows):
+            for r in range(world):
+                if r == rank:
+                    continue
+                for j in range(cpr):
+                    off = ((mm * world + r) * cpr + j) * 32 // 4
+                    w = recv[rank, off:off + 8]
+                    assert (w[1::2] == epoch).all()
+                    out[mm, r, 4 * j:4 * j + 4] = w[0::2]
+        assert np.array_equal(out, np.transpose(src, (1, 0, 2)))
