@@ -742,8 +742,9 @@ def measure_other_configs(args, local_rank):
                                                           "linear_tops", "library_int8_gemm_tops")})
     if errors:
         out["errors"] = errors
-    out["note"] = ("decode: chains of launches under programmatic dependent launch, weights rotated; M=64 goes through the "
-                   "dispatching entry (split-K tensor-core GEMM); library_int8_gemm_tops is torch._int_mm on the same box, "
+    out["note"] = ("decode: chains of launches under programmatic dependent launch, weights rotated; M=64 goes where "
+                   "ops.w4a16_linear sends it (tcgen05 weight-streaming kernel with a 64-token tile on the 70B-sized "
+                   "weights, split-K tensor-core GEMM otherwise); library_int8_gemm_tops is torch._int_mm on the same box, "
                    "a timing yardstick only (MEASURED_PEAKS.json has no int8 figure)")
     return out
 
@@ -828,12 +829,19 @@ def run_suite(args, local_rank, collect=None):
             for m in [int(v) for v in args.decode_m.split(",")]:
                 x = synth.normal_activation(m, k, seed=0).to(dev)
                 y = torch.empty((m, n), dtype=torch.float16, device=dev)
-                ws_dec = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, n, k), dev)
+                ws_dec = ops.new_workspace(max(ops.w4a16_decode_workspace_bytes(m, n, k), 20 << 20), dev)
                 ws_pre = ops.new_workspace(_lib.load().mp_w4a16_prefill_workspace_bytes(m, n, k), dev) if m > 16 else None
+                # 17..64 rows: what ops.w4a16_linear does -- the tcgen05 weight-streaming kernel with a 32/64-token
+                # tile where the library's rule picks it (or when asked for), else the split-K tensor-core GEMM
+                wide_umma = 16 < m <= 64 and (args.decode_kernel == "umma" or (
+                    args.decode_kernel in ("default", "auto") and ops.w4a16_decode_kernel_choice(m, n, k) == "umma"))
+                opt_umma = ops.decode_options(kernel="umma")
 
                 def call(pk, sz):
                     if m <= 16:
                         ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y)
+                    elif wide_umma:             # the tcgen05 weight-streaming kernel with a 32/64-token tile
+                        ops.w4a16_linear_decode(x, pk, sz, workspace=ws_dec, out=y, options=opt_umma)
                     else:                       # above 16 rows ops.w4a16_linear takes the split-K tensor-core GEMM
                         ops.w4a16_linear_prefill(x, pk, sz, workspace=ws_pre)
                 g = torch.cuda.CUDAGraph()
@@ -846,7 +854,8 @@ def run_suite(args, local_rank, collect=None):
                 t = timed(g.replay, 20) / copies
                 b = w4a16_bytes(n, k, m)
                 emit(suite="w4a16_decode", N=n, K=k, M=m, us=t * 1e6, gbs=b / t / 1e9,
-                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"], kernel=args.decode_kernel,
+                     frac_of_measured_hbm=b / t / 1e9 / peaks["hbm_gbs"],
+                     kernel=args.decode_kernel if m <= 16 else ("umma" if wide_umma else "gemm"),
                      **({"pdl": 1} if args.suite_pdl else {}))
             _lib.load().mp_set_programmatic_launch(0)
             del mods

@@ -228,14 +228,22 @@ int mp_set_programmatic_launch(int enabled);
 #define MP_DECODE_KERNEL_AUTO 2
 int mp_set_decode_kernel(int kind);
 /* Which kernel (MP_DECODE_KERNEL_MMA_SYNC or _UMMA) the process default sends a decode call of this shape to
- * (1 <= M <= 16), with or without a workspace; shapes the chosen kernel does not take still fall through. */
+ * (1 <= M <= 64), with or without a workspace; shapes the chosen kernel does not take still fall through.  For
+ * 17..64 rows _UMMA means the tcgen05 kernel with a 32- or 64-token activation tile (by default up to 32 rows
+ * on >= 24 MiB of packed weights with >= 8192 output rows, up to 64 rows on >= 40 MiB with >= 16384), and
+ * _MMA_SYNC that mp_w4a16_linear_decode would run its split-K kernel -- a caller then does better with
+ * mp_w4a16_linear_prefill, the tensor-core GEMM. */
 int mp_w4a16_decode_kernel_choice(int M, int N, int K, int have_workspace);
 
 /*
- * mp_w4a16_linear_decode for M <= 16 with the kernel and programmatic dependent
+ * mp_w4a16_linear_decode for M <= 64 with the kernel and programmatic dependent
  * launch chosen by THIS call (no process-wide state is read for what the
  * options name; 0 leaves everything at the process defaults):
- *   MP_DECODE_OPT_KERNEL_*     the kernel, as above
+ *   MP_DECODE_OPT_KERNEL_*     the kernel, as above.  For 17..64 rows
+ *                              MP_DECODE_OPT_KERNEL_UMMA runs the tcgen05 kernel
+ *                              with a 32- or 64-token activation tile (workspace
+ *                              of mp_w4a16_decode_workspace_bytes); the other
+ *                              choices run the workspace split-K kernel
  *   MP_DECODE_OPT_PDL_ON/_OFF  programmatic dependent launch for this call (see
  *                              mp_set_programmatic_launch for what it allows)
  */

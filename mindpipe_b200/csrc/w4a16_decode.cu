@@ -38,7 +38,7 @@ int read_and_clear_decode_error(int* value);
 // tcgen05 kernel for M <= 16 with the weights as the tensor-memory operand (w4a16_decode_umma.cu)
 int launch_decode_umma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
                        int group, void* workspace, size_t workspace_bytes, cudaStream_t st, bool pdl);
-size_t decode_umma_workspace_bytes();
+size_t decode_umma_workspace_bytes(int M);   // M <= 64: the activation tile is 16, 32 or 64 token rows
 // Which kernel serves M <= 16 when a call does not say: one of the MP_DECODE_KERNEL_* values.  Shapes the
 // chosen one does not take fall through to the next.
 static int g_decode_kernel = MP_DECODE_KERNEL_AUTO;
@@ -54,6 +54,20 @@ static int decode_kernel_for(int kind, int M, int N, int K, bool have_workspace)
   if (kind != MP_DECODE_KERNEL_AUTO) return kind;
   if (have_workspace && M > 8 && N >= 16384 && (size_t)N * (size_t)K / 2 >= (size_t)40 << 20) return MP_DECODE_KERNEL_UMMA;
   return MP_DECODE_KERNEL_MMA_SYNC;
+}
+
+// 17..64 rows: the tcgen05 kernel with a 32- or 64-token activation tile streams the weights once, where the
+// register-streaming kernel re-reads its activations per chunk; taken when the call names it.
+// AUTO (measured against the split-K tensor-core GEMM, chains under programmatic dependent launch): up to 32
+// rows on at least 24 MiB of packed weights with at least 8192 output rows (28672x8192: 54 vs 98 us, 22016x4096:
+// 31 vs 53, 8192x28672: 58 vs 90, 12288x4096: 24 vs 26; 4096x11008 loses 35 vs 24), and 33..64 rows on the
+// 70B-sized weights of the M <= 16 rule (28672x8192: 83 vs 98, 22016x4096: 47 vs 53; 8192x8192 loses 53 vs 33).
+static bool umma_above_16_rows(int kind, int M, int N, int K) {
+  if (kind == MP_DECODE_KERNEL_UMMA) return true;
+  if (kind != MP_DECODE_KERNEL_AUTO) return false;
+  const size_t packed = (size_t)N * (size_t)K / 2;
+  if (M <= 32) return N >= 8192 && packed >= ((size_t)24 << 20);
+  return N >= 16384 && packed >= ((size_t)40 << 20);
 }
 
 constexpr int kWarpsK = 4;        // warps along K inside a block
@@ -510,10 +524,13 @@ using namespace mp;
 extern "C" size_t mp_w4a16_decode_workspace_bytes_ex(int M, int N, int K, int k_split) {
   if (M <= 0 || M > 64 || N <= 0 || K <= 0 || K % kChunk != 0) return 0;
   if (M <= 16 && k_split <= 0) {             // partial tiles of the persistent tcgen05 kernels; the mma.sync kernels need none
-    return g_decode_kernel == MP_DECODE_KERNEL_MMA_SYNC ? 0 : decode_umma_workspace_bytes();
+    return g_decode_kernel == MP_DECODE_KERNEL_MMA_SYNC ? 0 : decode_umma_workspace_bytes(M);
   }
   const DecodePlan pl = plan_decode(M, N, K, k_split);
-  return kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
+  const size_t split_k = kCounterBytes + (size_t)pl.k_split * (size_t)M * (size_t)N * sizeof(float);
+  if (k_split <= 0 && g_decode_kernel != MP_DECODE_KERNEL_MMA_SYNC && decode_umma_workspace_bytes(M) > split_k)
+    return decode_umma_workspace_bytes(M);   // 17..64 rows may take the tcgen05 kernel with a wider activation tile
+  return split_k;
 }
 
 extern "C" size_t mp_w4a16_decode_workspace_bytes(int M, int N, int K) {
@@ -545,7 +562,7 @@ extern "C" int mp_w4a16_linear_decode_opts(const void* x_f16, const void* packed
   const unsigned int pd = options & MP_DECODE_OPT_PDL_MASK;
   if (pd == MP_DECODE_OPT_PDL_MASK) return MP_ERR_INVALID_ARG;
   const int pdl_choice = pd == MP_DECODE_OPT_PDL_ON ? 1 : pd == MP_DECODE_OPT_PDL_OFF ? 0 : -1;
-  if (M > 16) return MP_ERR_UNSUPPORTED;
+  if (M > 64) return MP_ERR_UNSUPPORTED;
   return decode_linear(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace, workspace_bytes, 0,
                        kind, pdl_choice, stream);
 }
@@ -587,6 +604,12 @@ static int decode_linear(const void* x_f16, const void* packed_i32, const void* 
     const int row_blocks = (N + kClusterRows - 1) / kClusterRows;
     return M <= 8 ? launch_decode_cluster<true>(p, row_blocks, ck, st)
                   : launch_decode_cluster<false>(p, row_blocks, ck, st);
+  }
+  if (M > 16 && k_split <= 0 && umma_above_16_rows(kind, M, N, K)) {
+    const bool pdl = pdl_choice < 0 ? decode_programmatic_launch() : pdl_choice != 0;
+    const int rc_umma = launch_decode_umma(x_f16, packed_i32, sz_f16x2, bias_f16, y_f16, M, N, K, group, workspace,
+                                           workspace_bytes, st, pdl);
+    if (rc_umma != MP_ERR_UNSUPPORTED) return rc_umma;
   }
   const DecodePlan pl = plan_decode(M, N, K, k_split);
   if ((size_t)pl.row_blocks * sizeof(int) > kCounterBytes) return MP_ERR_UNSUPPORTED;
@@ -736,7 +759,9 @@ extern "C" int mp_w4a16_linear_decode(const void* x_f16, const void* packed_i32,
 }
 
 extern "C" int mp_w4a16_decode_kernel_choice(int M, int N, int K, int have_workspace) {
-  if (M <= 0 || M > 16 || N <= 0 || K <= 0) return MP_ERR_INVALID_ARG;
+  if (M <= 0 || M > 64 || N <= 0 || K <= 0) return MP_ERR_INVALID_ARG;
+  if (M > 16) return have_workspace && umma_above_16_rows(g_decode_kernel, M, N, K) ? MP_DECODE_KERNEL_UMMA
+                                                                                    : MP_DECODE_KERNEL_MMA_SYNC;
   return decode_kernel_for(g_decode_kernel, M, N, K, have_workspace != 0);
 }
 

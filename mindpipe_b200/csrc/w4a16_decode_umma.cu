@@ -1,5 +1,5 @@
-// W4A16 decode linear (M <= 16) on the tcgen05 tensor core with the weights as
-// the TENSOR-MEMORY operand: y = x @ dequant(W)^T.
+// W4A16 decode linear (M <= 16; 17..64 rows with a wider activation tile) on the tcgen05
+// tensor core with the weights as the TENSOR-MEMORY operand: y = x @ dequant(W)^T.
 //
 // A thread owns ONE weight row: it reads 16 bytes (32 codes) of its row from
 // the shared-memory ring, expands them with dequant8 -- exactly
@@ -34,8 +34,12 @@
 //               packed word, so the swizzle does not matter), off the dequant
 //               warps' critical path
 // TMEM (256 columns per block, two blocks per SM): accumulator at columns
-// [0,16); three 64-column A slots (128 K each) used round robin by the "units"
-// (stage, half) in issue order.  One accumulator is enough: the first MMA of a
+// [0,TOK); three 64-column A slots (128 K each) after it, used round robin by the
+// "units" (stage, half) in issue order.  TOK = 16, 32 or 64 token rows (the UMMA N):
+// the wider tiles serve 17..64 rows with the weights still streamed once; their
+// activation tile is 16 / 32 KB per stage, so the ring is 3 / 2 stages deep, and an
+// MMA costs about 110 / 135 / 190 clocks at N = 16 / 32 / 64 (measured end to end on
+// 28672x8192), which is why 32 rows cost 1.2x and 64 rows 1.9x the time of 16.  One accumulator is enough: the first MMA of a
 // segment needs weights from warps 0-3, which they store only after they have
 // read the previous segment's accumulator.
 // Every mbarrier wait is bounded.
@@ -52,26 +56,30 @@ constexpr int kStageK = 256;
 constexpr int kDequantWarps = 8;
 constexpr int kProducerWarp = 8, kMmaWarp = 9, kPermuteWarp = 10;
 constexpr int kThreads = 11 * 32;
-constexpr int kTokens = 16;                          // UMMA N
 constexpr int kWBytes = kRows * (kStageK / 2);       // 16384
-constexpr int kXSub = kTokens * 128;                 // [16 tokens x 64 columns] fp16
-constexpr int kXBytes = 4 * kXSub;                   // 8192
+// TOK = token rows of the activation tile = UMMA N: 16, 32 or 64
+__host__ __device__ constexpr int x_sub(int tok) { return tok * 128; }        // [TOK tokens x 64 columns] fp16
+__host__ __device__ constexpr int x_bytes(int tok) { return 4 * x_sub(tok); }
 constexpr int kMaxStages = 4;
 constexpr int kBars = 3 * kMaxStages + 7;
 constexpr size_t kSmemBlockMax = 113 * 1024;         // two blocks per SM
-__host__ __device__ constexpr int stage_bytes(int groups_per_stage) {   // ring stride, a multiple of 1024
-  return kWBytes + kXBytes + ((groups_per_stage * kRows * 4 + 1023) & ~1023);
+__host__ __device__ constexpr int stage_bytes(int tok, int groups_per_stage) {   // ring stride, a multiple of 1024
+  return kWBytes + x_bytes(tok) + ((groups_per_stage * kRows * 4 + 1023) & ~1023);
 }
-__host__ __device__ constexpr size_t smem_bytes(int stages, int groups_per_stage) {
-  return 1024 + (size_t)stages * stage_bytes(groups_per_stage) + kBars * 8 + 64;
+__host__ __device__ constexpr size_t smem_bytes(int tok, int stages, int groups_per_stage) {
+  return 1024 + (size_t)stages * stage_bytes(tok, groups_per_stage) + kBars * 8 + 64;
 }
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kASlot0 = 32, kASlotCols = 64;    // three A slots at columns 32, 96, 160
+constexpr uint32_t kASlotCols = 64;                  // three A slots (128 K each) after the accumulator columns
+__host__ __device__ constexpr uint32_t a_slot0(int tok) { return tok <= 32 ? 32u : 64u; }
 constexpr int kASlots = 3;
 constexpr int kMaxBlocks = 2 * kSmCount;
 constexpr size_t kCounterBytes = 16384;              // one arrival counter per row block (<= 4096 of them)
-constexpr size_t kTileBytes = (size_t)kTokens * kRows * sizeof(float);
-constexpr size_t kWorkspaceBytes = kCounterBytes + (size_t)kMaxBlocks * 2 * kTileBytes;
+__host__ __device__ constexpr size_t tile_floats(int tok) { return (size_t)tok * kRows; }
+__host__ __device__ constexpr size_t workspace_bytes(int tok) {
+  return kCounterBytes + (size_t)kMaxBlocks * 2 * tile_floats(tok) * sizeof(float);
+}
+__host__ __device__ constexpr int tokens_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 }  // namespace du
 
 struct DecodeUmmaParams {
@@ -83,7 +91,7 @@ struct DecodeUmmaParams {
   int groups_per_stage;    // rows of the (scale, zero) box
   int gshift;              // log2(group) for groups shorter than 128 columns
   int* counters;           // workspace: [row blocks], zero between calls
-  float* tiles;            // workspace: [grid][2][16][128] fp32 partial tiles
+  float* tiles;            // workspace: [grid][2][TOK][128] fp32 partial tiles
   int* error_word;
 };
 
@@ -138,13 +146,15 @@ __device__ __forceinline__ uint4 pair_permute_u4(const uint4 in) {
   return v;
 }
 
-template <int STAGES>
+template <int STAGES, int TOK>
 __global__ void __launch_bounds__(du::kThreads, 2)
 w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                          const __grid_constant__ CUtensorMap tmap_sz, const DecodeUmmaParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int stage_bytes = du::stage_bytes(p.groups_per_stage);
+  constexpr int kXSub = du::x_sub(TOK), kXBytes = du::x_bytes(TOK);
+  constexpr uint32_t kASlot0 = du::a_slot0(TOK);
+  const int stage_bytes = du::stage_bytes(TOK, p.groups_per_stage);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + STAGES * stage_bytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + du::kBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -191,7 +201,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       prefetch_tensormap(&tmap_w);
       prefetch_tensormap(&tmap_x);
       prefetch_tensormap(&tmap_sz);
-      const uint32_t tx_bytes = du::kWBytes + du::kXBytes + p.groups_per_stage * du::kRows * 4;
+      const uint32_t tx_bytes = du::kWBytes + kXBytes + p.groups_per_stage * du::kRows * 4;
       auto issue_weights = [&](int i) {
         const int s = i % STAGES;
         const int t = t0 + i, rb = t / ST, st = t - rb * ST;
@@ -199,7 +209,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         unsigned char* base = ring + s * stage_bytes;
         mbar_arrive_expect_tx(full, tx_bytes);
         tma_load_2d(smem_u32(base), &tmap_w, full, st * (du::kStageK / 2), rb * du::kRows);
-        tma_load_2d(smem_u32(base + du::kWBytes + du::kXBytes), &tmap_sz, full, rb * du::kRows,
+        tma_load_2d(smem_u32(base + du::kWBytes + kXBytes), &tmap_sz, full, rb * du::kRows,
                     (st * du::kStageK) / p.group);
       };
       auto issue_x = [&](int i) {
@@ -208,7 +218,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         const uint32_t full = full0 + 8 * s;
         unsigned char* xb = ring + s * stage_bytes + du::kWBytes;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tma_load_2d(smem_u32(xb + j * du::kXSub), &tmap_x, full, st * du::kStageK + j * 64, 0);
+        for (int j = 0; j < 4; ++j) tma_load_2d(smem_u32(xb + j * kXSub), &tmap_x, full, st * du::kStageK + j * 64, 0);
       };
       const int prologue = min(n_stages, STAGES);
       for (int i = 0; i < prologue; ++i) issue_weights(i);     // weights never depend on the previous kernel
@@ -226,7 +236,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
   } else if (warp == du::kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, du::kRows, du::kTokens);
+      constexpr uint32_t idesc = umma_idesc(kIdescDFormatF32 | kIdescABFormatF16, du::kRows, TOK);
       bool ok = true;
       int st = t0 % ST;
       bool seg_first = true;
@@ -242,10 +252,10 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
           if (!mbar_wait_sleep(afull0 + 8 * q, aphase, abort_flag, 100)) { ok = false; break; }
           if (h == 0 && !mbar_wait_sleep(xp0 + 8 * s, phase, abort_flag, 100)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint32_t a_tmem = tmem_base + du::kASlot0 + q * du::kASlotCols;
+          const uint32_t a_tmem = tmem_base + kASlot0 + q * du::kASlotCols;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {     // 16 K per instruction: 8 TMEM columns of A, 32 bytes of B's rows
-            const uint64_t b_desc = umma_desc_k_sw128(xb + (h * 2 + (kk >> 2)) * du::kXSub) + 2 * (kk & 3);
+            const uint64_t b_desc = umma_desc_k_sw128(xb + (h * 2 + (kk >> 2)) * kXSub) + 2 * (kk & 3);
             umma_f16_ts(tmem_base, a_tmem + kk * 8, b_desc, idesc, !(seg_first && h == 0 && kk == 0));
           }
           umma_commit(aempty0 + 8 * q);
@@ -267,7 +277,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       if (!__all_sync(0xffffffffu, mbar_wait_sleep(full0 + 8 * s, phase, abort_flag, 400))) break;
       uint4* xt = reinterpret_cast<uint4*>(ring + s * stage_bytes + du::kWBytes);
 #pragma unroll 4
-      for (int c = lane; c < du::kXBytes / 16; c += 32) xt[c] = pair_permute_u4(xt[c]);
+      for (int c = lane; c < kXBytes / 16; c += 32) xt[c] = pair_permute_u4(xt[c]);
       fence_proxy_async_smem();                                // generic-proxy stores -> visible to the MMA's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(xp0 + 8 * s);
@@ -283,7 +293,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     int w_off[4];                                  // this row's four 16-byte chunks of its half (128-byte swizzle)
 #pragma unroll
     for (int j = 0; j < 4; ++j) w_off[j] = row * 128 + (((kh * 4 + j) ^ sw) << 4);
-    const int sz_off = du::kWBytes + du::kXBytes + row * 4;
+    const int sz_off = du::kWBytes + kXBytes + row * 4;
     int rb = t0 / ST, st = t0 - rb * ST;
     int seg_begin_i = 0, seg_begin_st = st, seg_idx = 0;
     for (int i = 0; i < n_stages; ++i) {
@@ -302,7 +312,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       }
       const int u = 2 * i + kh, q = u % du::kASlots;
       const uint32_t aphase = ((u / du::kASlots) & 1) ^ 1;
-      const uint32_t a_tmem = tmem_base + lane_field + du::kASlot0 + q * du::kASlotCols;
+      const uint32_t a_tmem = tmem_base + lane_field + kASlot0 + q * du::kASlotCols;
       // (waiting for the slot here, before the expansion, measured 8 % faster at 16 tokens than waiting
       // just before the first store)
       if (!__all_sync(0xffffffffu, mbar_wait(aempty0 + 8 * q, aphase, abort_flag))) break;
@@ -339,24 +349,31 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
           // ---- segment epilogue: lane = weight row, column = token
           if (!__all_sync(0xffffffffu, mbar_wait(dfull, seg_idx & 1, abort_flag))) break;
           tcgen05_fence_after();
-          uint32_t acc[16];
-          tmem_ld_32x32_x16(tmem_base + lane_field, acc);
-          tmem_ld_wait();
+          // 16 token columns at a time (more would not fit beside the dequant registers)
           asm volatile("griddepcontrol.wait;" ::: "memory");   // before anything of the previous kernel is overwritten
           const int n = rb * du::kRows + row;
           const float bias = (p.bias && n < p.N) ? h2f(p.bias[n]) : 0.0f;
-          if (seg_begin_st == 0 && st == ST - 1) {             // the whole K of this row block: final
-            if (n < p.N) {
+          const bool whole = seg_begin_st == 0 && st == ST - 1;   // the whole K of this row block: final
+          const int which = seg_begin_i == 0 ? 0 : 1;              // a block has at most two partial segments
+          float* tile = p.tiles + ((size_t)blk * 2 + which) * du::tile_floats(TOK);
+#pragma unroll 1
+          for (int t0c = 0; t0c < TOK; t0c += 16) {
+            uint32_t acc[16];
+            tmem_ld_32x32_x16(tmem_base + lane_field + t0c, acc);
+            tmem_ld_wait();
+            if (whole) {
+              if (n < p.N) {
 #pragma unroll
-              for (int m = 0; m < du::kTokens; ++m)
-                if (m < p.M) p.y[(size_t)m * p.N + n] = f2h(__uint_as_float(acc[m]) + bias);
+                for (int m = 0; m < 16; ++m)
+                  if (t0c + m < p.M) p.y[(size_t)(t0c + m) * p.N + n] = f2h(__uint_as_float(acc[m]) + bias);
+              }
+            } else {
+#pragma unroll
+              for (int m = 0; m < 16; ++m)
+                if (t0c + m < p.M) tile[(t0c + m) * du::kRows + row] = __uint_as_float(acc[m]);
             }
-          } else {
-            const int which = seg_begin_i == 0 ? 0 : 1;        // a block has at most two partial segments
-            float* tile = p.tiles + ((size_t)blk * 2 + which) * (du::kTokens * du::kRows);
-#pragma unroll
-            for (int m = 0; m < du::kTokens; ++m)
-              if (m < p.M) tile[m * du::kRows + row] = __uint_as_float(acc[m]);
+          }
+          if (!whole) {
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (warp == 0 && lane == 0) {
@@ -370,20 +387,23 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (epi_word[0]) {
               const int fb = epi_word[1], lb = epi_word[2];
-              float sum[du::kTokens];
+#pragma unroll 1
+              for (int t0c = 0; t0c < TOK && t0c < p.M; t0c += 16) {
+                float sum[16];
 #pragma unroll
-              for (int m = 0; m < du::kTokens; ++m) sum[m] = 0.0f;
-              for (int b2 = fb; b2 <= lb; ++b2) {              // block order: deterministic
-                const int w2 = range_start(b2, grid, p.total) >= rb * ST ? 0 : 1;
-                const float* t2 = p.tiles + ((size_t)b2 * 2 + w2) * (du::kTokens * du::kRows) + row;
+                for (int m = 0; m < 16; ++m) sum[m] = 0.0f;
+                for (int b2 = fb; b2 <= lb; ++b2) {            // block order: deterministic
+                  const int w2 = range_start(b2, grid, p.total) >= rb * ST ? 0 : 1;
+                  const float* t2 = p.tiles + ((size_t)b2 * 2 + w2) * du::tile_floats(TOK) + row;
 #pragma unroll
-                for (int m = 0; m < du::kTokens; ++m)
-                  if (m < p.M) sum[m] += __ldcg(t2 + m * du::kRows);
-              }
-              if (n < p.N) {
+                  for (int m = 0; m < 16; ++m)
+                    if (t0c + m < p.M) sum[m] += __ldcg(t2 + (t0c + m) * du::kRows);
+                }
+                if (n < p.N) {
 #pragma unroll
-                for (int m = 0; m < du::kTokens; ++m)
-                  if (m < p.M) p.y[(size_t)m * p.N + n] = f2h(sum[m] + bias);
+                  for (int m = 0; m < 16; ++m)
+                    if (t0c + m < p.M) p.y[(size_t)(t0c + m) * p.N + n] = f2h(sum[m] + bias);
+                }
               }
             }
           }
@@ -413,17 +433,17 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
 int* decode_error_word_ptr(int* out_rc);   // w4a16_decode_tma.cu: device address of the decode error word
 
-size_t decode_umma_workspace_bytes() { return du::kWorkspaceBytes; }
+size_t decode_umma_workspace_bytes(int M) { return du::workspace_bytes(du::tokens_for(M)); }
 
 static bool umma_shape_ok(int M, int N, int K, int group) {
-  if (M > du::kTokens || K % 64 != 0 || N % 4 != 0) return false;
+  if (M > 64 || K % 64 != 0 || N % 4 != 0) return false;
   return group == 32 || group == 64 || group == 128 || group == du::kStageK || group % du::kStageK == 0;
 }
 
-template <int STAGES>
+template <int STAGES, int TOK>
 static int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tsz, const DecodeUmmaParams& p,
                        int grid, size_t smem, cudaStream_t st, bool pdl) {
-  auto kern = w4a16_decode_umma_kernel<STAGES>;
+  auto kern = w4a16_decode_umma_kernel<STAGES, TOK>;
   static thread_local int configured_device = -1;
   int device = 0;
   MP_CUDA_TRY(cudaGetDevice(&device));
@@ -456,7 +476,8 @@ static int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, const CUten
 int launch_decode_umma(const void* x, const void* packed, const void* sz, const void* bias, void* y, int M, int N, int K,
                        int group, void* workspace, size_t workspace_bytes, cudaStream_t st, bool pdl) {
   if (!umma_shape_ok(M, N, K, group)) return MP_ERR_UNSUPPORTED;
-  if (!workspace || workspace_bytes < du::kWorkspaceBytes || !aligned(workspace, 16)) return MP_ERR_UNSUPPORTED;
+  const int tok = du::tokens_for(M);
+  if (!workspace || workspace_bytes < du::workspace_bytes(tok) || !aligned(workspace, 16)) return MP_ERR_UNSUPPORTED;
   if (!aligned(x, 16) || !aligned(packed, 16) || !aligned(sz, 16)) return MP_ERR_UNSUPPORTED;
   const int row_blocks = (N + du::kRows - 1) / du::kRows;
   if ((size_t)row_blocks * sizeof(int) > du::kCounterBytes) return MP_ERR_UNSUPPORTED;
@@ -465,7 +486,7 @@ int launch_decode_umma(const void* x, const void* packed, const void* sz, const 
                                 (uint64_t)K / 2, 128, du::kRows, true);
   if (rc != MP_OK) return rc;
   rc = encode_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64,
-                            du::kTokens, true);
+                            tok, true);
   if (rc != MP_OK) return rc;
   const int gps = group < du::kStageK ? du::kStageK / group : 1;
   rc = encode_tensor_map_2d(&tsz, CU_TENSOR_MAP_DATA_TYPE_UINT32, sz, (uint64_t)N, (uint64_t)(K / group),
@@ -486,11 +507,20 @@ int launch_decode_umma(const void* x, const void* packed, const void* sz, const 
   if (rc_err != MP_OK) return rc_err;
   // two blocks per SM, each with at least two stages of work
   const int grid = max(1, min(du::kMaxBlocks, p.total / 2));
-  // the deepest ring that still lets two blocks share an SM (groups of 32 columns carry 4 KB of
-  // (scale, zero) pairs per stage and get three stages)
-  const bool deep = du::smem_bytes(4, gps) <= du::kSmemBlockMax;
-  if (deep) return launch_umma<4>(tw, tx, tsz, p, grid, du::smem_bytes(4, gps), st, pdl);
-  return launch_umma<3>(tw, tx, tsz, p, grid, du::smem_bytes(3, gps), st, pdl);
+  // the deepest ring that still lets two blocks share an SM (groups of 32 columns carry 4 KB of (scale, zero)
+  // pairs per stage; a 32-token activation tile is 16 KB per stage, a 64-token one 32 KB)
+  auto fits = [&](int stages) { return du::smem_bytes(tok, stages, gps) <= du::kSmemBlockMax; };
+  if (tok == 16) {
+    if (fits(4)) return launch_umma<4, 16>(tw, tx, tsz, p, grid, du::smem_bytes(16, 4, gps), st, pdl);
+    return launch_umma<3, 16>(tw, tx, tsz, p, grid, du::smem_bytes(16, 3, gps), st, pdl);
+  }
+  if (tok == 32) {
+    if (fits(3)) return launch_umma<3, 32>(tw, tx, tsz, p, grid, du::smem_bytes(32, 3, gps), st, pdl);
+    if (fits(2)) return launch_umma<2, 32>(tw, tx, tsz, p, grid, du::smem_bytes(32, 2, gps), st, pdl);
+    return MP_ERR_UNSUPPORTED;
+  }
+  if (fits(2)) return launch_umma<2, 64>(tw, tx, tsz, p, grid, du::smem_bytes(64, 2, gps), st, pdl);
+  return MP_ERR_UNSUPPORTED;
 }
 
 }  // namespace mp

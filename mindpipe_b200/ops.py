@@ -71,7 +71,8 @@ def w4a16_decode_workspace_bytes(m: int, n: int, k: int, k_split: int = 0) -> in
 
 
 def w4a16_decode_kernel_choice(m: int, n: int, k: int, have_workspace: bool = True) -> str:
-    """Name of the kernel the process default picks for a decode call of this shape (1 <= m <= 16)."""
+    """Name of the kernel the process default picks for a decode call of this shape (1 <= m <= 64); above 16 rows
+    ``"mma_sync"`` means the split-K kernel, which the tensor-core GEMM (``w4a16_linear_prefill``) beats."""
     kind = _lib.load().mp_w4a16_decode_kernel_choice(m, n, k, 1 if have_workspace else 0)
     _lib.check(min(kind, 0), "w4a16_decode_kernel_choice", M=m, N=n, K=k)
     return {0: "mma_sync", 1: "umma"}[kind]
@@ -152,7 +153,8 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
 
     ``workspace`` (uint8, zero-filled when created, not shared by calls that
     may overlap) defaults to a cached buffer per device and stream.  ``options``
-    (see :func:`decode_options`, M <= 16 only) fixes kernel / launch mode for this call.
+    (see :func:`decode_options`) fixes kernel / launch mode for this call; with 17..64 rows ``kernel="umma"``
+    runs the tcgen05 kernel with a 32- or 64-token activation tile, the other choices the split-K kernel.
     """
     x2 = _req(x, "x", torch.float16, 2)
     p = _req(weight_packed, "weight_packed", torch.int32, 2)
@@ -279,14 +281,18 @@ def w4a16_linear_prefill(x, weight_packed, scale_zero, bias=None, *, workspace=N
 def w4a16_linear(x, weight_packed, scale_zero, bias=None):
     """W4A16 linear for any number of rows.
 
-    Up to 16 rows go to the weight-streaming decode kernel, more to the
-    tensor-core prefill kernel (which splits K when the batch gives it few
-    tiles); shapes the prefill kernel does not take (K or the group size not
-    a multiple of 64) are processed by the decode kernels in 64-row slabs.
+    Up to 16 rows go to the weight-streaming decode kernels; 17..64 rows on
+    large weights to the tcgen05 weight-streaming kernel with a 32- or
+    64-token tile (the library's rule, ``w4a16_decode_kernel_choice``); the
+    rest to the tensor-core prefill kernel (which splits K when the batch gives
+    it few tiles); shapes the prefill kernel does not take (K or the group size
+    not a multiple of 64) are processed by the decode kernels in 64-row slabs.
     """
     m, k = x.shape
     if m <= 16:
         return w4a16_linear_decode(x, weight_packed, scale_zero, bias)
+    if m <= 64 and w4a16_decode_kernel_choice(m, weight_packed.shape[0], k) == "umma":
+        return w4a16_linear_decode(x, weight_packed, scale_zero, bias)   # weights streamed once, 32/64-token tile
     group = k // scale_zero.shape[0]
     if k % 64 == 0 and group % 64 == 0:
         return w4a16_linear_prefill(x, weight_packed, scale_zero, bias)

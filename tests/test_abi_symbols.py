@@ -93,7 +93,12 @@ def test_decode_kernel_selector_and_its_workspace_rule(built_lib):
         assert ops.w4a16_decode_kernel_choice(16, 22016, 4096, have_workspace=False) == "mma_sync"
         assert ops.w4a16_decode_kernel_choice(8, 22016, 4096) == "mma_sync"
         assert ops.w4a16_decode_kernel_choice(16, 4096, 4096) == "mma_sync"
-        assert lib.mp_w4a16_decode_kernel_choice(17, 4096, 4096, 1) < 0
+        assert ops.w4a16_decode_kernel_choice(32, 28672, 8192) == "umma"          # 17..64 rows: wide activation tile
+        assert ops.w4a16_decode_kernel_choice(32, 4096, 11008) == "mma_sync"
+        assert ops.w4a16_decode_kernel_choice(64, 28672, 8192) == "umma"
+        assert ops.w4a16_decode_kernel_choice(64, 8192, 8192) == "mma_sync"
+        assert ops.w4a16_decode_kernel_choice(64, 28672, 8192, have_workspace=False) == "mma_sync"
+        assert lib.mp_w4a16_decode_kernel_choice(65, 4096, 4096, 1) < 0
         assert ops.decode_options() == 0
         assert ops.decode_options(kernel="umma", pdl=True) == 0x2 | 0x10
         assert ops.decode_options(kernel="mma_sync", pdl=False) == 0x1 | 0x20

@@ -123,3 +123,69 @@ def test_back_to_back_launches_under_programmatic_dependent_launch(kind):
             assert torch.equal(a, b)
     finally:
         ops.set_decode_kernel(prev_kind)
+
+
+# ---- 17..64 rows: the same kernel with a 32- or 64-token activation tile, chosen per call ----
+def _wide_case(ops, n, k, m, group=128, seed=0, bias=False):
+    w = synth.normal_weight(n, k, seed=seed, index=1).numpy()
+    x = synth.normal_activation(m, k, seed=seed, index=2).numpy()
+    b = (synth.normal_activation(1, n, seed=seed, index=3).numpy()[0] * np.float16(0.1)).astype(np.float16) if bias else None
+    packed, scale, zero, _ = ops.w4a16_quantize(torch.from_numpy(w).cuda(), group)
+    wdq = ops.w4a16_dequant(packed, scale, zero, n, k)
+    sz = ops.w4a16_prepare(scale, zero, k)
+    xd = torch.from_numpy(x).cuda()
+    bd = None if b is None else torch.from_numpy(b).cuda()
+    ws = ops.new_workspace(20 << 20, "cuda")                # 64-token partial tiles: 16 KB + 296 x 2 x 32 KB
+    y = ops.w4a16_linear_decode(xd, packed, sz, bd, workspace=ws, options=ops.decode_options(kernel="umma"))
+    torch.cuda.synchronize()
+    return y, O.linear_f16(x, wdq.cpu().numpy(), b), (xd, packed, sz, bd, ws, wdq)
+
+
+@pytest.mark.parametrize("m", [17, 24, 32, 33, 48, 64])
+def test_umma_wide_tile_all_row_counts(m):
+    from mindpipe_b200 import ops
+    y, ref, _ = _wide_case(ops, 256, 1024, m, bias=True)
+    ops.check_device_errors()
+    assert y.shape == ref.shape
+    assert O.rel_frobenius(y.cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("n,k,group", [(40, 256, 64), (72, 384, 32), (264, 1280, 128), (128, 1024, 512), (4104, 512, 128)])
+def test_umma_wide_tile_ragged_shapes_and_groups(n, k, group):
+    from mindpipe_b200 import ops
+    for m in (20, 64):
+        y, ref, _ = _wide_case(ops, n, k, m, group=group, bias=True)
+        ops.check_device_errors()
+        assert O.rel_frobenius(y.cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (22016, 4096), (4096, 11008)])
+@pytest.mark.parametrize("m", [32, 64])
+def test_umma_wide_tile_llama_shapes_and_agreement_with_the_gemm(n, k, m):
+    from mindpipe_b200 import ops
+    y, ref, (xd, packed, sz, bd, ws, _) = _wide_case(ops, n, k, m, seed=1)
+    ops.check_device_errors()
+    assert O.rel_frobenius(y.cpu().numpy(), ref) <= TOL
+    y2 = ops.w4a16_linear_prefill(xd, packed, sz, bd)      # same fp16 weights, another summation order
+    assert O.rel_frobenius(y.cpu().numpy(), y2.cpu().numpy()) <= TOL_KERNELS
+    for _ in range(3):                                      # fixed-order fix-up: identical from run to run
+        again = ops.w4a16_linear_decode(xd, packed, sz, bd, workspace=ws, options=ops.decode_options(kernel="umma"))
+        assert torch.equal(again, y)
+    assert int(ws[:16384].view(torch.int32).abs().sum().item()) == 0       # arrival counters re-armed
+
+
+@pytest.mark.parametrize("m", [32, 64])
+def test_umma_wide_tile_one_hot_rows_bit_for_bit(m):
+    from mindpipe_b200 import ops
+    n, k = 384, 1024
+    w = synth.normal_weight(n, k, seed=4, index=1).cuda()
+    packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+    wdq = ops.w4a16_dequant(packed, scale, zero, n, k)
+    sz = ops.w4a16_prepare(scale, zero, k)
+    ws = ops.new_workspace(20 << 20, "cuda")
+    for k0 in (0, 5, 130, k - m):
+        x = torch.zeros((m, k), dtype=torch.float16, device="cuda")
+        x[torch.arange(m), k0 + torch.arange(m)] = 1.0
+        y = ops.w4a16_linear_decode(x, packed, sz, workspace=ws, options=ops.decode_options(kernel="umma"))
+        assert torch.equal(y.view(torch.int16), wdq[:, k0:k0 + m].t().contiguous().view(torch.int16))
+    ops.check_device_errors()
