@@ -412,52 +412,63 @@ def measure_moe(world, rank, dev, dist, iters=10):
             exchange = f"nccl all_to_all_single ({type(err).__name__})"
     else:
         layer = mod
-    for _ in range(2):
-        layer(hs, idx, wts)
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    replay = None
-    if exchange.startswith("peer-memory") or world == 1:
-        # the layer is a fixed launch sequence (no host read, barrier epochs in device memory): capture it
-        # once and replay it, as a serving runtime would, so that host launch gaps are not timed
-        side = torch.cuda.Stream(device=dev)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                layer(hs, idx, wts)
-        replay = (graph, side)
-        launch_mode = "cuda graph replay"
-    else:
-        launch_mode = "eager"
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if replay is not None:
-        graph, side = replay
-        with torch.cuda.stream(side):
-            graph.replay()                               # one untimed replay
-            e0.record(side)
-            for _ in range(iters):
-                graph.replay()
-            e1.record(side)
-    else:
-        e0.record()
-        for _ in range(iters):
+
+    def time_layer(layer):
+        for _ in range(2):
             layer(hs, idx, wts)
-        e1.record()
-    torch.cuda.synchronize()
-    ops.check_device_errors()
-    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        replay = None
+        if exchange.startswith("peer-memory") or world == 1:
+            # the layer is a fixed launch sequence (no host read, barrier epochs in device memory): capture it
+            # once and replay it, as a serving runtime would, so that host launch gaps are not timed
+            side = torch.cuda.Stream(device=dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    layer(hs, idx, wts)
+            replay = (graph, side)
+            launch_mode = "cuda graph replay"
+        else:
+            launch_mode = "eager"
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if replay is not None:
+            graph, side = replay
+            with torch.cuda.stream(side):
+                graph.replay()                               # one untimed replay
+                e0.record(side)
+                for _ in range(iters):
+                    graph.replay()
+                e1.record(side)
+        else:
+            e0.record()
+            for _ in range(iters):
+                layer(hs, idx, wts)
+            e1.record()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), launch_mode
+
+    ms, launch_mode = time_layer(layer)
+    extra = {}
+    if world > 1 and exchange.startswith("peer-memory"):
+        # the same layer with the GEMMs in two halves of the row tiles and the exchange of one half overlapping the
+        # other half's GEMMs on a second stream (an option of the module, off by default), for comparison
+        halves = SymmetricExpertParallelMoE(mod, shape.num_experts, max_tokens_per_rank=t_loc, top_k=shape.top_k,
+                                            overlap=True)
+        extra["ms_per_layer_with_overlapped_exchange"] = time_layer(halves)[0]
     int8_ops = 2 * (shape.top_k * shape.tokens) * shape.hidden * 2 * shape.ffn + \
         2 * (shape.top_k * shape.tokens) * shape.ffn * shape.hidden
     return {"config": "mixtral-8x7b-shaped layer, 8192 tokens, top-2, experts sharded over the ranks (all-to-all)",
             "ms_per_layer": ms, "tokens_per_s": shape.tokens / (ms * 1e-3), "int8_tops": int8_ops / (ms * 1e-3) / 1e12,
-            "n_gpus": world, "exchange": exchange, "launches": launch_mode}
+            "n_gpus": world, "exchange": exchange, "launches": launch_mode, **extra}
 
 
 def workload_config():

@@ -452,6 +452,27 @@ int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_scale_f32, co
                                    size_t workspace_bytes, int* error_word, mp_stream_t stream);
 
 /*
+ * mp_moe_expert_stage in three launches (same workspace, same bits), each grouped GEMM optionally on ONE HALF of
+ * the 256-row tiles in use (tile_part: -1 = all, 0 / 1 = first / second half; split at (tiles + 1) / 2).  An
+ * expert-parallel caller uses the halves to overlap the exchange with the GEMMs on two streams -- the runtime's
+ * own pattern of overlapping the token exchange with the expert matmuls
+ * (acceleration/runtime_patches/vllm_ascend.patch:2482-2544):
+ *   gemm1(0) | gemm1(1) | requant | gemm2(0) | gemm2(1)   on one stream,
+ *   the pull of half 1 beside gemm1(0) and the push of half 0 beside gemm2(1) on another
+ * (mp_moe_ep_pull_part / mp_moe_ep_push_part take the same `part`).  mp_moe_gemm1_swiglu(part 1) keeps the row
+ * maxima part 0 produced; mp_moe_requant runs once, over all rows, between the two GEMMs.
+ */
+int mp_moe_gemm1_swiglu(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
+                        int padded_rows, int H, int I, int num_local_experts, const void* w13_q_i8,
+                        const void* w13_scale_f32, void* workspace, size_t workspace_bytes, int tile_part,
+                        int* error_word, mp_stream_t stream);
+int mp_moe_requant(const void* plan_i32, int padded_rows, int I, int num_local_experts, void* workspace,
+                   size_t workspace_bytes, mp_stream_t stream);
+int mp_moe_gemm2(const void* plan_i32, int padded_rows, int I, int H, int num_local_experts,
+                 const void* w2_q_i8, const void* w2_scale_f32, void* d_out_f16, void* workspace,
+                 size_t workspace_bytes, int tile_part, int* error_word, mp_stream_t stream);
+
+/*
  * out[t] = sum_j f16(d[dest_row(t,j)] * w[t,j]) in fp16, experts in ascending
  * order: npu_moe_token_unpermute (vllm_ascend.patch:2415-2419), i.e.
  * fake_quant.py:188-189.  Entries with dest_row < 0 are skipped.
@@ -577,6 +598,13 @@ int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale
                    void* scale_sorted_f32, mp_stream_t stream);
 int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
                    int capacity_rows, int H, const void* const* peer_back_ptrs, mp_stream_t stream);
+/* The same two copies restricted to one half of the 256-row tiles in use (part 0 / 1; -1 = all rows), split where
+ * mp_moe_gemm1_swiglu / mp_moe_gemm2 split their tiles. */
+int mp_moe_ep_pull_part(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,
+                        int world, int num_local_experts, int capacity_rows, int H, void* q_sorted_i8,
+                        void* scale_sorted_f32, int part, mp_stream_t stream);
+int mp_moe_ep_push_part(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                        int capacity_rows, int H, const void* const* peer_back_ptrs, int part, mp_stream_t stream);
 
 /*
  * dst row i = src row row_map[i] (rows of row_bytes bytes; 4, or a multiple of

@@ -60,6 +60,9 @@ SIGNATURES = {
     "mp_moe_expert_stage": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
     "mp_moe_expert_stage_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _Z, _P, _P]),
     "mp_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "mp_moe_gemm1_swiglu": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _I, _P, _P]),
+    "mp_moe_requant": (_I, [_P, _I, _I, _I, _P, _Z, _P]),
+    "mp_moe_gemm2": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _Z, _I, _P, _P]),
     "mp_w8a8_gate_up_swiglu_requant_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "mp_w8a8_gate_up_swiglu_requant": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P, _P]),
     "mp_gather_rows": (_I, [_P, _P, _I, _I, _P, _P]),
@@ -77,6 +80,8 @@ SIGNATURES = {
     "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "mp_moe_ep_push": (_I, [_P, _P, _I, _I, _I, _I, _P, _P]),
+    "mp_moe_ep_pull_part": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "mp_moe_ep_push_part": (_I, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),
 }
 
 

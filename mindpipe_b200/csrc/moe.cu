@@ -322,6 +322,80 @@ static int expert_stage(const void* routed_q_i8, const void* routed_scale_f32, c
                           num_tiles, tile_expert, d_out_f16, error_word, st, scatter);
 }
 
+// ---- the expert stage in three launches, each GEMM optionally on one half of the row tiles -----------------
+// Same workspace layout and arithmetic as mp_moe_expert_stage; a caller that overlaps the exchange with the GEMMs
+// runs: gemm1(half 0) | gemm1(half 1) | requant | gemm2(half 0) | gemm2(half 1), with the pull of half 1 next to
+// gemm1(half 0) and the push of half 0 next to gemm2(half 1) on a second stream.
+struct StageBuffers {
+  __half* h;
+  unsigned int* absmax;
+  int8_t* q2;
+  float* scale2;
+};
+static int stage_buffers(void* workspace, size_t workspace_bytes, int padded_rows, int I, StageBuffers& b) {
+  if (padded_rows <= 0 || I <= 0) return MP_ERR_INVALID_ARG;
+  if (padded_rows % kMoeSegmentAlign != 0 || I % 16 != 0) return MP_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < mp_moe_expert_stage_workspace_bytes(padded_rows, I)) return MP_ERR_WORKSPACE;
+  if (!aligned(workspace, 256)) return MP_ERR_ALIGNMENT;
+  const size_t P = (size_t)padded_rows;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  b.h = reinterpret_cast<__half*>(ws);
+  b.absmax = reinterpret_cast<unsigned int*>(ws + align256(P * I * 2));
+  b.q2 = reinterpret_cast<int8_t*>(ws + align256(P * I * 2) + align256(P * 4));
+  b.scale2 = reinterpret_cast<float*>(ws + align256(P * I * 2) + align256(P * 4) + align256(P * I));
+  return MP_OK;
+}
+
+extern "C" int mp_moe_gemm1_swiglu(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
+                                   int padded_rows, int H, int I, int num_local_experts, const void* w13_q_i8,
+                                   const void* w13_scale_f32, void* workspace, size_t workspace_bytes, int tile_part,
+                                   int* error_word, mp_stream_t stream) {
+  if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || H <= 0 || num_local_experts <= 0 ||
+      tile_part < -1 || tile_part > 1)
+    return MP_ERR_INVALID_ARG;
+  if (H % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
+  if (!aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16)) return MP_ERR_ALIGNMENT;
+  StageBuffers b;
+  const int rc = stage_buffers(workspace, workspace_bytes, padded_rows, I, b);
+  if (rc != MP_OK) return rc;
+  const int E = num_local_experts;
+  const int* plan = static_cast<const int*>(plan_i32);
+  return launch_moe_gemm1_swiglu(routed_q_i8, static_cast<const float*>(routed_scale_f32), w13_q_i8,
+                                 static_cast<const float*>(w13_scale_f32), padded_rows, H, I, E, plan + 3 * E + 1,
+                                 plan + 3 * E + 2, b.h, b.absmax, error_word, static_cast<cudaStream_t>(stream), tile_part);
+}
+
+extern "C" int mp_moe_requant(const void* plan_i32, int padded_rows, int I, int num_local_experts, void* workspace,
+                              size_t workspace_bytes, mp_stream_t stream) {
+  if (!plan_i32 || num_local_experts <= 0 || num_local_experts > kMaxExperts) return MP_ERR_INVALID_ARG;
+  StageBuffers b;
+  const int rc = stage_buffers(workspace, workspace_bytes, padded_rows, I, b);
+  if (rc != MP_OK) return rc;
+  const int* plan = static_cast<const int*>(plan_i32);
+  moe_requant_kernel<<<padded_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(b.h, b.absmax, I,
+                                                                                plan + 3 * num_local_experts + 1, b.q2, b.scale2);
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_moe_gemm2(const void* plan_i32, int padded_rows, int I, int H, int num_local_experts,
+                            const void* w2_q_i8, const void* w2_scale_f32, void* d_out_f16, void* workspace,
+                            size_t workspace_bytes, int tile_part, int* error_word, mp_stream_t stream) {
+  if (!plan_i32 || !w2_q_i8 || !w2_scale_f32 || !d_out_f16 || H <= 0 || num_local_experts <= 0 || tile_part < -1 ||
+      tile_part > 1)
+    return MP_ERR_INVALID_ARG;
+  if (H % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
+  if (!aligned(w2_q_i8, 16) || !aligned(d_out_f16, 16)) return MP_ERR_ALIGNMENT;
+  StageBuffers b;
+  const int rc = stage_buffers(workspace, workspace_bytes, padded_rows, I, b);
+  if (rc != MP_OK) return rc;
+  const int E = num_local_experts;
+  const int* plan = static_cast<const int*>(plan_i32);
+  return launch_moe_gemm2(b.q2, b.scale2, w2_q_i8, static_cast<const float*>(w2_scale_f32), padded_rows, I, H, E,
+                          plan + 3 * E + 1, plan + 3 * E + 2, d_out_f16, error_word, static_cast<cudaStream_t>(stream),
+                          nullptr, tile_part);
+}
+
 extern "C" int mp_moe_expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
                                    int padded_rows, int H, int I, int num_local_experts,
                                    const void* w13_q_i8, const void* w13_scale_f32, const void* w2_q_i8,

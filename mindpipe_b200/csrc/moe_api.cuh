@@ -45,11 +45,17 @@ __device__ __forceinline__ bool ep_locate(const int* xplan, int world, int e_loc
 // h[r, n] = f16(silu(f16(gate)) * f16(up)) for the expert-sorted int8 rows, plus per-row max |h|.
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
-                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st);
+                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st, int tile_part = -1);
 
 // d[r, :] = f16(acc * scale2[r] * w2_scale[e, :]) for the re-quantised rows.
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
                      int I, int H, int E, const int* num_tiles_dev, const int* tile_expert, void* d_out,
-                     int* error_word, cudaStream_t st, const RowScatter* scatter = nullptr);
+                     int* error_word, cudaStream_t st, const RowScatter* scatter = nullptr, int tile_part = -1);
+
+// tile_part: -1 = every row tile; 0 / 1 = the first / second half of the 256-row tiles in use (the halves are
+// split at (tiles + 1) / 2, the same split mp_moe_ep_pull_part / mp_moe_ep_push_part use for rows).
+__host__ __device__ constexpr int moe_half_split_rows(int tiles_128) {     // first row of the second half
+  return (((tiles_128 + 1) / 2 + 1) / 2) * kMoeSegmentAlign;
+}
 
 }  // namespace mp

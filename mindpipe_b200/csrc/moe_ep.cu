@@ -158,18 +158,27 @@ __device__ __forceinline__ EpLocator ep_cache_plan(const int* __restrict__ xplan
   return EpLocator{s_seg, s_cum, s_src, world, e_loc};
 }
 
+// Rows [row_lo, row_hi) a launch handles: all padded rows in use (part < 0), or the first / second half of the
+// 256-row tiles (part 0 / 1), split where the grouped GEMMs split their row tiles.
+__device__ __forceinline__ void ep_row_range(int rows_in_use, int part, int& row_lo, int& row_hi) {
+  const int split = min(rows_in_use, moe_half_split_rows(rows_in_use / kEpTile));
+  row_lo = part == 1 ? split : 0;
+  row_hi = part == 0 ? split : rows_in_use;
+}
+
 // Sorted row i <- peer row (int8 codes and fp32 scale).  One warp per row: a lane requests all its 16-byte
 // pieces of the row before it stores the first, so a row costs one NVLink round trip; warps stride over the
 // rows in use.  VPL = 16-byte pieces per lane.
 template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xplan, int world, int e_loc, int ext,
-               int vec_per_row, uint4* __restrict__ q_sorted, float* __restrict__ s_sorted) {
+               int vec_per_row, uint4* __restrict__ q_sorted, float* __restrict__ s_sorted, int part) {
   __shared__ int s_plan[kEpLocateInts];
   const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
-  const int rows = loc.seg[e_loc];                                  // padded rows in use
+  int row_lo, rows;                                                 // padded rows in use, or one half of them
+  ep_row_range(loc.seg[e_loc], part, row_lo, rows);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
+  for (int i = row_lo + blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
     int s, src;
     if (!loc.locate(i, s, src)) {
       if (lane == 0) s_sorted[i] = 0.0f;                            // padding row: neutralised by a zero scale
@@ -195,12 +204,13 @@ ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xpl
 template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const uint4* __restrict__ d_sorted, const int* __restrict__ xplan, int world, int e_loc, int ext,
-               int vec_per_row, PeerPtrs peer_back) {
+               int vec_per_row, PeerPtrs peer_back, int part) {
   __shared__ int s_plan[kEpLocateInts];
   const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
-  const int rows = loc.seg[e_loc];
+  int row_lo, rows;
+  ep_row_range(loc.seg[e_loc], part, row_lo, rows);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
+  for (int i = row_lo + blockIdx.x * 8 + warp; i < rows; i += gridDim.x * 8) {
     int s, src;
     if (!loc.locate(i, s, src)) continue;
     const uint4* from = d_sorted + (size_t)i * vec_per_row;
@@ -398,9 +408,10 @@ extern "C" int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int 
   return MP_OK;
 }
 
-extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,
-                              int world, int num_local_experts, int capacity_rows, int H, void* q_sorted_i8,
-                              void* scale_sorted_f32, mp_stream_t stream) {
+extern "C" int mp_moe_ep_pull_part(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs,
+                                   const void* xplan_i32, int world, int num_local_experts, int capacity_rows, int H,
+                                   void* q_sorted_i8, void* scale_sorted_f32, int part, mp_stream_t stream) {
+  if (part < -1 || part > 1) return MP_ERR_INVALID_ARG;
   PeerPtrs pq, ps;
   int rc = fill_peers(pq, peer_q_ptrs, world);
   if (rc != MP_OK) return rc;
@@ -416,15 +427,17 @@ extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const*
   const int* xp = static_cast<const int*>(xplan_i32);
   uint4* qd = static_cast<uint4*>(q_sorted_i8);
   float* sd = static_cast<float*>(scale_sorted_f32);
-  if (vec == 256) ep_pull_kernel<8><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
-  else if (vec == 128) ep_pull_kernel<4><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
-  else ep_pull_kernel<0><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd);
+  if (vec == 256) ep_pull_kernel<8><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
+  else if (vec == 128) ep_pull_kernel<4><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
+  else ep_pull_kernel<0><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }
 
-extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
-                              int capacity_rows, int H, const void* const* peer_back_ptrs, mp_stream_t stream) {
+extern "C" int mp_moe_ep_push_part(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                                   int capacity_rows, int H, const void* const* peer_back_ptrs, int part,
+                                   mp_stream_t stream) {
+  if (part < -1 || part > 1) return MP_ERR_INVALID_ARG;
   PeerPtrs pb;
   int rc = fill_peers(pb, peer_back_ptrs, world);
   if (rc != MP_OK) return rc;
@@ -437,9 +450,22 @@ extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint4* dd = static_cast<const uint4*>(d_sorted_f16);
   const int* xp = static_cast<const int*>(xplan_i32);
-  if (vec == 512) ep_push_kernel<16><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
-  else if (vec == 256) ep_push_kernel<8><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
-  else ep_push_kernel<0><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb);
+  if (vec == 512) ep_push_kernel<16><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
+  else if (vec == 256) ep_push_kernel<8><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
+  else ep_push_kernel<0><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
   MP_LAUNCH_CHECK();
   return MP_OK;
+}
+
+extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,
+                              int world, int num_local_experts, int capacity_rows, int H, void* q_sorted_i8,
+                              void* scale_sorted_f32, mp_stream_t stream) {
+  return mp_moe_ep_pull_part(peer_q_ptrs, peer_scale_ptrs, xplan_i32, world, num_local_experts, capacity_rows, H,
+                             q_sorted_i8, scale_sorted_f32, -1, stream);
+}
+
+extern "C" int mp_moe_ep_push(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                              int capacity_rows, int H, const void* const* peer_back_ptrs, mp_stream_t stream) {
+  return mp_moe_ep_push_part(d_sorted_f16, xplan_i32, world, num_local_experts, capacity_rows, H, peer_back_ptrs, -1,
+                             stream);
 }

@@ -44,6 +44,8 @@ struct GemmParams {
   int* partial;
   RowScatter scatter;          // expert-parallel GEMM2: rows are stored at home (peer memory), see moe_api.cuh
   int group_m;                 // tile order: groups of this many M tiles are swept across all of N before the next group
+  int tile_part;               // grouped: -1 = all row tiles, 0 / 1 = the first / second half of them (two launches whose
+                               //          neighbours -- the pull of the other half, the push of this one -- overlap them)
   const int* m_tiles_dev;      // grouped: number of 128-row tiles in use (device side)
   const int* tile_expert;      // grouped: expert of each 128-row tile
   int b_rows_per_expert;       // grouped: weight rows per expert (2I for gate/up, H for down)
@@ -170,7 +172,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // tiles are 128 (PAIR: 256) rows of the activations; the grouped plan counts 128-row units
   const int m_units = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
-  const int m_tiles = PAIR ? (m_units + 1) / 2 : m_units;
+  const int m_tiles_all = PAIR ? (m_units + 1) / 2 : m_units;
+  // a launch may take one half of the row tiles (grouped mode): [m_lo, m_lo + m_tiles)
+  const int m_mid = (m_tiles_all + 1) / 2;
+  const int m_lo = p.tile_part == 1 ? m_mid : 0;
+  const int m_tiles = p.tile_part < 0 ? m_tiles_all : (p.tile_part == 0 ? m_mid : m_tiles_all - m_mid);
   const int total = m_tiles * p.n_tiles * p.k_split;           // work items: (tile, K slice)
   const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
   const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
@@ -181,10 +187,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (grouped) {
     if (threadIdx.x == 0) {
       int g = 0, i = 0;
-      while (i < m_tiles && g < kMaxTileGroups) {
-        const int e = p.tile_expert[PAIR ? 2 * i : i];
+      while (i < m_tiles && g < kMaxTileGroups) {      // indices relative to m_lo
+        const int e = p.tile_expert[PAIR ? 2 * (m_lo + i) : m_lo + i];
         int j = i + 1;
-        while (j < m_tiles && p.tile_expert[PAIR ? 2 * j : j] == e) ++j;
+        while (j < m_tiles && p.tile_expert[PAIR ? 2 * (m_lo + j) : m_lo + j] == e) ++j;
         const int len = j - i, parts = (len + 2 * p.group_m - 1) / (2 * p.group_m);
         for (int q = 0; q < parts && g < kMaxTileGroups; ++q) s_gfirst[g++] = i + (len * q) / parts;
         i = j;
@@ -195,8 +201,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncthreads();
   }
   auto coords = [&](int tile, int& m_tile, int& n_tile) {
-    if (grouped) tile_coords_grouped(tile, p.n_tiles, s_gfirst, s_groups, m_tile, n_tile);
-    else tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
+    if (grouped) {
+      tile_coords_grouped(tile, p.n_tiles, s_gfirst, s_groups, m_tile, n_tile);
+      m_tile += m_lo;
+    } else {
+      tile_coords(tile, m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
+    }
   };
 
   if (warp == 0) {
@@ -576,6 +586,7 @@ struct GemmCall {
   const int* m_tiles_dev; const int* tile_expert; int b_rows_per_expert; int up_row_offset;
   unsigned int* row_absmax;
   int* error_word;
+  int tile_part = -1;
 };
 
 template <int BN, int EPI, bool PAIR = false>
@@ -598,6 +609,7 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
   p.a_scale = c.a_scale; p.b_scale = c.b_scale; p.bias = c.bias; p.out = c.out;
   p.row_absmax = c.row_absmax; p.error_word = c.error_word;
   p.group_m = PAIR ? 8 : 16;            // 2048 activation rows per group
+  p.tile_part = c.m_tiles_dev ? c.tile_part : -1;
   p.k_split = c.k_split > 1 ? c.k_split : 1;
   p.kb_per_split = (p.k_blocks + p.k_split - 1) / p.k_split;
   p.partial = c.partial;
@@ -678,26 +690,29 @@ static int check_gemm_args(const void* a, const void* b, void* out, int M, int N
 // Grouped GEMMs of the MoE expert chain (declared in moe_api.cuh).
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
-                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st) {
+                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st, int tile_part) {
   GemmCall c{};
   c.a = routed_q; c.b = w13_q; c.M = padded_rows; c.N = I; c.K = H; c.a_rows = padded_rows;
   c.b_rows_total = E * 2 * I;
   c.a_scale = routed_scale; c.b_scale = w13_scale; c.out = h_out;
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = 2 * I; c.up_row_offset = I;
   c.row_absmax = row_absmax; c.error_word = error_word;
-  MP_CUDA_TRY(cudaMemsetAsync(row_absmax, 0, sizeof(unsigned int) * (size_t)padded_rows, st));
+  c.tile_part = tile_part;
+  // the second half's launch must not clear the maxima the first half has produced
+  if (tile_part <= 0) MP_CUDA_TRY(cudaMemsetAsync(row_absmax, 0, sizeof(unsigned int) * (size_t)padded_rows, st));
   return launch_gemm<256, EPI_SWIGLU, true>(c, st);   // expert segments are 256-row aligned: pair tiles fit
 }
 
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,
                      int I, int H, int E, const int* num_tiles_dev, const int* tile_expert, void* d_out,
-                     int* error_word, cudaStream_t st, const RowScatter* scatter) {
+                     int* error_word, cudaStream_t st, const RowScatter* scatter, int tile_part) {
   GemmCall c{};
   c.a = q2; c.b = w2_q; c.M = padded_rows; c.N = H; c.K = I; c.a_rows = padded_rows; c.b_rows_total = E * H;
   c.a_scale = scale2; c.b_scale = w2_scale; c.out = d_out;
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = H;
   c.error_word = error_word;
   c.scatter = scatter;
+  c.tile_part = tile_part;
   return launch_gemm<256, EPI_F16, true>(c, st);
 }
 

@@ -177,8 +177,9 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
     """Expert-parallel W8A8 MoE whose dispatch and return run over NVLink peer memory, driven
     entirely from the device: no row count ever visits the host and the barrier epochs live in
     device memory, so a forward is a fixed sequence of stream-ordered launches (route -> barrier ->
-    plan -> pull -> expert stage -> push -> barrier -> combine) that can be captured in a CUDA graph and replayed (every rank must replay it the same
-    number of times).
+    plan -> pull -> expert stage -> push -> barrier -> combine; with ``overlap`` the pull, both GEMMs and the push
+    run in two halves on two streams) that can be captured in a CUDA graph and replayed (every rank must replay
+    it the same number of times).
 
     Each rank keeps its routing plan, routed int8 rows, their scales and a result buffer in one
     symmetric allocation that every peer maps (``torch.distributed._symmetric_memory``).  Peers
@@ -189,9 +190,16 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
     """
 
     def __init__(self, experts, num_experts: int, max_tokens_per_rank: int, top_k: int = 2, group=None,
-                 fuse_return: bool = False):
+                 fuse_return: bool = False, overlap: bool = False):
         super().__init__()
         import torch.distributed._symmetric_memory as symm
+        # True: the expert GEMMs run in two halves of the row tiles and the exchange overlaps them on a second
+        # stream -- the pull of the second half beside the first half's GEMM1, the push of the first half beside
+        # the second half's GEMM2 (stream-level dependencies only, so the forward still captures into one graph).
+        # Bit-identical; measured at 2 GPUs on the Mixtral-shaped layer it hides nothing (1.186 vs 1.176 ms): the
+        # GEMMs run against the power cap, so a copy kernel beside them costs them the clocks it saves in time,
+        # and each GEMM pays a second launch and tail.  Hence off by default.
+        self.overlap = bool(overlap) and not fuse_return
         # True: the second GEMM's epilogue stores results at home instead of a push kernel.  Measured on the
         # Mixtral-shaped layer: equal at 2 GPUs, 11 % slower at 8 (0.418 vs 0.375 ms) -- the row-per-thread
         # 64-byte peer stores hold the epilogue warps -- so the separate push kernel stays the default.
@@ -246,6 +254,66 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
         self.q_sorted = torch.empty((self.sorted_cap, self.hidden), dtype=torch.int8, device=dev)
         self.s_sorted = torch.empty(self.sorted_cap, dtype=torch.float32, device=dev)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)     # advanced by the barrier kernel itself
+        if self.overlap:
+            # buffers that two streams touch are owned by the module, not taken from the caching allocator per call
+            self.side = torch.cuda.Stream(device=dev)
+            self.stage_bytes = int(lib.mp_moe_expert_stage_workspace_bytes(self.sorted_cap, self.inter))
+            self.stage_ws = torch.empty(self.stage_bytes, dtype=torch.uint8, device=dev)
+            self.d_sorted = torch.empty((self.sorted_cap, self.hidden), dtype=torch.float16, device=dev)
+
+    def _expert_stage_overlapped(self, h: int):
+        """pull | GEMM1 | requant | GEMM2 | push with each GEMM in two halves of the row tiles; the second half's
+        pull and the first half's push run on ``self.side`` next to the other half's GEMM.  Only events order the
+        two streams, so the sequence captures into a CUDA graph as a fork and a join."""
+        from . import _lib, ops
+        lib = _lib.load()
+        ex = self.experts
+        main = torch.cuda.current_stream()
+        side = self.side
+        err = ops._error_word(self.buf.device).data_ptr()
+        xp, ws, nb = self.xplan.data_ptr(), self.stage_ws.data_ptr(), self.stage_bytes
+
+        def pull(part, stream):
+            _lib.check(lib.mp_moe_ep_pull_part(self.p_q, self.p_scale, xp, self.world, self.e_loc, self.sorted_cap, h,
+                                               self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), part,
+                                               stream.cuda_stream), "moe_ep_pull")
+
+        def push(part, stream):
+            _lib.check(lib.mp_moe_ep_push_part(self.d_sorted.data_ptr(), xp, self.world, self.e_loc, self.sorted_cap, h,
+                                               self.p_back, part, stream.cuda_stream), "moe_ep_push")
+
+        def gemm1(part):
+            _lib.check(lib.mp_moe_gemm1_swiglu(self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), xp, self.sorted_cap, h,
+                                               self.inter, self.e_loc, ex.gate_up_proj.data_ptr(),
+                                               ex.gate_up_proj_scale.data_ptr(), ws, nb, part, err, main.cuda_stream),
+                       "moe_gemm1_swiglu")
+
+        def gemm2(part):
+            _lib.check(lib.mp_moe_gemm2(xp, self.sorted_cap, self.inter, h, self.e_loc, ex.down_proj.data_ptr(),
+                                        ex.down_proj_scale.data_ptr(), self.d_sorted.data_ptr(), ws, nb, part, err,
+                                        main.cuda_stream), "moe_gemm2")
+
+        planned = torch.cuda.Event()
+        planned.record(main)
+        side.wait_event(planned)                           # fork: the plan is in place
+        pull(0, main)
+        pull(1, side)
+        pulled = torch.cuda.Event()
+        pulled.record(side)
+        gemm1(0)
+        main.wait_event(pulled)
+        gemm1(1)
+        _lib.check(lib.mp_moe_requant(xp, self.sorted_cap, self.inter, self.e_loc, ws, nb, main.cuda_stream), "moe_requant")
+        gemm2(0)
+        half_done = torch.cuda.Event()
+        half_done.record(main)
+        side.wait_event(half_done)
+        push(0, side)
+        pushed = torch.cuda.Event()
+        pushed.record(side)
+        gemm2(1)
+        push(1, main)
+        main.wait_event(pushed)                            # join
 
     def _barrier(self):
         from . import _lib, ops
@@ -272,10 +340,15 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
         self._barrier()                                    # every rank's routed rows and plan are in place
         _lib.check(lib.mp_moe_ep_plan(self.p_plan, self.world, self.rank, self.num_experts, self.sorted_cap,
                                       self.xplan.data_ptr(), stream), "moe_ep_plan")
+        ex = self.experts
+        if self.overlap:
+            self._expert_stage_overlapped(h)
+            self._barrier()                                # every result row has landed at home
+            out = ops.moe_combine(self.back, routing.dest_row, ids, w, t)
+            return out.reshape(shape)
         _lib.check(lib.mp_moe_ep_pull(self.p_q, self.p_scale, self.xplan.data_ptr(), self.world, self.e_loc,
                                       self.sorted_cap, h, self.q_sorted.data_ptr(), self.s_sorted.data_ptr(), stream),
                    "moe_ep_pull")
-        ex = self.experts
         if self.fuse_return:
             # both grouped GEMMs; the second one's epilogue stores each result row at its original position in
             # the source rank's buffer (peer stores over NVLink): the return path costs no kernel of its own

@@ -65,14 +65,15 @@ def verify_multi_gpu(rank: int, world: int, dev: torch.device, oracle=None) -> d
         out = ExpertParallelMoE(local, shape.num_experts)(xa, ia, wa)          # NCCL all-to-all fallback
         ops.check_device_errors()
         ok_ep = torch.equal(out, ref[a:b])
-        sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7)
-        for _ in range(3):                                                       # repeated forwards reuse the buffers
-            out2 = sym(xa, ia, wa)
-        ops.check_device_errors()
-        ok_ep = ok_ep and torch.equal(out2, ref[a:b])
-        out3 = _graph_replays(lambda: sym(xa, ia, wa), lambda o: o, dev)        # barrier epochs live on the device
-        ops.check_device_errors()
-        ok_ep = ok_ep and torch.equal(out3, ref[a:b])
+        for overlap in (False, True):            # serial launch sequence; halves of the GEMMs overlapped with the exchange
+            sym = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, overlap=overlap)
+            for _ in range(3):                                                   # repeated forwards reuse the buffers
+                out2 = sym(xa, ia, wa)
+            ops.check_device_errors()
+            ok_ep = ok_ep and torch.equal(out2, ref[a:b])
+            out3 = _graph_replays(lambda: sym(xa, ia, wa), lambda o: o, dev)    # barrier epochs live on the device
+            ops.check_device_errors()
+            ok_ep = ok_ep and torch.equal(out3, ref[a:b])
         sym2 = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, fuse_return=True)
         for _ in range(3):
             out4 = sym2(xa, ia, wa)
