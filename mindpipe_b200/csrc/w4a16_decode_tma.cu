@@ -70,10 +70,24 @@ struct DecodeTmaParams {
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Ring reads by 32-bit shared-window address.  The ring pointer is derived by integer arithmetic (1 KB alignment),
+// which hides the address space from the compiler: written as plain dereferences these were generic loads.
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  // not volatile: free to move among the MMAs; the memory clobber keeps it behind the stage's barrier wait
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 // (k0..k7 in natural order) -> (k0,k4) (k1,k5) (k2,k6) (k3,k7), the order dequant8 emits
@@ -107,7 +121,7 @@ constexpr uint32_t kOnesLo = 0x00010001u, kOnesHi = 0x00100010u;
 // D = A * B with a zero accumulator input (no register has to be cleared first)
 __device__ __forceinline__ void mma_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
@@ -219,24 +233,25 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int w_off = (wn * 32 + g) * 128 + (((kh * 4 + t) ^ g) << 4);                 // + r * 8 * 128
     const int x_off = dt::kWBytes + (kh * 2 + (t >> 1)) * C::kXSub + g * 128;          // + ((cc ^ g) << 4) (+ 8 rows)
     const int sz_off = dt::kWBytes + C::kXBytes + (grp_local * dt::kRows + wn * 32 + g) * 4;   // + r * 32
+    const uint32_t ring_addr = smem_u32(ring);
     bool ok = true;
     for (int i = 0; i < n_stages; ++i) {
       const int s = i % dt::kStages;
       const uint32_t phase = (i / dt::kStages) & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, phase, abort_flag));
       if (!ok) break;
-      const unsigned char* base = ring + s * C::kStageBytes;
+      const uint32_t base = ring_addr + s * C::kStageBytes;
       if constexpr (FOLD) {
         static_assert(HALF || !FOLD, "the folded form is written for the swapped-operand (M <= 8) layout");
         uint4 q[4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) q[r] = *reinterpret_cast<const uint4*>(base + w_off + r * 1024);
+        for (int r = 0; r < 4; ++r) q[r] = lds_v4(base + w_off + r * 1024);
         float raw[2][4];
         float ones[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int xo = x_off + ((((t & 1) * 4 + c) ^ g) << 4);
-          const uint4 alo = scale_odd_pairs(pair_permute(*reinterpret_cast<const uint4*>(base + xo)));
+          const uint4 alo = scale_odd_pairs(pair_permute(lds_v4(base + xo)));
           if (c == 0) {
             mma_16816_first(ones, kOnesLo, kOnesLo, kOnesHi, kOnesHi, alo.x, alo.y);
           } else {
@@ -264,7 +279,7 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         // raw[rp]: [0],[1] = row g of row group 2rp, tokens 2t, 2t+1; [2],[3] = row g of row group 2rp+1
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          const uint32_t szw = *reinterpret_cast<const uint32_t*>(base + sz_off + r * 32);
+          const uint32_t szw = lds_u32(base + sz_off + r * 32);
           const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&szw));
           const float s24 = szf.x * 16777216.0f;
 #pragma unroll
@@ -278,15 +293,15 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         ScaleZero sp[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          q[r] = *reinterpret_cast<const uint4*>(base + w_off + r * 1024);
-          const uint32_t szw = *reinterpret_cast<const uint32_t*>(base + sz_off + r * 32);
+          q[r] = lds_v4(base + w_off + r * 1024);
+          const uint32_t szw = lds_u32(base + sz_off + r * 32);
           const __half2 h = *reinterpret_cast<const __half2*>(&szw);
           sp[r] = make_scale_zero(__low2half(h), __high2half(h));
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int xo = x_off + ((((t & 1) * 4 + c) ^ g) << 4);
-          const uint4 alo = pair_permute(*reinterpret_cast<const uint4*>(base + xo));
+          const uint4 alo = pair_permute(lds_v4(base + xo));
           if (HALF) {
             // weights are the A operand: the row groups 2rp and 2rp+1 fill one 16-row tile, the 8 token
             // rows are the B operand.  acc[2*rp] is the tile D[16 weight rows][8 tokens]:
@@ -304,7 +319,7 @@ w4a16_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
               mma_16816(acc[2 * rp], h2_as_u32(va[2]), h2_as_u32(vb[2]), h2_as_u32(va[3]), h2_as_u32(vb[3]), alo.z, alo.w);
             }
           } else {
-            const uint4 ahi = pair_permute(*reinterpret_cast<const uint4*>(base + xo + 1024));
+            const uint4 ahi = pair_permute(lds_v4(base + xo + 1024));
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
               const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
