@@ -136,6 +136,29 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       : "memory");
 }
 
+// Ring accesses by 32-bit shared-window address (the 1 KB-aligned ring pointer hides the address space from the
+// compiler; plain dereferences of it are generic loads and stores).
+__device__ __forceinline__ uint4 du_lds_v4(uint32_t addr) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+// volatile instead of a memory clobber: keeps its place among the other volatile statements (barrier waits,
+// stores) without being a compiler barrier between neighbouring loads
+__device__ __forceinline__ uint4 du_lds_v4_ordered(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t du_lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void du_sts_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w));
+}
+
 // eight fp16 values (k0..k7) -> (k0,k4,k1,k5,k2,k6,k3,k7), the column order dequant8 emits
 __device__ __forceinline__ uint4 pair_permute_u4(const uint4 in) {
   uint4 v;
@@ -275,9 +298,15 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       const int s = i % STAGES;
       const uint32_t phase = (i / STAGES) & 1;
       if (!__all_sync(0xffffffffu, mbar_wait_sleep(full0 + 8 * s, phase, abort_flag, 400))) break;
-      uint4* xt = reinterpret_cast<uint4*>(ring + s * stage_bytes + du::kWBytes);
-#pragma unroll 4
-      for (int c = lane; c < kXBytes / 16; c += 32) xt[c] = pair_permute_u4(xt[c]);
+      const uint32_t xt = smem_u32(ring + s * stage_bytes + du::kWBytes);
+      // four chunks per lane in flight: the loads are issued together, then permuted and stored
+      for (int c = lane; c < kXBytes / 16; c += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = du_lds_v4_ordered(xt + (c + 32 * j) * 16);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) du_sts_v4(xt + (c + 32 * j) * 16, pair_permute_u4(v[j]));
+      }
       fence_proxy_async_smem();                                // generic-proxy stores -> visible to the MMA's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(xp0 + 8 * s);
@@ -294,19 +323,20 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
     for (int j = 0; j < 4; ++j) w_off[j] = row * 128 + (((kh * 4 + j) ^ sw) << 4);
     const int sz_off = du::kWBytes + kXBytes + row * 4;
+    const uint32_t ring_addr = smem_u32(ring);
     int rb = t0 / ST, st = t0 - rb * ST;
     int seg_begin_i = 0, seg_begin_st = st, seg_idx = 0;
     for (int i = 0; i < n_stages; ++i) {
       const int s = i % STAGES;
       const uint32_t phase = (i / STAGES) & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, phase, abort_flag))) break;
-      const unsigned char* base = ring + s * stage_bytes;
+      const uint32_t base = ring_addr + s * stage_bytes;
       uint4 q4[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) q4[j] = *reinterpret_cast<const uint4*>(base + w_off[j]);
+      for (int j = 0; j < 4; ++j) q4[j] = du_lds_v4(base + w_off[j]);
       ScaleZero sp;
       {
-        const uint32_t szw = *reinterpret_cast<const uint32_t*>(base + sz_off + grp0 * (du::kRows * 4));
+        const uint32_t szw = du_lds_u32(base + sz_off + grp0 * (du::kRows * 4));
         const __half2 h = *reinterpret_cast<const __half2*>(&szw);
         sp = make_scale_zero(__low2half(h), __high2half(h));
       }
@@ -321,7 +351,7 @@ w4a16_decode_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       for (int j = 0; j < 4; ++j) {
         if (j > 0 && short_groups && ((j * 32) & (p.group - 1)) == 0) {   // groups of 32 or 64 columns: next (scale, zero)
           const int grp = (kh * 128 + j * 32) >> p.gshift;
-          const uint32_t szw = *reinterpret_cast<const uint32_t*>(base + sz_off + grp * (du::kRows * 4));
+          const uint32_t szw = du_lds_u32(base + sz_off + grp * (du::kRows * 4));
           const __half2 h = *reinterpret_cast<const __half2*>(&szw);
           sp = make_scale_zero(__low2half(h), __high2half(h));
         }
