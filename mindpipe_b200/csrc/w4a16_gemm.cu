@@ -346,7 +346,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
         const __half2 hz = *reinterpret_cast<const __half2*>(&szc);
         const ScaleZero sp = make_scale_zero(__low2half(hz), __high2half(hz));
         if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag))) { ok = false; break; }
-        unsigned char* row_base = sB + stage * kBStage + row_off;
+        const uint32_t row_base = smem_u32(sB + stage * kBStage + row_off);   // st.shared below, not generic stores
 #pragma unroll
         for (int jj = 0; jj < 4 * kVec; ++jj) {                   // 16-byte chunk j = columns 8j..8j+7
           const int j = part * 4 + jj;
@@ -360,7 +360,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4GemmParams
           o.y = prmt(c, d, 0x5410);
           o.z = prmt(a, b, 0x7632);
           o.w = prmt(c, d, 0x7632);
-          *reinterpret_cast<uint4*>(row_base + ((j ^ sw) << 4)) = o;   // 128-byte swizzle
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + ((j ^ sw) << 4)), "r"(o.x), "r"(o.y),
+                       "r"(o.z), "r"(o.w) : "memory");                // 128-byte swizzle
         }
         fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
