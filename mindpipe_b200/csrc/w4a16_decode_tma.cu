@@ -505,7 +505,10 @@ static int launch_tma(const CUtensorMap& tw, const CUtensorMap& tx, const CUtens
   attrs[0].val.clusterDim.y = ck;
   attrs[0].val.clusterDim.z = 1;
   int n_attrs = 1;
-  if (pdl && !PUSH) {      // a push launch shares its block counter with the previous one: no early start
+  // (push launches too: their block counter and call number are touched only after griddepcontrol.wait, i.e. after
+  // the previous push kernel and the finish kernel between them have completed; the early start lets the next
+  // shard's weight fetch run under the exchange)
+  if (pdl) {
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     n_attrs = 2;
