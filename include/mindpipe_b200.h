@@ -590,6 +590,11 @@ int mp_w4a16_rowparallel_finish_ll(const void* partial0_f32, const void* partial
                                    void* const* peer_recv2_0, void* const* peer_recv2_1, int world, int rank,
                                    const void* epoch_counter_u32, int M, int N, const void* bias_f16,
                                    void* y_f16, int* error_word, mp_stream_t stream);
+/* mp_peer_barrier_counted followed by mp_moe_ep_plan in one launch (the block meets its peers, then reads their
+ * counts): one kernel less on the path of every layer. */
+int mp_moe_ep_barrier_plan(const void* const* peer_flag_ptrs, const void* const* peer_plan_ptrs, int world, int rank,
+                           void* epoch_counter_u32, int num_experts, int capacity_rows, void* xplan_i32,
+                           int* error_word, mp_stream_t stream);
 size_t mp_moe_ep_plan_ints(int world, int num_local_experts, int capacity_rows);
 int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int rank, int num_experts,
                    int capacity_rows, void* xplan_i32, mp_stream_t stream);

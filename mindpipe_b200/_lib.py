@@ -78,6 +78,7 @@ SIGNATURES = {
     "mp_w4a16_rowparallel_finish_ll": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_moe_ep_plan_ints": (_Z, [_I, _I, _I]),
     "mp_moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P]),
+    "mp_moe_ep_barrier_plan": (_I, [_P, _P, _I, _I, _P, _I, _I, _P, _P, _P]),
     "mp_moe_ep_pull": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "mp_moe_ep_push": (_I, [_P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull_part": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),

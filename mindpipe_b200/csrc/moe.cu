@@ -87,6 +87,48 @@ __global__ void moe_plan_kernel(int* __restrict__ plan, int E, int max_tiles) {
   *num_tiles = tiles;
 }
 
+// Count and plan in one launch (one block): the per-expert counts are taken in shared memory, thread 0 lays out the
+// padded segments exactly as moe_plan_kernel does, and the scales of every segment's padding rows are zeroed -- so
+// the routing needs no memset of the counters or of the scale buffer and two launches instead of five nodes.
+__global__ void __launch_bounds__(1024)
+moe_count_plan_kernel(const int* __restrict__ ids, int n_entries, int lo, int hi, int* __restrict__ plan, int E,
+                      int max_tiles, float* __restrict__ routed_scale) {
+  __shared__ int s_counts[kMaxExperts];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) s_counts[i] = 0;
+  __syncthreads();
+  for (int i0 = 0; i0 < n_entries; i0 += blockDim.x) {          // uniform trip count: the vote below is warp-wide
+    const int i = i0 + threadIdx.x;
+    const int e = i < n_entries ? ids[i] : -1;
+    const int key = (e >= lo && e < hi) ? e - lo : -1;
+    const unsigned int same = __match_any_sync(0xffffffffu, key);   // one shared-memory add per expert and warp
+    if (key >= 0 && (threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_counts[key], __popc(same));
+  }
+  __syncthreads();
+  int* counts = plan;
+  int* cursors = plan + E;
+  int* seg = plan + 2 * E;
+  if (threadIdx.x == 0) {
+    int* num_tiles = plan + 3 * E + 1;
+    int* tile_expert = plan + 3 * E + 2;
+    int off = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      counts[e] = s_counts[e];
+      seg[e] = off;
+      cursors[e] = 0;
+      const int nt = moe_segment_tiles(s_counts[e]);
+      for (int i = 0; i < nt && tiles < max_tiles; ++i) tile_expert[tiles++] = e;
+      off += nt * kTileRows;
+    }
+    seg[E] = off;
+    *num_tiles = tiles;
+  }
+  __syncthreads();
+  // padding rows get scale 0, so whatever codes they hold turn into zeros downstream
+  for (int e = 0; e < E; ++e)
+    for (int r = seg[e] + s_counts[e] + threadIdx.x; r < seg[e + 1]; r += blockDim.x) routed_scale[r] = 0.0f;
+  for (int r = seg[E] + threadIdx.x; r < max_tiles * kTileRows; r += blockDim.x) routed_scale[r] = 0.0f;   // unused tail
+}
+
 // One block per routed entry (t, j): claim a row in the expert's segment, record it, and
 // write the token's int8 codes and scale there -- the gather and the per-token quant of
 // npu_moe_init_routing_quant (acceleration/runtime_patches/vllm_ascend.patch:2369-2379)
@@ -263,15 +305,24 @@ extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* top
   int* plan = static_cast<int*>(plan_i32);
   const int n_entries = T * k;
   const int padded = mp_moe_padded_rows(E, n_entries);
-  MP_CUDA_TRY(cudaMemsetAsync(plan, 0, sizeof(int) * E, st));
-  // padding rows get scale 0, so whatever codes they hold turn into zeros downstream
-  MP_CUDA_TRY(cudaMemsetAsync(routed_scale_f32, 0, sizeof(float) * padded, st));
-  int blocks = (n_entries + 255) / 256;
-  if (blocks > 4 * kSmCount) blocks = 4 * kSmCount;
-  moe_count_kernel<<<blocks, 256, 0, st>>>(static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi, plan);
-  MP_LAUNCH_CHECK();
-  moe_plan_kernel<<<1, 32, 0, st>>>(plan, E, padded / kTileRows);
-  MP_LAUNCH_CHECK();
+  if (n_entries <= 8192) {
+    // few entries (a rank's share under expert parallelism, decode batches): one block counts, plans and zeroes the
+    // padding rows' scales -- two launches instead of five graph nodes; with more entries one block's pass over the
+    // ids costs what the extra nodes do (16384 entries: equal within 0.2 %), so those keep the multi-block count
+    moe_count_plan_kernel<<<1, 1024, 0, st>>>(static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi,
+                                              plan, E, padded / kTileRows, static_cast<float*>(routed_scale_f32));
+    MP_LAUNCH_CHECK();
+  } else {
+    MP_CUDA_TRY(cudaMemsetAsync(plan, 0, sizeof(int) * E, st));
+    // padding rows get scale 0, so whatever codes they hold turn into zeros downstream
+    MP_CUDA_TRY(cudaMemsetAsync(routed_scale_f32, 0, sizeof(float) * padded, st));
+    int blocks = (n_entries + 255) / 256;
+    if (blocks > 4 * kSmCount) blocks = 4 * kSmCount;
+    moe_count_kernel<<<blocks, 256, 0, st>>>(static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi, plan);
+    MP_LAUNCH_CHECK();
+    moe_plan_kernel<<<1, 32, 0, st>>>(plan, E, padded / kTileRows);
+    MP_LAUNCH_CHECK();
+  }
   moe_gather_quant_kernel<<<n_entries, 256, 0, st>>>(
       static_cast<const __half*>(hidden_f16), static_cast<const int*>(topk_ids_i32), H, k, expert_lo, expert_hi, plan,
       E, static_cast<int*>(dest_row_i32), static_cast<int8_t*>(routed_q_i8), static_cast<float*>(routed_scale_f32));

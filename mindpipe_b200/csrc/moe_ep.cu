@@ -82,8 +82,8 @@ __global__ void peer_barrier_counted_kernel(PeerPtrs peer_flags, int world, int 
 //                                       (counts[El] | cursors[El] | seg[El+1] | num_tiles | tile_expert[...])
 //   ext + e*(W+1) + s                   cum[e][s]: rows of local expert e that come from ranks < s
 //   ext + El*(W+1) + e*W + s            src_seg[e][s]: first row of that segment in rank s's routed buffer
-__global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_total, int e_loc, int max_tiles,
-                               int ext, int* __restrict__ xplan) {
+__device__ __forceinline__ void ep_plan_body(const PeerPtrs& peer_plans, int world, int rank, int e_total, int e_loc,
+                                             int max_tiles, int ext, int* __restrict__ xplan) {
   // one thread per (local expert, source rank) fetches that peer's count and segment offset over NVLink
   __shared__ int s_cnt[256], s_seg[256];
   const int pairs = e_loc * world;
@@ -121,6 +121,27 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
   }
   seg[e_loc] = off;
   *num_tiles = tiles;
+}
+
+__global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_total, int e_loc, int max_tiles,
+                               int ext, int* __restrict__ xplan) {
+  ep_plan_body(peer_plans, world, rank, e_total, e_loc, max_tiles, ext, xplan);
+}
+
+// The barrier in front of the plan and the plan itself in one launch: the block first meets its peers (bounded),
+// then reads their counts.  One graph node less on the path of every layer.
+__global__ void ep_barrier_plan_kernel(PeerPtrs peer_flags, PeerPtrs peer_plans, int world, int rank,
+                                       unsigned int* epoch_counter, int e_total, int e_loc, int max_tiles, int ext,
+                                       int* __restrict__ xplan, int* error_word) {
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_counter + 1;
+    *epoch_counter = s_epoch;
+  }
+  __syncthreads();
+  peer_barrier_body(peer_flags, world, rank, s_epoch, error_word);
+  __syncthreads();
+  ep_plan_body(peer_plans, world, rank, e_total, e_loc, max_tiles, ext, xplan);
 }
 
 // The part of the extended plan that ep_locate reads (segment offsets, per-source cumulative counts, source
@@ -404,6 +425,28 @@ extern "C" int mp_moe_ep_plan(const void* const* peer_plan_ptrs, int world, int 
   const int ext = 3 * e_loc + 2 + max_tiles;
   ep_plan_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, rank, num_experts, e_loc, max_tiles, ext,
                                                                   static_cast<int*>(xplan_i32));
+  MP_LAUNCH_CHECK();
+  return MP_OK;
+}
+
+extern "C" int mp_moe_ep_barrier_plan(const void* const* peer_flag_ptrs, const void* const* peer_plan_ptrs, int world,
+                                      int rank, void* epoch_counter_u32, int num_experts, int capacity_rows,
+                                      void* xplan_i32, int* error_word, mp_stream_t stream) {
+  PeerPtrs pf, pp;
+  int rc = fill_peers(pf, peer_flag_ptrs, world);
+  if (rc != MP_OK) return rc;
+  rc = fill_peers(pp, peer_plan_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (rank < 0 || rank >= world || !epoch_counter_u32 || !xplan_i32 || num_experts <= 0 || num_experts % world != 0 ||
+      capacity_rows <= 0 || capacity_rows % kMoeSegmentAlign != 0)
+    return MP_ERR_INVALID_ARG;
+  if (num_experts > 256) return MP_ERR_UNSUPPORTED;
+  const int e_loc = num_experts / world;
+  const int max_tiles = capacity_rows / kEpTile;
+  const int ext = 3 * e_loc + 2 + max_tiles;
+  ep_barrier_plan_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      pf, pp, world, rank, static_cast<unsigned int*>(epoch_counter_u32), num_experts, e_loc, max_tiles, ext,
+      static_cast<int*>(xplan_i32), error_word);
   MP_LAUNCH_CHECK();
   return MP_OK;
 }

@@ -337,9 +337,11 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
         stream = torch.cuda.current_stream().cuda_stream
         routing = ops.moe_route_gather_quant(hs, ids, 0, self.num_experts,
                                              out=(self.plan, self.routed_q, self.routed_scale))
-        self._barrier()                                    # every rank's routed rows and plan are in place
-        _lib.check(lib.mp_moe_ep_plan(self.p_plan, self.world, self.rank, self.num_experts, self.sorted_cap,
-                                      self.xplan.data_ptr(), stream), "moe_ep_plan")
+        # barrier (every rank's routed rows and plan are in place), then this rank's layout from the peers' counts
+        _lib.check(lib.mp_moe_ep_barrier_plan(self.p_flags, self.p_plan, self.world, self.rank, self.epoch.data_ptr(),
+                                              self.num_experts, self.sorted_cap, self.xplan.data_ptr(),
+                                              ops._error_word(self.buf.device).data_ptr(), stream),
+                   "moe_ep_barrier_plan")
         ex = self.experts
         if self.overlap:
             self._expert_stage_overlapped(h)
