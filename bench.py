@@ -456,6 +456,10 @@ def measure_moe(world, rank, dev, dist, iters=10):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), launch_mode
 
+    # every launch of the layer waits for its predecessor on the device (griddepcontrol.wait), so the launches may be
+    # scheduled early: the switch is read when a launch is issued, i.e. at capture time
+    from mindpipe_b200 import _lib
+    pdl_before = _lib.load().mp_set_programmatic_launch(1)
     ms, launch_mode = time_layer(layer)
     extra = {}
     if world > 1 and exchange.startswith("peer-memory"):
@@ -464,6 +468,7 @@ def measure_moe(world, rank, dev, dist, iters=10):
         halves = SymmetricExpertParallelMoE(mod, shape.num_experts, max_tokens_per_rank=t_loc, top_k=shape.top_k,
                                             overlap=True)
         extra["ms_per_layer_with_overlapped_exchange"] = time_layer(halves)[0]
+    _lib.load().mp_set_programmatic_launch(pdl_before)
     int8_ops = 2 * (shape.top_k * shape.tokens) * shape.hidden * 2 * shape.ffn + \
         2 * (shape.top_k * shape.tokens) * shape.ffn * shape.hidden
     return {"config": "mixtral-8x7b-shaped layer, 8192 tokens, top-2, experts sharded over the ranks (all-to-all)",

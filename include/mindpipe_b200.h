@@ -198,6 +198,13 @@ int mp_w4a16_linear_decode_static(const void* x_f16, const void* packed_i32, con
  * activations, bias and outputs are only touched after that kernel has
  * completed.  Enable it only when no kernel still in flight writes the weight
  * buffers (weights are loaded once and then static, as in serving).
+ * The same switch covers the W8A8 GEMMs and the kernels of the MoE layer
+ * (routing, expert-parallel exchange and barriers, re-quantisation, combine):
+ * each of them may be scheduled early, sets up its shared / tensor memory, and
+ * then waits on the device for the preceding kernel before it reads or writes
+ * anything else -- the launch latencies of the chain overlap, results are
+ * the same bits.  The setting is read when a launch is issued (for a CUDA
+ * graph: at capture).
  */
 int mp_set_programmatic_launch(int enabled);
 
@@ -610,6 +617,23 @@ int mp_moe_ep_pull_part(const void* const* peer_q_ptrs, const void* const* peer_
                         void* scale_sorted_f32, int part, mp_stream_t stream);
 int mp_moe_ep_push_part(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
                         int capacity_rows, int H, const void* const* peer_back_ptrs, int part, mp_stream_t stream);
+/*
+ * The return path with the closing barrier folded into its two neighbours (two launches instead of three).
+ * mp_moe_ep_push_signal = mp_moe_ep_push, after which the block that finishes last advances *epoch_counter_u32 and
+ * raises this rank's arrival word on every peer (peer_flag_ptrs as for mp_peer_barrier_counted; block_counter_i32
+ * is a device int that is zero between calls).  mp_moe_combine_after_peers = mp_moe_combine whose blocks first
+ * wait (bounded, 2 s -> error word 4) until every peer's arrival word in this rank's own array has reached
+ * *epoch_counter_u32, i.e. until all result rows have landed in d_f16.  Both calls go on the same stream, the push
+ * first; every rank issues the same sequence of epoch-advancing calls.
+ */
+int mp_moe_ep_push_signal(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                          int capacity_rows, int H, const void* const* peer_back_ptrs,
+                          const void* const* peer_flag_ptrs, int rank, void* epoch_counter_u32,
+                          void* block_counter_i32, mp_stream_t stream);
+int mp_moe_combine_after_peers(const void* arrival_words_u32, int world, const void* epoch_counter_u32,
+                               const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,
+                               const void* topk_weights_f16, int T, int H, int k, void* out_f16,
+                               int* error_word, mp_stream_t stream);
 
 /*
  * dst row i = src row row_map[i] (rows of row_bytes bytes; 4, or a multiple of

@@ -83,6 +83,8 @@ SIGNATURES = {
     "mp_moe_ep_push": (_I, [_P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_moe_ep_pull_part": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "mp_moe_ep_push_part": (_I, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "mp_moe_ep_push_signal": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P]),
+    "mp_moe_combine_after_peers": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
 }
 
 

@@ -29,6 +29,34 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 
 constexpr int kSmCount = 148;  // B200
 
+// ---- programmatic dependent launch for chains of short kernels -------------
+// With the process-wide switch on (mp_set_programmatic_launch), launch_chained() lets a kernel be scheduled
+// while the previous kernel of the stream is still running; the kernel itself waits for that kernel's results
+// with chain_wait() before it reads or writes anything the stream ordered, and chain_release() lets the next
+// one be scheduled in turn.  Without the attribute both instructions do nothing.
+bool decode_programmatic_launch();   // w4a16_decode_tma.cu
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+int launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = decode_programmatic_launch() ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+  return MP_OK;
+}
+#endif
+
 // ---- fp16 arithmetic as torch evaluates it on the CPU ----------------------
 // torch computes each elementwise half op as half(op(float(a), float(b))).
 // Every helper below widens, applies the IEEE fp32 op with round-to-nearest,

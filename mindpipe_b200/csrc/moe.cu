@@ -93,6 +93,8 @@ __global__ void moe_plan_kernel(int* __restrict__ plan, int E, int max_tiles) {
 __global__ void __launch_bounds__(1024)
 moe_count_plan_kernel(const int* __restrict__ ids, int n_entries, int lo, int hi, int* __restrict__ plan, int E,
                       int max_tiles, float* __restrict__ routed_scale) {
+  chain_wait();
+  chain_release();
   __shared__ int s_counts[kMaxExperts];
   for (int i = threadIdx.x; i < E; i += blockDim.x) s_counts[i] = 0;
   __syncthreads();
@@ -137,6 +139,8 @@ __global__ void __launch_bounds__(256)
 moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict__ ids, int H, int k, int lo, int hi,
                         int* __restrict__ plan, int E, int* __restrict__ dest_row,
                         int8_t* __restrict__ routed_q, float* __restrict__ routed_scale) {
+  chain_wait();
+  chain_release();
   __shared__ float s_red[8];
   __shared__ float s_scale;
   __shared__ int s_dest;
@@ -184,31 +188,66 @@ moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict
   }
 }
 
-// Second activation quant (fake_quant.py:186) with the row abs-max already
-// known from the GEMM1 epilogue: one pass over h.
+// Second activation quant (fake_quant.py:186) with the abs-max of every row within every 128-column tile already
+// known from the GEMM1 epilogue (absmax[row][slots]): the row's maximum is the maximum of its slots, then one pass
+// over h.
 __global__ void __launch_bounds__(256)
-moe_requant_kernel(const __half* __restrict__ h, const unsigned int* __restrict__ absmax_bits, int I,
+moe_requant_kernel(const __half* __restrict__ h, const float* __restrict__ absmax, int slots, int I,
                    const int* __restrict__ num_tiles, int8_t* __restrict__ q, float* __restrict__ scale) {
-  const int row = blockIdx.x;
-  if (row >= *num_tiles * kTileRows) return;
+  chain_wait();
+  chain_release();
+  __shared__ float s_red[8];
+  const int rows = *num_tiles * kTileRows;                       // rows in use; the grid strides over them
   const float eps = h2f(f2h(1e-5f));
-  const float sf = h2f(f2h(__fdiv_rn(fmaxf(__uint_as_float(absmax_bits[row]), eps), 127.0f)));
-  const RowQuant rq = make_row_quant(sf);
-  if (threadIdx.x == 0) scale[row] = sf;
-  const __half* hr = h + (size_t)row * I;
-  int8_t* qr = q + (size_t)row * I;
-  for (int c = threadIdx.x; c < (I >> 3); c += 256) {
-    uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
-    *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float m = 0.0f;
+    for (int i = threadIdx.x; i < slots; i += 256) m = fmaxf(m, absmax[(size_t)row * slots + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();                                              // the previous row's readers are done with s_red
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
+    const float sf = h2f(f2h(__fdiv_rn(fmaxf(m, eps), 127.0f)));
+    const RowQuant rq = make_row_quant(sf);
+    if (threadIdx.x == 0) scale[row] = sf;
+    const __half* hr = h + (size_t)row * I;
+    int8_t* qr = q + (size_t)row * I;
+    for (int c = threadIdx.x; c < (I >> 3); c += 256) {
+      uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
+      *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+    }
   }
+}
+
+static int launch_requant(const __half* h, const float* absmax, int I, const int* num_tiles, int padded_rows,
+                          int8_t* q2, float* scale2, cudaStream_t st) {
+  const int grid = padded_rows < 8 * kSmCount ? padded_rows : 8 * kSmCount;
+  return launch_chained(moe_requant_kernel, dim3(grid), dim3(256), 0, st, h, absmax, moe_absmax_slots(I), I, num_tiles,
+                        q2, scale2);
 }
 
 // out[t] = sum_j f16(d[dest(t,j)] * w[t,j]) with fp16 adds, visiting the token's experts in
 // ascending order as the reference's per-expert index_add_ does (fake_quant.py:188-189).
 // Entries routed elsewhere (dest < 0) contribute nothing.
+// Expert-parallel form (arrivals != null): the rows of d are stored by the peers, each of which then raises its
+// arrival word here (arrivals[r], see the push kernel in moe_ep.cu) to the epoch this rank's own push has just
+// written to *epoch; every block waits for all of them (bounded) before it reads a row.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __half* __restrict__ d, const int* __restrict__ dest_row, const int* __restrict__ ids,
-                   const __half* __restrict__ weights, int T, int H, int k, __half* __restrict__ out) {
+                   const __half* __restrict__ weights, int T, int H, int k, __half* __restrict__ out,
+                   const unsigned int* arrivals, int world, const unsigned int* epoch, int* error_word) {
+  chain_wait();
+  chain_release();
+  if (arrivals != nullptr) {
+    if (static_cast<int>(threadIdx.x) < world) {
+      peer_flag_wait(arrivals + threadIdx.x, *epoch, error_word);
+      __threadfence_system();
+    }
+    __syncthreads();
+  }
   const int t = blockIdx.x;
   int order[8];
   for (int j = 0; j < k; ++j) order[j] = j;
@@ -309,9 +348,10 @@ extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* top
     // few entries (a rank's share under expert parallelism, decode batches): one block counts, plans and zeroes the
     // padding rows' scales -- two launches instead of five graph nodes; with more entries one block's pass over the
     // ids costs what the extra nodes do (16384 entries: equal within 0.2 %), so those keep the multi-block count
-    moe_count_plan_kernel<<<1, 1024, 0, st>>>(static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi,
-                                              plan, E, padded / kTileRows, static_cast<float*>(routed_scale_f32));
-    MP_LAUNCH_CHECK();
+    const int rc = launch_chained(moe_count_plan_kernel, dim3(1), dim3(1024), 0, st,
+                                  static_cast<const int*>(topk_ids_i32), n_entries, expert_lo, expert_hi, plan, E,
+                                  padded / kTileRows, static_cast<float*>(routed_scale_f32));
+    if (rc != MP_OK) return rc;
   } else {
     MP_CUDA_TRY(cudaMemsetAsync(plan, 0, sizeof(int) * E, st));
     // padding rows get scale 0, so whatever codes they hold turn into zeros downstream
@@ -323,63 +363,26 @@ extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* top
     moe_plan_kernel<<<1, 32, 0, st>>>(plan, E, padded / kTileRows);
     MP_LAUNCH_CHECK();
   }
-  moe_gather_quant_kernel<<<n_entries, 256, 0, st>>>(
-      static_cast<const __half*>(hidden_f16), static_cast<const int*>(topk_ids_i32), H, k, expert_lo, expert_hi, plan,
-      E, static_cast<int*>(dest_row_i32), static_cast<int8_t*>(routed_q_i8), static_cast<float*>(routed_scale_f32));
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(moe_gather_quant_kernel, dim3(n_entries), dim3(256), 0, st,
+                        static_cast<const __half*>(hidden_f16), static_cast<const int*>(topk_ids_i32), H, k, expert_lo,
+                        expert_hi, plan, E, static_cast<int*>(dest_row_i32), static_cast<int8_t*>(routed_q_i8),
+                        static_cast<float*>(routed_scale_f32));
 }
 
 // ---- expert stage on rows that are already routed and quantised ------------
-// Workspace (bytes, each part 256-byte aligned): h f16 [P, I] | absmax u32 [P] | q2 i8 [P, I] | scale2 f32 [P]
+// Workspace (bytes, each part 256-byte aligned):
+//   h f16 [P, I] | absmax f32 [P, ceil(I / 128)] | q2 i8 [P, I] | scale2 f32 [P]
 static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 extern "C" size_t mp_moe_expert_stage_workspace_bytes(int padded_rows, int I) {
   if (padded_rows <= 0 || I <= 0) return 0;
   const size_t P = (size_t)padded_rows;
-  return align256(P * I * 2) + align256(P * 4) + align256(P * I) + align256(P * 4);
+  return align256(P * I * 2) + align256(P * moe_absmax_slots(I) * 4) + align256(P * I) + align256(P * 4);
 }
 
-static int expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32, int padded_rows,
-                        int H, int I, int num_local_experts, const void* w13_q_i8, const void* w13_scale_f32,
-                        const void* w2_q_i8, const void* w2_scale_f32, void* d_out_f16, const RowScatter* scatter,
-                        void* workspace, size_t workspace_bytes, int* error_word, mp_stream_t stream) {
-  if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || !w2_q_i8 || !w2_scale_f32 ||
-      (!d_out_f16 && !scatter) || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
-    return MP_ERR_INVALID_ARG;
-  if (padded_rows % kMoeSegmentAlign != 0 || H % 16 != 0 || I % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
-  if (!workspace || workspace_bytes < mp_moe_expert_stage_workspace_bytes(padded_rows, I)) return MP_ERR_WORKSPACE;
-  if (!aligned(workspace, 256) || !aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16) || !aligned(w2_q_i8, 16) ||
-      (d_out_f16 && !aligned(d_out_f16, 16)))
-    return MP_ERR_ALIGNMENT;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int E = num_local_experts;
-  const size_t P = (size_t)padded_rows;
-  unsigned char* ws = static_cast<unsigned char*>(workspace);
-  __half* h = reinterpret_cast<__half*>(ws);
-  unsigned int* absmax = reinterpret_cast<unsigned int*>(ws + align256(P * I * 2));
-  int8_t* q2 = reinterpret_cast<int8_t*>(ws + align256(P * I * 2) + align256(P * 4));
-  float* scale2 = reinterpret_cast<float*>(ws + align256(P * I * 2) + align256(P * 4) + align256(P * I));
-  const int* plan = static_cast<const int*>(plan_i32);
-  const int* num_tiles = plan + 3 * E + 1;
-  const int* tile_expert = plan + 3 * E + 2;
-  int rc = launch_moe_gemm1_swiglu(routed_q_i8, static_cast<const float*>(routed_scale_f32), w13_q_i8,
-                                   static_cast<const float*>(w13_scale_f32), padded_rows, H, I, E, num_tiles,
-                                   tile_expert, h, absmax, error_word, st);
-  if (rc != MP_OK) return rc;
-  moe_requant_kernel<<<padded_rows, 256, 0, st>>>(h, absmax, I, num_tiles, q2, scale2);
-  MP_LAUNCH_CHECK();
-  return launch_moe_gemm2(q2, scale2, w2_q_i8, static_cast<const float*>(w2_scale_f32), padded_rows, I, H, E,
-                          num_tiles, tile_expert, d_out_f16, error_word, st, scatter);
-}
-
-// ---- the expert stage in three launches, each GEMM optionally on one half of the row tiles -----------------
-// Same workspace layout and arithmetic as mp_moe_expert_stage; a caller that overlaps the exchange with the GEMMs
-// runs: gemm1(half 0) | gemm1(half 1) | requant | gemm2(half 0) | gemm2(half 1), with the pull of half 1 next to
-// gemm1(half 0) and the push of half 0 next to gemm2(half 1) on a second stream.
 struct StageBuffers {
   __half* h;
-  unsigned int* absmax;
+  float* absmax;
   int8_t* q2;
   float* scale2;
 };
@@ -391,12 +394,48 @@ static int stage_buffers(void* workspace, size_t workspace_bytes, int padded_row
   const size_t P = (size_t)padded_rows;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   b.h = reinterpret_cast<__half*>(ws);
-  b.absmax = reinterpret_cast<unsigned int*>(ws + align256(P * I * 2));
-  b.q2 = reinterpret_cast<int8_t*>(ws + align256(P * I * 2) + align256(P * 4));
-  b.scale2 = reinterpret_cast<float*>(ws + align256(P * I * 2) + align256(P * 4) + align256(P * I));
+  ws += align256(P * I * 2);
+  b.absmax = reinterpret_cast<float*>(ws);
+  ws += align256(P * moe_absmax_slots(I) * 4);
+  b.q2 = reinterpret_cast<int8_t*>(ws);
+  ws += align256(P * I);
+  b.scale2 = reinterpret_cast<float*>(ws);
   return MP_OK;
 }
 
+static int expert_stage(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32, int padded_rows,
+                        int H, int I, int num_local_experts, const void* w13_q_i8, const void* w13_scale_f32,
+                        const void* w2_q_i8, const void* w2_scale_f32, void* d_out_f16, const RowScatter* scatter,
+                        void* workspace, size_t workspace_bytes, int* error_word, mp_stream_t stream) {
+  if (!routed_q_i8 || !routed_scale_f32 || !plan_i32 || !w13_q_i8 || !w13_scale_f32 || !w2_q_i8 || !w2_scale_f32 ||
+      (!d_out_f16 && !scatter) || padded_rows <= 0 || H <= 0 || I <= 0 || num_local_experts <= 0)
+    return MP_ERR_INVALID_ARG;
+  if (H % 16 != 0 || num_local_experts > kMaxExperts) return MP_ERR_UNSUPPORTED;
+  StageBuffers b;
+  int rc = stage_buffers(workspace, workspace_bytes, padded_rows, I, b);
+  if (rc != MP_OK) return rc;
+  if (!aligned(routed_q_i8, 16) || !aligned(w13_q_i8, 16) || !aligned(w2_q_i8, 16) ||
+      (d_out_f16 && !aligned(d_out_f16, 16)))
+    return MP_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = num_local_experts;
+  const int* plan = static_cast<const int*>(plan_i32);
+  const int* num_tiles = plan + 3 * E + 1;
+  const int* tile_expert = plan + 3 * E + 2;
+  rc = launch_moe_gemm1_swiglu(routed_q_i8, static_cast<const float*>(routed_scale_f32), w13_q_i8,
+                               static_cast<const float*>(w13_scale_f32), padded_rows, H, I, E, num_tiles, tile_expert,
+                               b.h, b.absmax, error_word, st);
+  if (rc != MP_OK) return rc;
+  rc = launch_requant(b.h, b.absmax, I, num_tiles, padded_rows, b.q2, b.scale2, st);
+  if (rc != MP_OK) return rc;
+  return launch_moe_gemm2(b.q2, b.scale2, w2_q_i8, static_cast<const float*>(w2_scale_f32), padded_rows, I, H, E,
+                          num_tiles, tile_expert, d_out_f16, error_word, st, scatter);
+}
+
+// ---- the expert stage in three launches, each GEMM optionally on one half of the row tiles -----------------
+// Same workspace layout and arithmetic as mp_moe_expert_stage; a caller that overlaps the exchange with the GEMMs
+// runs: gemm1(half 0) | gemm1(half 1) | requant | gemm2(half 0) | gemm2(half 1), with the pull of half 1 next to
+// gemm1(half 0) and the push of half 0 next to gemm2(half 1) on a second stream.
 extern "C" int mp_moe_gemm1_swiglu(const void* routed_q_i8, const void* routed_scale_f32, const void* plan_i32,
                                    int padded_rows, int H, int I, int num_local_experts, const void* w13_q_i8,
                                    const void* w13_scale_f32, void* workspace, size_t workspace_bytes, int tile_part,
@@ -423,10 +462,8 @@ extern "C" int mp_moe_requant(const void* plan_i32, int padded_rows, int I, int 
   const int rc = stage_buffers(workspace, workspace_bytes, padded_rows, I, b);
   if (rc != MP_OK) return rc;
   const int* plan = static_cast<const int*>(plan_i32);
-  moe_requant_kernel<<<padded_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(b.h, b.absmax, I,
-                                                                                plan + 3 * num_local_experts + 1, b.q2, b.scale2);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_requant(b.h, b.absmax, I, plan + 3 * num_local_experts + 1, padded_rows, b.q2, b.scale2,
+                        static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mp_moe_gemm2(const void* plan_i32, int padded_rows, int I, int H, int num_local_experts,
@@ -488,9 +525,25 @@ extern "C" int mp_moe_combine(const void* d_f16, const void* dest_row_i32, const
     return MP_ERR_INVALID_ARG;
   if (H % 8 != 0 || k > 8) return MP_ERR_UNSUPPORTED;
   if (!aligned(d_f16, 16) || !aligned(out_f16, 16)) return MP_ERR_ALIGNMENT;
-  moe_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(d_f16), static_cast<const int*>(dest_row_i32), static_cast<const int*>(topk_ids_i32),
-      static_cast<const __half*>(topk_weights_f16), T, H, k, static_cast<__half*>(out_f16));
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(moe_combine_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                        static_cast<const __half*>(d_f16), static_cast<const int*>(dest_row_i32),
+                        static_cast<const int*>(topk_ids_i32), static_cast<const __half*>(topk_weights_f16), T, H, k,
+                        static_cast<__half*>(out_f16), static_cast<const unsigned int*>(nullptr), 0,
+                        static_cast<const unsigned int*>(nullptr), static_cast<int*>(nullptr));
+}
+
+extern "C" int mp_moe_combine_after_peers(const void* arrival_words_u32, int world, const void* epoch_counter_u32,
+                                          const void* d_f16, const void* dest_row_i32, const void* topk_ids_i32,
+                                          const void* topk_weights_f16, int T, int H, int k, void* out_f16,
+                                          int* error_word, mp_stream_t stream) {
+  if (!arrival_words_u32 || !epoch_counter_u32 || world <= 0 || world > kMoeMaxRanks || !d_f16 || !dest_row_i32 ||
+      !topk_ids_i32 || !topk_weights_f16 || !out_f16 || T <= 0 || H <= 0 || k <= 0)
+    return MP_ERR_INVALID_ARG;
+  if (H % 8 != 0 || k > 8) return MP_ERR_UNSUPPORTED;
+  if (!aligned(d_f16, 16) || !aligned(out_f16, 16)) return MP_ERR_ALIGNMENT;
+  return launch_chained(moe_combine_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                        static_cast<const __half*>(d_f16), static_cast<const int*>(dest_row_i32),
+                        static_cast<const int*>(topk_ids_i32), static_cast<const __half*>(topk_weights_f16), T, H, k,
+                        static_cast<__half*>(out_f16), static_cast<const unsigned int*>(arrival_words_u32), world,
+                        static_cast<const unsigned int*>(epoch_counter_u32), error_word);
 }

@@ -42,10 +42,35 @@ __device__ __forceinline__ bool ep_locate(const int* xplan, int world, int e_loc
   return true;
 }
 
-// h[r, n] = f16(silu(f16(gate)) * f16(up)) for the expert-sorted int8 rows, plus per-row max |h|.
+#ifdef __CUDACC__
+// Wait (at most 2 s) until a peer's arrival word has reached `epoch`; the words only grow, and the comparison is
+// wrap-safe.  On giving up the error word is set to 4 ("a peer did not arrive") and the caller carries on.
+__device__ __forceinline__ void peer_flag_wait(const unsigned int* flag, unsigned int epoch, int* error_word) {
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (unsigned int it = 0;; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - epoch) >= 0) break;
+    if ((it & 0xFF) == 0xFF) {
+      uint64_t t1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {
+        if (error_word) atomicExch(error_word, 4);
+        break;
+      }
+    }
+  }
+}
+#endif
+
+// h[r, n] = f16(silu(f16(gate)) * f16(up)) for the expert-sorted int8 rows, plus max |h| of every row within
+// every 128-column tile: row_absmax[r * moe_absmax_slots(I) + tile] (plain stores, so nothing is zeroed first;
+// rows of tiles that are not in use are left untouched).
+__host__ __device__ constexpr int moe_absmax_slots(int I) { return (I + 127) / 128; }
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
-                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st, int tile_part = -1);
+                            void* h_out, float* row_absmax, int* error_word, cudaStream_t st, int tile_part = -1);
 
 // d[r, :] = f16(acc * scale2[r] * w2_scale[e, :]) for the re-quantised rows.
 int launch_moe_gemm2(const void* q2, const float* scale2, const void* w2_q, const float* w2_scale, int padded_rows,

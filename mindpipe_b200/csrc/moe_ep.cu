@@ -45,17 +45,7 @@ __device__ __forceinline__ void peer_barrier_body(const PeerPtrs& peer_flags, in
   __threadfence_system();                                           // everything this GPU wrote so far is visible
   unsigned int* remote = static_cast<unsigned int*>(peer_flags.p[r]) + rank;
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-  const unsigned int* mine = static_cast<const unsigned int*>(peer_flags.p[rank]) + r;
-  const uint64_t t0 = ep_timer_ns();
-  for (unsigned int it = 0;; ++it) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    if (static_cast<int>(v - epoch) >= 0) break;                    // peer r reached this epoch (wrap-safe)
-    if ((it & 0xFF) == 0xFF && ep_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, report, return
-      if (error_word) atomicExch(error_word, 4);
-      break;
-    }
-  }
+  peer_flag_wait(static_cast<const unsigned int*>(peer_flags.p[rank]) + r, epoch, error_word);   // peer r reached this epoch
   __threadfence_system();
 }
 
@@ -68,6 +58,8 @@ __global__ void peer_barrier_kernel(PeerPtrs peer_flags, int world, int rank, un
 // sequence of barriers, so the counters advance in step).
 __global__ void peer_barrier_counted_kernel(PeerPtrs peer_flags, int world, int rank, unsigned int* epoch_counter,
                                             int* error_word) {
+  chain_wait();
+  chain_release();
   __shared__ unsigned int s_epoch;
   if (threadIdx.x == 0) {
     s_epoch = *epoch_counter + 1;
@@ -133,6 +125,8 @@ __global__ void ep_plan_kernel(PeerPtrs peer_plans, int world, int rank, int e_t
 __global__ void ep_barrier_plan_kernel(PeerPtrs peer_flags, PeerPtrs peer_plans, int world, int rank,
                                        unsigned int* epoch_counter, int e_total, int e_loc, int max_tiles, int ext,
                                        int* __restrict__ xplan, int* error_word) {
+  chain_wait();
+  chain_release();
   __shared__ unsigned int s_epoch;
   if (threadIdx.x == 0) {
     s_epoch = *epoch_counter + 1;
@@ -194,6 +188,8 @@ template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xplan, int world, int e_loc, int ext,
                int vec_per_row, uint4* __restrict__ q_sorted, float* __restrict__ s_sorted, int part) {
+  chain_wait();
+  chain_release();
   __shared__ int s_plan[kEpLocateInts];
   const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
   int row_lo, rows;                                                 // padded rows in use, or one half of them
@@ -221,11 +217,22 @@ ep_pull_kernel(PeerPtrs peer_q, PeerPtrs peer_scale, const int* __restrict__ xpl
   }
 }
 
+// Optional tail of the push kernel: once every block's stores are out, raise this rank's arrival word on every
+// peer with the next epoch (the second half of a barrier; the consumer of the rows does the waiting half).
+struct EpSignal {
+  PeerPtrs peer_flags;
+  unsigned int* epoch_counter;   // null: no signal
+  int* block_counter;            // zero between calls
+  int world, rank;
+};
+
 // Result row i -> the source rank's result buffer, at the row's original position; one warp per row.
 template <int VPL>
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const uint4* __restrict__ d_sorted, const int* __restrict__ xplan, int world, int e_loc, int ext,
-               int vec_per_row, PeerPtrs peer_back, int part) {
+               int vec_per_row, PeerPtrs peer_back, int part, EpSignal sig) {
+  chain_wait();
+  chain_release();
   __shared__ int s_plan[kEpLocateInts];
   const EpLocator loc = ep_cache_plan(xplan, world, e_loc, ext, s_plan);
   int row_lo, rows;
@@ -245,6 +252,24 @@ ep_push_kernel(const uint4* __restrict__ d_sorted, const int* __restrict__ xplan
     } else {
       for (int v = lane; v < vec_per_row; v += 32) to[v] = from[v];
     }
+  }
+  if (sig.epoch_counter == nullptr) return;
+  // the block that finishes last tells every peer that this rank's result rows have landed
+  __shared__ bool s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(sig.block_counter, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (threadIdx.x == 0) {
+    *sig.block_counter = 0;                                          // ready for the next call
+    *sig.epoch_counter += 1;
+  }
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < sig.world) {
+    unsigned int* remote = static_cast<unsigned int*>(sig.peer_flags.p[threadIdx.x]) + sig.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(*sig.epoch_counter) : "memory");
   }
 }
 
@@ -277,10 +302,8 @@ extern "C" int mp_peer_barrier_counted(const void* const* peer_flag_ptrs, int wo
   int rc = fill_peers(pf, peer_flag_ptrs, world);
   if (rc != MP_OK) return rc;
   if (rank < 0 || rank >= world || !epoch_counter_u32) return MP_ERR_INVALID_ARG;
-  peer_barrier_counted_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      pf, world, rank, static_cast<unsigned int*>(epoch_counter_u32), error_word);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(peer_barrier_counted_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), pf, world,
+                        rank, static_cast<unsigned int*>(epoch_counter_u32), error_word);
 }
 
 // ---- row-parallel W8A8 linear: K sharded over GPUs ------------------------------------------------------
@@ -444,11 +467,9 @@ extern "C" int mp_moe_ep_barrier_plan(const void* const* peer_flag_ptrs, const v
   const int e_loc = num_experts / world;
   const int max_tiles = capacity_rows / kEpTile;
   const int ext = 3 * e_loc + 2 + max_tiles;
-  ep_barrier_plan_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
-      pf, pp, world, rank, static_cast<unsigned int*>(epoch_counter_u32), num_experts, e_loc, max_tiles, ext,
-      static_cast<int*>(xplan_i32), error_word);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(ep_barrier_plan_kernel, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream), pf, pp, world,
+                        rank, static_cast<unsigned int*>(epoch_counter_u32), num_experts, e_loc, max_tiles, ext,
+                        static_cast<int*>(xplan_i32), error_word);
 }
 
 extern "C" int mp_moe_ep_pull_part(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs,
@@ -470,11 +491,8 @@ extern "C" int mp_moe_ep_pull_part(const void* const* peer_q_ptrs, const void* c
   const int* xp = static_cast<const int*>(xplan_i32);
   uint4* qd = static_cast<uint4*>(q_sorted_i8);
   float* sd = static_cast<float*>(scale_sorted_f32);
-  if (vec == 256) ep_pull_kernel<8><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
-  else if (vec == 128) ep_pull_kernel<4><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
-  else ep_pull_kernel<0><<<grid, 256, 0, st>>>(pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  auto kern = vec == 256 ? ep_pull_kernel<8> : (vec == 128 ? ep_pull_kernel<4> : ep_pull_kernel<0>);
+  return launch_chained(kern, dim3(grid), dim3(256), 0, st, pq, ps, xp, world, num_local_experts, ext, vec, qd, sd, part);
 }
 
 extern "C" int mp_moe_ep_push_part(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
@@ -493,11 +511,37 @@ extern "C" int mp_moe_ep_push_part(const void* d_sorted_f16, const void* xplan_i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint4* dd = static_cast<const uint4*>(d_sorted_f16);
   const int* xp = static_cast<const int*>(xplan_i32);
-  if (vec == 512) ep_push_kernel<16><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
-  else if (vec == 256) ep_push_kernel<8><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
-  else ep_push_kernel<0><<<grid, 256, 0, st>>>(dd, xp, world, num_local_experts, ext, vec, pb, part);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  auto kern = vec == 512 ? ep_push_kernel<16> : (vec == 256 ? ep_push_kernel<8> : ep_push_kernel<0>);
+  return launch_chained(kern, dim3(grid), dim3(256), 0, st, dd, xp, world, num_local_experts, ext, vec, pb, part,
+                        EpSignal{});
+}
+
+extern "C" int mp_moe_ep_push_signal(const void* d_sorted_f16, const void* xplan_i32, int world, int num_local_experts,
+                                     int capacity_rows, int H, const void* const* peer_back_ptrs,
+                                     const void* const* peer_flag_ptrs, int rank, void* epoch_counter_u32,
+                                     void* block_counter_i32, mp_stream_t stream) {
+  PeerPtrs pb;
+  EpSignal sig{};
+  int rc = fill_peers(pb, peer_back_ptrs, world);
+  if (rc != MP_OK) return rc;
+  rc = fill_peers(sig.peer_flags, peer_flag_ptrs, world);
+  if (rc != MP_OK) return rc;
+  if (!d_sorted_f16 || !xplan_i32 || H <= 0 || H % 8 != 0 || rank < 0 || rank >= world || !epoch_counter_u32 ||
+      !block_counter_i32)
+    return MP_ERR_INVALID_ARG;
+  if (num_local_experts > 64) return MP_ERR_UNSUPPORTED;
+  sig.epoch_counter = static_cast<unsigned int*>(epoch_counter_u32);
+  sig.block_counter = static_cast<int*>(block_counter_i32);
+  sig.world = world;
+  sig.rank = rank;
+  const int ext = 3 * num_local_experts + 2 + capacity_rows / kEpTile;
+  const int vec = H / 8;
+  int grid = (capacity_rows + 7) / 8;
+  if (grid > 4 * kSmCount) grid = 4 * kSmCount;
+  auto kern = vec == 512 ? ep_push_kernel<16> : (vec == 256 ? ep_push_kernel<8> : ep_push_kernel<0>);
+  return launch_chained(kern, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                        static_cast<const uint4*>(d_sorted_f16), static_cast<const int*>(xplan_i32), world,
+                        num_local_experts, ext, vec, pb, -1, sig);
 }
 
 extern "C" int mp_moe_ep_pull(const void* const* peer_q_ptrs, const void* const* peer_scale_ptrs, const void* xplan_i32,

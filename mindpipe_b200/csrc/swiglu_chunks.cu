@@ -37,15 +37,25 @@ chunk_stage_kernel(const uint4* __restrict__ x, const float* __restrict__ x_scal
   for (int v = threadIdx.x; v < vec_per_row; v += 256) dst[v] = __ldg(src + v);
 }
 
-// Per-token quantisation of h with the row maximum the GEMM epilogue already found; arithmetic of the
-// second activation quant in the expert path (moe.cu), rows written to out[c, t, :].
+// Per-token quantisation of h with the maxima the GEMM epilogue already found (one per row and 128-column tile);
+// arithmetic of the second activation quant in the expert path (moe.cu), rows written to out[c, t, :].
 __global__ void __launch_bounds__(256)
-chunk_requant_kernel(const __half* __restrict__ h, const unsigned int* __restrict__ absmax_bits, int T, int t_pad,
+chunk_requant_kernel(const __half* __restrict__ h, const float* __restrict__ absmax, int slots, int T, int t_pad,
                      int C, int8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float s_red[8];
   const int c = blockIdx.x / T, t = blockIdx.x % T;
   const size_t src_row = (size_t)c * t_pad + t;
+  float m = 0.0f;
+  for (int i = threadIdx.x; i < slots; i += 256) m = fmaxf(m, absmax[src_row * slots + i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
   const float eps = h2f(f2h(1e-5f));
-  const float sf = h2f(f2h(__fdiv_rn(fmaxf(__uint_as_float(absmax_bits[src_row]), eps), 127.0f)));
+  const float sf = h2f(f2h(__fdiv_rn(fmaxf(m, eps), 127.0f)));
   const RowQuant rq = make_row_quant(sf);
   if (threadIdx.x == 0) scale[blockIdx.x] = sf;
   const __half* hr = h + src_row * C;
@@ -63,12 +73,13 @@ static int padded_tokens(int T) { return (T + kMoeSegmentAlign - 1) / kMoeSegmen
 
 using namespace mp;
 
-// Workspace: plan ints | replicated codes i8 [P, H] | replicated scales f32 [P] | h f16 [P, C] | max|h| u32 [P],
-// P = chunks * (T rounded up to 256), every part 256-byte aligned.
+// Workspace: plan ints | replicated codes i8 [P, H] | replicated scales f32 [P] | h f16 [P, C] |
+// max|h| f32 [P, ceil(C / 128)]; P = chunks * (T rounded up to 256), every part 256-byte aligned.
 extern "C" size_t mp_w8a8_gate_up_swiglu_requant_workspace_bytes(int T, int H, int C, int chunks) {
   if (T <= 0 || H <= 0 || C <= 0 || chunks <= 0) return 0;
   const size_t P = (size_t)chunks * padded_tokens(T);
-  return up256((1 + P / kMoeTileRows) * sizeof(int)) + up256(P * H) + up256(P * 4) + up256(P * C * 2) + up256(P * 4);
+  return up256((1 + P / kMoeTileRows) * sizeof(int)) + up256(P * H) + up256(P * 4) + up256(P * C * 2) +
+         up256(P * moe_absmax_slots(C) * 4);
 }
 
 extern "C" int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_scale_f32, const void* w_i8,
@@ -96,7 +107,7 @@ extern "C" int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_sc
   ws += up256(P * 4);
   __half* h = reinterpret_cast<__half*>(ws);
   ws += up256(P * C * 2);
-  unsigned int* absmax = reinterpret_cast<unsigned int*>(ws);
+  float* absmax = reinterpret_cast<float*>(ws);
   chunk_stage_kernel<<<(unsigned)P, 256, 0, st>>>(static_cast<const uint4*>(x_i8),
                                                   static_cast<const float*>(x_scale_f32), T, t_pad, H / 16, chunks,
                                                   reinterpret_cast<uint4*>(x_rep), scale_rep, plan);
@@ -104,7 +115,7 @@ extern "C" int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_sc
   int rc = launch_moe_gemm1_swiglu(x_rep, scale_rep, w_i8, static_cast<const float*>(w_scale_f32), (int)P, H, C,
                                    chunks, plan, plan + 1, h, absmax, error_word, st);
   if (rc != MP_OK) return rc;
-  chunk_requant_kernel<<<(unsigned)(chunks * T), 256, 0, st>>>(h, absmax, T, t_pad, C,
+  chunk_requant_kernel<<<(unsigned)(chunks * T), 256, 0, st>>>(h, absmax, moe_absmax_slots(C), T, t_pad, C,
                                                                static_cast<int8_t*>(q_out_i8),
                                                                static_cast<float*>(scale_out_f32));
   MP_LAUNCH_CHECK();

@@ -54,7 +54,7 @@ struct GemmParams {
   const float* b_scale;        // per-channel scales, indexed like the weight rows
   const __half* bias;          // [N] or null
   void* out;                   // f16 [M,N] or int32 [M,N]
-  unsigned int* row_absmax;    // SwiGLU: per-row max |h| as float bits (atomicMax target)
+  float* row_absmax;           // SwiGLU: max |h| of every (row, 128-column tile), [rows][n_tiles]
   const float* a_zero;         // AFFINE: per-token zero points (integer valued) and code row sums
   const int* a_rowsum;
   const float* b_zero;         // AFFINE: per-channel zero points and code row sums
@@ -169,6 +169,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // everything above touched only this block's shared and tensor memory: under programmatic dependent launch it
+  // ran beside the previous kernel's tail; from here on that kernel's results are read
+  chain_wait();
+  chain_release();
 
   // tiles are 128 (PAIR: 256) rows of the activations; the grouped plan counts 128-row units
   const int m_units = p.m_tiles_dev ? min(*p.m_tiles_dev, p.m_tiles) : p.m_tiles;
@@ -396,7 +401,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
-        if (row_ok) atomicMax(p.row_absmax + row, __float_as_uint(hmax));
+        if (row_ok) p.row_absmax[(size_t)row * p.n_tiles + n_tile] = hmax;   // one slot per (row, column tile): no atomics, nothing to zero
       } else {
         const int n0 = n_tile * BN;
 #pragma unroll 1
@@ -584,7 +589,7 @@ struct GemmCall {
   const float* a_scale; const float* b_scale; const __half* bias;
   void* out;
   const int* m_tiles_dev; const int* tile_expert; int b_rows_per_expert; int up_row_offset;
-  unsigned int* row_absmax;
+  float* row_absmax;
   int* error_word;
   int tile_part = -1;
 };
@@ -632,21 +637,21 @@ static int launch_gemm(const GemmCall& c, cudaStream_t st) {
     cfg.blockDim = dim3(192, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = decode_programmatic_launch() ? 2 : 1;
     MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     return MP_OK;
   }
   const long long total = (long long)p.m_tiles * p.n_tiles * p.k_split;
   const int grid = (int)(total < kSmCount ? total : kSmCount);
-  kern<<<grid, 192, Cfg::kSmem, st>>>(ta, tb, p);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(kern, dim3(grid), dim3(192), Cfg::kSmem, st, ta, tb, p);
 }
 
 // Few output tiles (decode and small batches: the GEMM is a weight stream, and a CTA sustains only
@@ -690,7 +695,7 @@ static int check_gemm_args(const void* a, const void* b, void* out, int M, int N
 // Grouped GEMMs of the MoE expert chain (declared in moe_api.cuh).
 int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, const void* w13_q, const float* w13_scale,
                             int padded_rows, int H, int I, int E, const int* num_tiles_dev, const int* tile_expert,
-                            void* h_out, unsigned int* row_absmax, int* error_word, cudaStream_t st, int tile_part) {
+                            void* h_out, float* row_absmax, int* error_word, cudaStream_t st, int tile_part) {
   GemmCall c{};
   c.a = routed_q; c.b = w13_q; c.M = padded_rows; c.N = I; c.K = H; c.a_rows = padded_rows;
   c.b_rows_total = E * 2 * I;
@@ -698,8 +703,6 @@ int launch_moe_gemm1_swiglu(const void* routed_q, const float* routed_scale, con
   c.m_tiles_dev = num_tiles_dev; c.tile_expert = tile_expert; c.b_rows_per_expert = 2 * I; c.up_row_offset = I;
   c.row_absmax = row_absmax; c.error_word = error_word;
   c.tile_part = tile_part;
-  // the second half's launch must not clear the maxima the first half has produced
-  if (tile_part <= 0) MP_CUDA_TRY(cudaMemsetAsync(row_absmax, 0, sizeof(unsigned int) * (size_t)padded_rows, st));
   return launch_gemm<256, EPI_SWIGLU, true>(c, st);   // expert segments are 256-row aligned: pair tiles fit
 }
 

@@ -176,10 +176,11 @@ class ExpertParallelMoE(torch.nn.Module):
 class SymmetricExpertParallelMoE(torch.nn.Module):
     """Expert-parallel W8A8 MoE whose dispatch and return run over NVLink peer memory, driven
     entirely from the device: no row count ever visits the host and the barrier epochs live in
-    device memory, so a forward is a fixed sequence of stream-ordered launches (route -> barrier ->
-    plan -> pull -> expert stage -> push -> barrier -> combine; with ``overlap`` the pull, both GEMMs and the push
-    run in two halves on two streams) that can be captured in a CUDA graph and replayed (every rank must replay
-    it the same number of times).
+    device memory, so a forward is a fixed sequence of stream-ordered launches (route -> barrier
+    and plan -> pull -> expert stage -> push, which ends by signalling the peers -> combine, which begins by
+    waiting for theirs; with ``overlap`` the pull, both GEMMs and the push run in two halves on two streams and a
+    barrier launch closes the exchange) that can be captured in a CUDA graph and replayed (every rank must
+    replay it the same number of times).
 
     Each rank keeps its routing plan, routed int8 rows, their scales and a result buffer in one
     symmetric allocation that every peer maps (``torch.distributed._symmetric_memory``).  Peers
@@ -254,6 +255,8 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
         self.q_sorted = torch.empty((self.sorted_cap, self.hidden), dtype=torch.int8, device=dev)
         self.s_sorted = torch.empty(self.sorted_cap, dtype=torch.float32, device=dev)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)     # advanced by the barrier kernel itself
+        self.push_blocks = torch.zeros(1, dtype=torch.int32, device=dev)   # block counter of the signalling push
+        self.arrivals = v[self.off_flags:self.off_flags + 4 * self.world].view(torch.int32)   # peers' words, here
         if self.overlap:
             # buffers that two streams touch are owned by the module, not taken from the caching allocator per call
             self.side = torch.cuda.Stream(device=dev)
@@ -364,8 +367,19 @@ class SymmetricExpertParallelMoE(torch.nn.Module):
         else:
             d_sorted = ops.moe_expert_stage(self.q_sorted, self.s_sorted, self.xplan, self.e_loc, ex.gate_up_proj,
                                             ex.gate_up_proj_scale, ex.down_proj, ex.down_proj_scale)
-            _lib.check(lib.mp_moe_ep_push(d_sorted.data_ptr(), self.xplan.data_ptr(), self.world, self.e_loc,
-                                          self.sorted_cap, h, self.p_back, stream), "moe_ep_push")
+            # the push ends by raising this rank's arrival word on every peer; the combine's blocks wait for the
+            # peers' words: the closing barrier without a launch of its own
+            _lib.check(lib.mp_moe_ep_push_signal(d_sorted.data_ptr(), self.xplan.data_ptr(), self.world, self.e_loc,
+                                                 self.sorted_cap, h, self.p_back, self.p_flags, self.rank,
+                                                 self.epoch.data_ptr(), self.push_blocks.data_ptr(), stream),
+                       "moe_ep_push_signal")
+            out = torch.empty((t, h), dtype=torch.float16, device=hs.device)
+            if t:
+                _lib.check(lib.mp_moe_combine_after_peers(
+                    self.arrivals.data_ptr(), self.world, self.epoch.data_ptr(), self.back.data_ptr(),
+                    routing.dest_row.data_ptr(), ids.data_ptr(), w.data_ptr(), t, h, ids.shape[1], out.data_ptr(),
+                    ops._error_word(hs.device).data_ptr(), stream), "moe_combine_after_peers")
+            return out.reshape(shape)
         self._barrier()                                    # every result row has landed at home
         out = ops.moe_combine(self.back, routing.dest_row, ids, w, t)
         return out.reshape(shape)

@@ -35,7 +35,7 @@ def _graph_replays(fn, out_of, dev, replays=3):
 def verify_multi_gpu(rank: int, world: int, dev: torch.device, oracle=None) -> dict:
     """Returns ``{"ep": bool, "column": bool, "row_w4": bool, "row_w8": bool}`` for this rank; every rank
     of the default process group must call it (the checks contain collectives)."""
-    from . import ops, synth
+    from . import _lib, ops, synth
     from .column_parallel import ColumnParallelW4A16Linear
     from .expert_parallel import ExpertParallelMoE, SymmetricExpertParallelMoE, expert_partition
     from .modules import SmoothQuantPackedMoeExperts, VllmPackedInt4Linear
@@ -74,6 +74,20 @@ def verify_multi_gpu(rank: int, world: int, dev: torch.device, oracle=None) -> d
             out3 = _graph_replays(lambda: sym(xa, ia, wa), lambda o: o, dev)    # barrier epochs live on the device
             ops.check_device_errors()
             ok_ep = ok_ep and torch.equal(out3, ref[a:b])
+        # the same launch sequence with every launch allowed to be scheduled before its predecessor has finished
+        # (each kernel waits on the device): eager and as a replayed graph
+        before = _lib.load().mp_set_programmatic_launch(1)
+        try:
+            chained = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7)
+            for _ in range(3):
+                out5 = chained(xa, ia, wa)
+            ops.check_device_errors()
+            ok_ep = ok_ep and torch.equal(out5, ref[a:b])
+            out6 = _graph_replays(lambda: chained(xa, ia, wa), lambda o: o, dev)
+            ops.check_device_errors()
+            ok_ep = ok_ep and torch.equal(out6, ref[a:b])
+        finally:
+            _lib.load().mp_set_programmatic_launch(before)
         sym2 = SymmetricExpertParallelMoE(local, shape.num_experts, max_tokens_per_rank=b - a + 7, fuse_return=True)
         for _ in range(3):
             out4 = sym2(xa, ia, wa)

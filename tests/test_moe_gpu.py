@@ -112,6 +112,38 @@ def test_moe_expert_ranges_sum_to_full_output():
     assert np.array_equal(acc.astype(np.float16), full)
 
 
+def test_moe_layer_under_programmatic_dependent_launch_same_bits():
+    """Every launch of the layer may be scheduled before its predecessor has finished (each kernel waits for it on
+    the device): same bits as the serialised sequence, eagerly and as a replayed CUDA graph."""
+    from mindpipe_b200 import _lib, ops
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+    shape = synth.MoeShape(num_experts=8, hidden=512, ffn=1024, top_k=2, tokens=700)
+    gu, dn = synth.moe_weights(shape, seed=21, std=0.05)
+    hs = synth.normal_activation(shape.tokens, shape.hidden, seed=21, index=11).cuda()
+    idx, w = ops.moe_router_topk(synth.router_logits(shape.tokens, 8, seed=21).cuda(), 2)
+    mod = SmoothQuantPackedMoeExperts(gu.cuda(), dn.cuda(), torch.nn.SiLU())
+    base = mod(hs, idx, w)
+    lib = _lib.load()
+    before = lib.mp_set_programmatic_launch(1)
+    try:
+        for _ in range(3):
+            assert torch.equal(mod(hs, idx, w), base)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            mod(hs, idx, w)                                   # allocations of the first call on this stream
+            with torch.cuda.graph(graph, stream=side):
+                out = mod(hs, idx, w)
+            for _ in range(3):
+                graph.replay()
+        side.synchronize()
+        assert torch.equal(out, base)
+    finally:
+        lib.mp_set_programmatic_launch(before)
+    ops.check_device_errors()
+
+
 def test_peer_barrier_wait_is_bounded_and_reports():
     """A peer that never shows up: the barrier's wait runs out (2 s), the kernel records an error
     word and returns, and the context stays usable.  The 'peer' is a second flag array on the same
