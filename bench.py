@@ -15,7 +15,9 @@ Reported metric: algorithmic HBM bytes per second of the W4A16 decode linears
 (packed codes + scales + packed zero points + X + Y, per linear, per step).
 ``value`` is measured with inputs resident in HBM and the step replayed from a
 CUDA graph; ``e2e`` goes through ``VllmPackedInt4Linear.forward_host`` (the host-buffer
-C-ABI entry: pinned H2D of X, kernel and D2H of Y inside the timed region).  With N>1
+C-ABI entry: pinned H2D of X, kernel and D2H of Y inside the timed region; the host keeps three independent
+steps in flight, each with its own pinned buffers and stream, and ``e2e.timing.synchronous_ms_per_step`` is the
+same loop with one step in flight).  With N>1
 every rank runs an independent replica (this config does not shard) and the
 values add up ("weak").  ``--impl reference`` times the reference's CPU path
 for the same linears, ``F.linear(x, Wdq)`` on the host cores.
@@ -621,16 +623,40 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
 
     # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
-    # Every linear of the set gets its own stream (forward_host only enqueues and returns), so one linear's
-    # copies overlap another's kernel; the step ends when all results are back in host memory.
+    # Steps are independent requests, so the host keeps E2E_DEPTH of them in flight, as a serving loop does: each
+    # in-flight step has its own pinned input / output buffers and its own stream (forward_host only enqueues
+    # H2D of X, the kernel and D2H of Y and returns), and before a step's buffers are reused the host waits until
+    # the results of the step that used them last are in host memory.  One step's copies then overlap another
+    # step's kernels.  `synchronous_ms_per_step` in `e2e.timing` is the same loop with a device synchronisation
+    # after every step (one step in flight, the set's linears on separate streams).
+    E2E_DEPTH = 3                                       # divides POOL_SETS: a module always meets the same slot
+    x_slots = [x_host] + [{n: t.clone().pin_memory() for n, t in x_host.items()} for _ in range(E2E_DEPTH - 1)]
+    y_slots = [y_host] + [{n: torch.empty_like(t).pin_memory() for n, t in y_host.items()} for _ in range(E2E_DEPTH - 1)]
+    slot_streams = [torch.cuda.Stream(device=dev) for _ in range(E2E_DEPTH)]
+    slot_done = [torch.cuda.Event() for _ in range(E2E_DEPTH)]
     e2e_streams = [torch.cuda.Stream(device=dev) for _ in layer_shapes()]
 
-    def e2e_step(layer):
+    def e2e_issue(i, layer):
+        slot = i % E2E_DEPTH
+        slot_done[slot].synchronize()                  # this slot's previous results have reached host memory
+        for name, mod in layer:
+            mod.forward_host(x_slots[slot][name], y_slots[slot][name], stream=slot_streams[slot])
+        slot_done[slot].record(slot_streams[slot])
+
+    def e2e_run(count):
+        t0 = time.perf_counter()
+        for i in range(count):
+            e2e_issue(i, pool[(args.warmup + i) % POOL_SETS])
+        for ev in slot_done:                           # every result is in host memory before the clock stops
+            ev.synchronize()
+        return time.perf_counter() - t0
+
+    def e2e_step(layer):                               # one step in flight
         for s_, (name, mod) in zip(e2e_streams, layer):
             mod.forward_host(x_host[name], y_host[name], stream=s_)   # H2D of X, kernel, D2H of Y on this stream
         torch.cuda.synchronize()
 
-    def e2e_run(count):
+    def e2e_run_synchronous(count):
         t0 = time.perf_counter()
         for i in range(count):
             e2e_step(pool[(args.warmup + i) % POOL_SETS])
@@ -642,8 +668,7 @@ def run_ours(args, rank, world, local_rank):
         # first forward_host of a module allocates its staging buffers and encodes its tensor maps
         for layer in pool:
             e2e_step(layer)
-        for i in range(args.warmup):
-            e2e_step(pool[i % POOL_SETS])
+        e2e_run(2 * POOL_SETS + args.warmup)
         # `steps` steps take a few milliseconds: repeat the run until at least 0.5 s has been timed per sample,
         # take five samples and report the median per-step time
         probe = e2e_run(args.steps)
@@ -655,8 +680,12 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         samples.sort()
         e2e_s = samples[len(samples) // 2]
+        sync_samples = sorted(e2e_run_synchronous(args.steps * inner) / inner for _ in range(3))
+        barrier()
         e2e_detail = {"samples_ms_per_step": [round(v / args.steps * 1e3, 4) for v in samples],
-                      "steps_per_sample": args.steps * inner, "statistic": "median of 5"}
+                      "steps_per_sample": args.steps * inner, "statistic": "median of 5",
+                      "steps_in_flight": E2E_DEPTH,
+                      "synchronous_ms_per_step": round(sync_samples[1] / args.steps * 1e3, 4)}
         # For information: the same host-buffer calls captured once per layer set in a CUDA graph (H2D copies, kernels
         # and D2H copies as graph nodes, the linears on forked streams) and replayed, one synchronisation per step --
         # what a serving loop that captures its step pays.  Not the headline `e2e`, which issues every call.

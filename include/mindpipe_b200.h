@@ -138,10 +138,23 @@ int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void* const* pee
  * y_host, all enqueued on `stream` without blocking; y_host is valid once the
  * stream has been synchronised.  x_stage [M,K] and y_stage [M,N] are device
  * buffers of the caller (nothing is allocated here).
+ * y_host_f16 may be NULL: the result then stays in y_stage and no copy is
+ * issued.  With y_stage = the device alias of a pinned host buffer
+ * (mp_host_buffer_device_alias) the kernel's own stores carry the result to
+ * host memory: one call less on the host per linear and no copy node between
+ * the kernel and the host's read.
  */
 int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
                                 const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
                                 void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream);
+/*
+ * The address under which the current device can read and write a page-locked
+ * host range (cudaHostAlloc / cudaHostRegister memory, e.g. torch's pinned
+ * tensors).  MP_ERR_UNSUPPORTED for pageable memory, a range that is not mapped
+ * for this device or that spans two registrations.  No reference counterpart
+ * (the reference's forward runs on host tensors directly).
+ */
+int mp_host_buffer_device_alias(const void* host_ptr, size_t bytes, void** device_ptr);
 
 /*
  * Prefill variant (any M; meant for M > 64): the same linear on the fp16 tensor

@@ -35,6 +35,7 @@ SIGNATURES = {
     "mp_w4a16_rowparallel_push": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_w4a16_linear_decode_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "mp_host_buffer_device_alias": (_I, [_P, _Z, _P]),
     "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_w4a16_prefill_workspace_bytes": (_Z, [_I, _I, _I]),
     "mp_w4a16_linear_prefill_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P, _P]),

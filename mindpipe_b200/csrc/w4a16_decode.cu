@@ -740,14 +740,34 @@ extern "C" int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void*
 extern "C" int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
                                            const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
                                            void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream) {
-  if (!x_host_f16 || !x_stage_f16 || !y_stage_f16 || !y_host_f16) return MP_ERR_INVALID_ARG;
+  if (!x_host_f16 || !x_stage_f16 || !y_stage_f16) return MP_ERR_INVALID_ARG;
   if (M > 16) return MP_ERR_UNSUPPORTED;          // the scratch-free kernels only
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MP_CUDA_TRY(cudaMemcpyAsync(x_stage_f16, x_host_f16, (size_t)M * K * sizeof(__half), cudaMemcpyHostToDevice, st));
   const int rc = mp_w4a16_linear_decode_ex(x_stage_f16, packed_i32, sz_f16x2, bias_f16, y_stage_f16, M, N, K, group,
                                            nullptr, 0, 0, stream);
   if (rc != MP_OK) return rc;
-  MP_CUDA_TRY(cudaMemcpyAsync(y_host_f16, y_stage_f16, (size_t)M * N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  // no y_host: the result stays where the kernel stored it (y_stage may be the device alias of a pinned host
+  // buffer, see mp_host_buffer_device_alias: the kernel's stores then are the device-to-host transfer)
+  if (y_host_f16)
+    MP_CUDA_TRY(cudaMemcpyAsync(y_host_f16, y_stage_f16, (size_t)M * N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  return MP_OK;
+}
+
+extern "C" int mp_host_buffer_device_alias(const void* host_ptr, size_t bytes, void** device_ptr) {
+  if (!host_ptr || !device_ptr || bytes == 0) return MP_ERR_INVALID_ARG;
+  *device_ptr = nullptr;
+  cudaPointerAttributes first{}, last{};
+  MP_CUDA_TRY(cudaPointerGetAttributes(&first, host_ptr));
+  MP_CUDA_TRY(cudaPointerGetAttributes(&last, static_cast<const char*>(host_ptr) + bytes - 1));
+  if (first.type != cudaMemoryTypeHost || last.type != cudaMemoryTypeHost || !first.devicePointer ||
+      !last.devicePointer)
+    return MP_ERR_UNSUPPORTED;                      // pageable memory, or not mapped for this device
+  if (static_cast<const char*>(last.devicePointer) - static_cast<const char*>(first.devicePointer) !=
+      static_cast<ptrdiff_t>(bytes - 1))
+    return MP_ERR_UNSUPPORTED;                      // the range spans two registrations
+  if (!aligned(first.devicePointer, 16)) return MP_ERR_ALIGNMENT;
+  *device_ptr = first.devicePointer;
   return MP_OK;
 }
 

@@ -122,19 +122,22 @@ class VllmPackedInt4Linear(nn.Module):
         y = ops.w4a16_linear(x2, self.weight_packed, self._scale_zero, self.bias)
         return y.reshape(*shape[:-1], self.out_features)
 
-    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, stream=None,
+                     zero_copy_output: bool = True) -> torch.Tensor:
         """Decode (<= 16 rows) on a CPU fp16 tensor, as the reference's CPU forward takes it: the H2D
         copy, the kernel and the D2H copy are enqueued on ``stream`` (default: the current stream) and
         the call returns at once; read ``y_host`` after synchronising.  Staging buffers are kept per row
         count and stream (calls on different streams may overlap, so they do not share staging), and a call
         that repeats an earlier one's buffers (same ``x_host`` / ``y_host`` storage, stream and weight-side
         tensors, as a serving loop with fixed pinned buffers does) skips the argument checks and goes
-        straight to the library."""
+        straight to the library; with ``zero_copy_output`` such a repeated call also lets the kernel store the
+        result into the pinned ``y_host`` directly (through its device-side address) instead of staging it and
+        copying -- the same bits, one enqueue less."""
         self._ensure_prepared()
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
         key = (x_host.data_ptr(), None if y_host is None else y_host.data_ptr(), tuple(x_host.shape), st,
                self.weight_packed.data_ptr(), self._scale_zero.data_ptr(),
-               None if self.bias is None else self.bias.data_ptr())
+               None if self.bias is None else self.bias.data_ptr(), zero_copy_output)
         plan = self._host_plans.get(key)
         if plan is not None:
             call, args, y_keep, shapes, _keep = plan
@@ -159,9 +162,18 @@ class VllmPackedInt4Linear(nn.Module):
                                                  y_host=y_host, x_stage=stage[0], y_stage=stage[1])
         if y_host is not None and x_host.is_pinned() and y_host.is_pinned():
             # validated once: remember the raw call (the tensors are kept alive by the plan)
+            import ctypes
             from . import _lib
+            y_out, y_copy = stage[1].data_ptr(), y_host.data_ptr()
+            if zero_copy_output:
+                # pinned memory is mapped into the device's address space: let the kernel store the result there
+                # itself instead of a staging buffer plus a D2H copy (one call less per linear on the host)
+                alias = ctypes.c_void_p()
+                if _lib.load().mp_host_buffer_device_alias(y_host.data_ptr(), y_host.numel() * 2,
+                                                           ctypes.byref(alias)) == 0 and alias.value:
+                    y_out, y_copy = alias.value, None
             args = (x_host.data_ptr(), stage[0].data_ptr(), self.weight_packed.data_ptr(), self._scale_zero.data_ptr(),
-                    None if self.bias is None else self.bias.data_ptr(), stage[1].data_ptr(), y_host.data_ptr(),
+                    None if self.bias is None else self.bias.data_ptr(), y_out, y_copy,
                     m, self.out_features, self.in_features, self.group_size)
             if len(self._host_plans) >= 64:
                 self._host_plans.clear()

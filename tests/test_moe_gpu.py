@@ -144,6 +144,60 @@ def test_moe_layer_under_programmatic_dependent_launch_same_bits():
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("chained", [0, 1])
+def test_expert_parallel_exchange_entries_with_this_gpu_as_its_only_peer(chained):
+    """The device-driven exchange through the C ABI at world size 1 (the rank is its own peer, so one GPU is
+    enough): route -> barrier + plan -> pull -> expert stage -> push that signals -> combine that waits, three
+    forwards in a row (epochs advance, the push's block counter re-arms), against the module's forward."""
+    import ctypes
+    from mindpipe_b200 import _lib, ops
+    from mindpipe_b200.modules import SmoothQuantPackedMoeExperts
+    lib = _lib.load()
+    e, h, inter, t, k = 4, 256, 512, 300, 2
+    shape = synth.MoeShape(num_experts=e, hidden=h, ffn=inter, top_k=k, tokens=t)
+    gu, dn = synth.moe_weights(shape, seed=31, std=0.05)
+    mod = SmoothQuantPackedMoeExperts(gu.cuda(), dn.cuda(), torch.nn.SiLU())
+    idx, w = ops.moe_router_topk(synth.router_logits(t, e, seed=31).cuda(), k)
+    r_cap = lib.mp_moe_padded_rows(e, t * k)
+    plan = torch.zeros(lib.mp_moe_plan_ints(e, t * k), dtype=torch.int32, device="cuda")
+    routed_q = torch.empty((r_cap, h), dtype=torch.int8, device="cuda")
+    routed_scale = torch.empty(r_cap, dtype=torch.float32, device="cuda")
+    back = torch.zeros((r_cap, h), dtype=torch.float16, device="cuda")
+    q_sorted = torch.empty((r_cap, h), dtype=torch.int8, device="cuda")
+    s_sorted = torch.empty(r_cap, dtype=torch.float32, device="cuda")
+    xplan = torch.zeros(lib.mp_moe_ep_plan_ints(1, e, r_cap), dtype=torch.int32, device="cuda")
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    blocks = torch.zeros(1, dtype=torch.int32, device="cuda")
+    err = ops._error_word(torch.device("cuda", torch.cuda.current_device())).data_ptr()
+    one = lambda tensor: (ctypes.c_void_p * 1)(tensor.data_ptr())
+    before = lib.mp_set_programmatic_launch(chained)
+    try:
+        for call in range(3):
+            hs = synth.normal_activation(t, h, seed=31, index=40 + call).cuda()
+            want = mod(hs, idx, w)
+            st = torch.cuda.current_stream().cuda_stream
+            routing = ops.moe_route_gather_quant(hs, idx, 0, e, out=(plan, routed_q, routed_scale))
+            _lib.check(lib.mp_moe_ep_barrier_plan(one(flags), one(plan), 1, 0, epoch.data_ptr(), e, r_cap,
+                                                  xplan.data_ptr(), err, st), "barrier_plan")
+            _lib.check(lib.mp_moe_ep_pull(one(routed_q), one(routed_scale), xplan.data_ptr(), 1, e, r_cap, h,
+                                          q_sorted.data_ptr(), s_sorted.data_ptr(), st), "pull")
+            d_sorted = ops.moe_expert_stage(q_sorted, s_sorted, xplan, e, mod.gate_up_proj, mod.gate_up_proj_scale,
+                                            mod.down_proj, mod.down_proj_scale)
+            _lib.check(lib.mp_moe_ep_push_signal(d_sorted.data_ptr(), xplan.data_ptr(), 1, e, r_cap, h, one(back),
+                                                 one(flags), 0, epoch.data_ptr(), blocks.data_ptr(), st), "push")
+            out = torch.empty((t, h), dtype=torch.float16, device="cuda")
+            _lib.check(lib.mp_moe_combine_after_peers(flags.data_ptr(), 1, epoch.data_ptr(), back.data_ptr(),
+                                                      routing.dest_row.data_ptr(), idx.data_ptr(), w.data_ptr(), t, h, k,
+                                                      out.data_ptr(), err, st), "combine")
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+            assert epoch.item() == 2 * (call + 1) and flags[0].item() == 2 * (call + 1) and blocks.item() == 0
+    finally:
+        lib.mp_set_programmatic_launch(before)
+    ops.check_device_errors()
+
+
 def test_peer_barrier_wait_is_bounded_and_reports():
     """A peer that never shows up: the barrier's wait runs out (2 s), the kernel records an error
     word and returns, and the context stays usable.  The 'peer' is a second flag array on the same

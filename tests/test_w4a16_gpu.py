@@ -189,6 +189,39 @@ def test_host_buffer_entry_matches_device_entry(m):
         mod.forward_host(synth.normal_activation(17, k, seed=3).pin_memory())
 
 
+def test_zero_copy_output_of_the_host_buffer_entry():
+    """Repeated host-buffer calls store the result into the pinned output through its device-side address; the
+    staged form (kernel into a device buffer, then a D2H copy) gives the same bits.  Pageable memory has no such
+    address and keeps the staged form."""
+    import ctypes
+    from mindpipe_b200 import _lib
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    lib = _lib.load()
+    pinned = torch.empty(4096, dtype=torch.float16).pin_memory()
+    alias = ctypes.c_void_p()
+    assert lib.mp_host_buffer_device_alias(pinned.data_ptr(), pinned.numel() * 2, ctypes.byref(alias)) == 0
+    assert alias.value
+    pageable = torch.empty(4096, dtype=torch.float16)
+    assert lib.mp_host_buffer_device_alias(pageable.data_ptr(), pageable.numel() * 2, ctypes.byref(alias)) != 0
+    n, k = 1536, 2048
+    mod = VllmPackedInt4Linear.from_float(torch.nn.Linear(k, n, bias=True).half().cuda())
+    for m in (1, 5, 16):
+        x_host = synth.normal_activation(m, k, seed=8, index=m).pin_memory()
+        want = mod(x_host.cuda()).cpu()
+        for zero_copy in (True, False):
+            y_host = torch.empty((m, n), dtype=torch.float16).pin_memory()
+            for _ in range(3):                      # the second and third call run the remembered form
+                y_host.zero_()
+                mod.forward_host(x_host, y_host, zero_copy_output=zero_copy)
+                torch.cuda.synchronize()
+                assert torch.equal(y_host, want)
+        y_pageable = torch.empty((m, n), dtype=torch.float16)
+        for _ in range(2):
+            mod.forward_host(x_host, y_pageable)
+            torch.cuda.synchronize()
+            assert torch.equal(y_pageable, want)
+
+
 def test_derived_buffers_follow_load_state_dict_and_in_place_updates():
     """The kernel-side (scale, zero) layout and the remembered host calls are rebuilt when the scales change
     under the module: through ``load_state_dict`` (copies in place) and through a plain in-place write."""
