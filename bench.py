@@ -636,9 +636,13 @@ def run_ours(args, rank, world, local_rank):
     slot_done = [torch.cuda.Event() for _ in range(E2E_DEPTH)]
     e2e_streams = [torch.cuda.Stream(device=dev) for _ in layer_shapes()]
 
+    waited = [0.0]                                     # seconds the host spent waiting for a slot's results
+
     def e2e_issue(i, layer):
         slot = i % E2E_DEPTH
+        w0 = time.perf_counter()
         slot_done[slot].synchronize()                  # this slot's previous results have reached host memory
+        waited[0] += time.perf_counter() - w0
         for name, mod in layer:
             mod.forward_host(x_slots[slot][name], y_slots[slot][name], stream=slot_streams[slot])
         slot_done[slot].record(slot_streams[slot])
@@ -675,8 +679,12 @@ def run_ours(args, rank, world, local_rank):
         inner = max(1, int(0.5 / max(probe, 1e-6)) + 1)
         barrier()
         samples = []
+        waited[0] = 0.0
         for _ in range(5):
             samples.append(e2e_run(args.steps * inner) / inner)
+        # share of the timed loop the host spent blocked on results: near 0 = the host's enqueue path is the
+        # limit, near 1 = the device is
+        host_wait_share = waited[0] / max(sum(samples) * inner, 1e-9)
         barrier()
         samples.sort()
         e2e_s = samples[len(samples) // 2]
@@ -684,7 +692,7 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         e2e_detail = {"samples_ms_per_step": [round(v / args.steps * 1e3, 4) for v in samples],
                       "steps_per_sample": args.steps * inner, "statistic": "median of 5",
-                      "steps_in_flight": E2E_DEPTH,
+                      "steps_in_flight": E2E_DEPTH, "host_wait_share": round(host_wait_share, 3),
                       "synchronous_ms_per_step": round(sync_samples[1] / args.steps * 1e3, 4)}
         # For information: the same host-buffer calls captured once per layer set in a CUDA graph (H2D copies, kernels
         # and D2H copies as graph nodes, the linears on forked streams) and replayed, one synchronisation per step --
