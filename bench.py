@@ -15,9 +15,9 @@ Reported metric: algorithmic HBM bytes per second of the W4A16 decode linears
 (packed codes + scales + packed zero points + X + Y, per linear, per step).
 ``value`` is measured with inputs resident in HBM and the step replayed from a
 CUDA graph; ``e2e`` goes through ``VllmPackedInt4Linear.forward_host`` (the host-buffer
-C-ABI entry: pinned H2D of X, kernel and D2H of Y inside the timed region; the host keeps three independent
-steps in flight, each with its own pinned buffers and stream, and ``e2e.timing.synchronous_ms_per_step`` is the
-same loop with one step in flight).  With N>1
+C-ABI entry: pinned H2D of X, kernels and D2H of Y inside the timed region; one ``forward_host_many`` call per
+step, and the host keeps three independent steps in flight, each with its own pinned buffers and stream;
+``e2e.timing.synchronous_ms_per_step`` is one ``forward_host`` call per linear with one step in flight).  With N>1
 every rank runs an independent replica (this config does not shard) and the
 values add up ("weak").  ``--impl reference`` times the reference's CPU path
 for the same linears, ``F.linear(x, Wdq)`` on the host cores.
@@ -624,11 +624,12 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end: module API, host buffers, H2D + D2H inside the timed region ----
     # Steps are independent requests, so the host keeps E2E_DEPTH of them in flight, as a serving loop does: each
-    # in-flight step has its own pinned input / output buffers and its own stream (forward_host only enqueues
-    # H2D of X, the kernel and D2H of Y and returns), and before a step's buffers are reused the host waits until
-    # the results of the step that used them last are in host memory.  One step's copies then overlap another
-    # step's kernels.  `synchronous_ms_per_step` in `e2e.timing` is the same loop with a device synchronisation
-    # after every step (one step in flight, the set's linears on separate streams).
+    # in-flight step has its own pinned input / output buffers and its own stream (forward_host_many only
+    # enqueues the H2D copies of X, the kernels and the D2H copies of Y and returns), and before a step's buffers
+    # are reused the host waits until the results of the step that used them last are in host memory.  One step's
+    # copies then overlap another step's kernels.  `synchronous_ms_per_step` in `e2e.timing` is one forward_host
+    # call per linear with a device synchronisation after every step (one step in flight, the set's linears on
+    # separate streams).
     E2E_DEPTH = 3                                       # divides POOL_SETS: a module always meets the same slot
     x_slots = [x_host] + [{n: t.clone().pin_memory() for n, t in x_host.items()} for _ in range(E2E_DEPTH - 1)]
     y_slots = [y_host] + [{n: torch.empty_like(t).pin_memory() for n, t in y_host.items()} for _ in range(E2E_DEPTH - 1)]
@@ -638,13 +639,27 @@ def run_ours(args, rank, world, local_rank):
 
     waited = [0.0]                                     # seconds the host spent waiting for a slot's results
 
+    from mindpipe_b200.modules import forward_host_many
+    many_args = {}                                     # (layer set, slot) -> argument lists of forward_host_many
+
     def e2e_issue(i, layer):
         slot = i % E2E_DEPTH
         w0 = time.perf_counter()
         slot_done[slot].synchronize()                  # this slot's previous results have reached host memory
         waited[0] += time.perf_counter() - w0
-        for name, mod in layer:
-            mod.forward_host(x_slots[slot][name], y_slots[slot][name], stream=slot_streams[slot])
+        if args.e2e_call == "many":
+            # the set's linears are independent: one library call enqueues their copies in, the kernels back to
+            # back (programmatic dependent launch between them) and the copies out
+            lists = many_args.get((id(layer), slot))
+            if lists is None:
+                lists = many_args[(id(layer), slot)] = ([mod for _, mod in layer],
+                                                        [x_slots[slot][name] for name, _ in layer],
+                                                        [y_slots[slot][name] for name, _ in layer])
+            forward_host_many(*lists, stream=slot_streams[slot])
+        else:
+            for name, mod in layer:
+                mod.forward_host(x_slots[slot][name], y_slots[slot][name], stream=slot_streams[slot],
+                                 zero_copy_output=args.e2e_call == "single_zero_copy")
         slot_done[slot].record(slot_streams[slot])
 
     def e2e_run(count):
@@ -693,6 +708,8 @@ def run_ours(args, rank, world, local_rank):
         e2e_detail = {"samples_ms_per_step": [round(v / args.steps * 1e3, 4) for v in samples],
                       "steps_per_sample": args.steps * inner, "statistic": "median of 5",
                       "steps_in_flight": E2E_DEPTH, "host_wait_share": round(host_wait_share, 3),
+                      "call": {"many": "forward_host_many (one call per step)", "single": "forward_host per linear",
+                               "single_zero_copy": "forward_host per linear, zero-copy output"}[args.e2e_call],
                       "synchronous_ms_per_step": round(sync_samples[1] / args.steps * 1e3, 4)}
         # For information: the same host-buffer calls captured once per layer set in a CUDA graph (H2D copies, kernels
         # and D2H copies as graph nodes, the linears on forked streams) and replayed, one synchronisation per step --
@@ -1049,6 +1066,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--e2e-call", default="many", choices=["many", "single", "single_zero_copy"],
+                    help="end-to-end leg: one forward_host_many call per step (default), one forward_host call per "
+                         "linear, or the latter with the kernels storing straight into the pinned output")
     ap.add_argument("--pool-sets", type=int, default=POOL_SETS, help="layer sets in the weight pool")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch for the decode linears")
     ap.add_argument("--fuse", type=int, default=1,

@@ -147,6 +147,33 @@ int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void* const* pee
 int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
                                 const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
                                 void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream);
+/* The same with a workspace of mp_w4a16_decode_workspace_bytes(M, N, K) bytes (zero-filled once, owned by the caller,
+ * not shared between calls that may overlap): the kernel is then chosen as mp_w4a16_linear_decode chooses it. */
+int mp_w4a16_linear_decode_host_ws(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
+                                   const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
+                                   void* y_host_f16, int M, int N, int K, int group, void* workspace,
+                                   size_t workspace_bytes, mp_stream_t stream);
+/*
+ * Several independent host-buffer linears on one stream in one call (the q/k/v or gate/up projections of a
+ * decoder layer, which read the same activations and do not depend on one another): all H2D copies are enqueued
+ * first, then the kernels back to back -- so that, with mp_set_programmatic_launch(1), each one fetches its weights
+ * while its predecessor drains -- then the D2H copies.  Every field means what the argument of the same name
+ * means in mp_w4a16_linear_decode_host_ws; the entries must not share staging buffers or workspaces.  The call
+ * stops at the first entry that fails and returns its status.
+ */
+typedef struct mp_host_linear {
+  const void* x_host_f16;
+  void* x_stage_f16;
+  const void* packed_i32;
+  const void* sz_f16x2;
+  const void* bias_f16;
+  void* y_stage_f16;
+  void* y_host_f16;
+  int M, N, K, group;
+  void* workspace;
+  size_t workspace_bytes;
+} mp_host_linear;
+int mp_w4a16_linear_decode_host_many(const mp_host_linear* linears, int count, mp_stream_t stream);
 /*
  * The address under which the current device can read and write a page-locked
  * host range (cudaHostAlloc / cudaHostRegister memory, e.g. torch's pinned

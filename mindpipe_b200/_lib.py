@@ -36,6 +36,8 @@ SIGNATURES = {
     "mp_w4a16_rowparallel_finish": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "mp_w4a16_linear_decode_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "mp_host_buffer_device_alias": (_I, [_P, _Z, _P]),
+    "mp_w4a16_linear_decode_host_ws": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
+    "mp_w4a16_linear_decode_host_many": (_I, [_P, _I, _P]),
     "mp_w4a16_linear_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "mp_w4a16_prefill_workspace_bytes": (_Z, [_I, _I, _I]),
     "mp_w4a16_linear_prefill_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P, _P]),
@@ -87,6 +89,14 @@ SIGNATURES = {
     "mp_moe_ep_push_signal": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P]),
     "mp_moe_combine_after_peers": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
 }
+
+
+class HostLinear(ctypes.Structure):
+    """``mp_host_linear`` of the C header: one entry of ``mp_w4a16_linear_decode_host_many``."""
+    _fields_ = [("x_host_f16", c_void_p), ("x_stage_f16", c_void_p), ("packed_i32", c_void_p), ("sz_f16x2", c_void_p),
+                ("bias_f16", c_void_p), ("y_stage_f16", c_void_p), ("y_host_f16", c_void_p),
+                ("M", c_int), ("N", c_int), ("K", c_int), ("group", c_int),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
 
 
 class MindPipeKernelError(RuntimeError):

@@ -737,20 +737,55 @@ extern "C" int mp_w4a16_rowparallel_finish(void* const* peer_partial0_f32, void*
   return MP_OK;
 }
 
-extern "C" int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
-                                           const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
-                                           void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream) {
+extern "C" int mp_w4a16_linear_decode_host_ws(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
+                                              const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
+                                              void* y_host_f16, int M, int N, int K, int group, void* workspace,
+                                              size_t workspace_bytes, mp_stream_t stream) {
   if (!x_host_f16 || !x_stage_f16 || !y_stage_f16) return MP_ERR_INVALID_ARG;
-  if (M > 16) return MP_ERR_UNSUPPORTED;          // the scratch-free kernels only
+  if (M > 16) return MP_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MP_CUDA_TRY(cudaMemcpyAsync(x_stage_f16, x_host_f16, (size_t)M * K * sizeof(__half), cudaMemcpyHostToDevice, st));
+  // without a workspace: the scratch-free kernels only
   const int rc = mp_w4a16_linear_decode_ex(x_stage_f16, packed_i32, sz_f16x2, bias_f16, y_stage_f16, M, N, K, group,
-                                           nullptr, 0, 0, stream);
+                                           workspace, workspace ? workspace_bytes : 0, 0, stream);
   if (rc != MP_OK) return rc;
   // no y_host: the result stays where the kernel stored it (y_stage may be the device alias of a pinned host
   // buffer, see mp_host_buffer_device_alias: the kernel's stores then are the device-to-host transfer)
   if (y_host_f16)
     MP_CUDA_TRY(cudaMemcpyAsync(y_host_f16, y_stage_f16, (size_t)M * N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  return MP_OK;
+}
+
+extern "C" int mp_w4a16_linear_decode_host(const void* x_host_f16, void* x_stage_f16, const void* packed_i32,
+                                           const void* sz_f16x2, const void* bias_f16, void* y_stage_f16,
+                                           void* y_host_f16, int M, int N, int K, int group, mp_stream_t stream) {
+  return mp_w4a16_linear_decode_host_ws(x_host_f16, x_stage_f16, packed_i32, sz_f16x2, bias_f16, y_stage_f16, y_host_f16,
+                                        M, N, K, group, nullptr, 0, stream);
+}
+
+extern "C" int mp_w4a16_linear_decode_host_many(const mp_host_linear* linears, int count, mp_stream_t stream) {
+  if (!linears || count <= 0) return MP_ERR_INVALID_ARG;
+  for (int i = 0; i < count; ++i) {
+    const mp_host_linear& c = linears[i];
+    if (!c.x_host_f16 || !c.x_stage_f16 || !c.y_stage_f16 || c.M <= 0 || c.K <= 0 || c.N <= 0) return MP_ERR_INVALID_ARG;
+    if (c.M > 16) return MP_ERR_UNSUPPORTED;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < count; ++i) {
+    const mp_host_linear& c = linears[i];
+    MP_CUDA_TRY(cudaMemcpyAsync(c.x_stage_f16, c.x_host_f16, (size_t)c.M * c.K * sizeof(__half), cudaMemcpyHostToDevice, st));
+  }
+  for (int i = 0; i < count; ++i) {
+    const mp_host_linear& c = linears[i];
+    const int rc = mp_w4a16_linear_decode_ex(c.x_stage_f16, c.packed_i32, c.sz_f16x2, c.bias_f16, c.y_stage_f16, c.M, c.N,
+                                             c.K, c.group, c.workspace, c.workspace ? c.workspace_bytes : 0, 0, stream);
+    if (rc != MP_OK) return rc;
+  }
+  for (int i = 0; i < count; ++i) {
+    const mp_host_linear& c = linears[i];
+    if (c.y_host_f16)
+      MP_CUDA_TRY(cudaMemcpyAsync(c.y_host_f16, c.y_stage_f16, (size_t)c.M * c.N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  }
   return MP_OK;
 }
 

@@ -123,7 +123,7 @@ class VllmPackedInt4Linear(nn.Module):
         return y.reshape(*shape[:-1], self.out_features)
 
     def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, stream=None,
-                     zero_copy_output: bool = True) -> torch.Tensor:
+                     zero_copy_output: bool = False) -> torch.Tensor:
         """Decode (<= 16 rows) on a CPU fp16 tensor, as the reference's CPU forward takes it: the H2D
         copy, the kernel and the D2H copy are enqueued on ``stream`` (default: the current stream) and
         the call returns at once; read ``y_host`` after synchronising.  Staging buffers are kept per row
@@ -132,7 +132,8 @@ class VllmPackedInt4Linear(nn.Module):
         tensors, as a serving loop with fixed pinned buffers does) skips the argument checks and goes
         straight to the library; with ``zero_copy_output`` such a repeated call also lets the kernel store the
         result into the pinned ``y_host`` directly (through its device-side address) instead of staging it and
-        copying -- the same bits, one enqueue less."""
+        copying -- the same bits and one enqueue less, but the kernel's stores then cross PCIe: measured 3 % more
+        throughput with several steps in flight and 17 % more latency for a lone call, hence off by default."""
         self._ensure_prepared()
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
         key = (x_host.data_ptr(), None if y_host is None else y_host.data_ptr(), tuple(x_host.shape), st,
@@ -150,16 +151,21 @@ class VllmPackedInt4Linear(nn.Module):
         stage = self._host_stage.get((m, st))
         if stage is None:
             dev = self.weight_packed.device
+            # scratch of this (row count, stream) pair, when the library's choice for the shape needs one: calls on
+            # one stream run in order, so they may share it
+            ws = None
+            if 0 < m <= 16 and ops.w4a16_decode_kernel_choice(m, self.out_features, self.in_features) == "umma":
+                ws = ops.new_workspace(ops.w4a16_decode_workspace_bytes(m, self.out_features, self.in_features), dev)
             stage = (torch.empty((m, self.in_features), dtype=torch.float16, device=dev),
-                     torch.empty((m, self.out_features), dtype=torch.float16, device=dev))
+                     torch.empty((m, self.out_features), dtype=torch.float16, device=dev), ws)
             self._host_stage[(m, st)] = stage
         if stream is None:
             y = ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias, y_host=y_host,
-                                             x_stage=stage[0], y_stage=stage[1])
+                                             x_stage=stage[0], y_stage=stage[1], workspace=stage[2])
         else:
             with torch.cuda.stream(stream):
                 y = ops.w4a16_linear_decode_host(x_host, self.weight_packed, self._scale_zero, self.bias,
-                                                 y_host=y_host, x_stage=stage[0], y_stage=stage[1])
+                                                 y_host=y_host, x_stage=stage[0], y_stage=stage[1], workspace=stage[2])
         if y_host is not None and x_host.is_pinned() and y_host.is_pinned():
             # validated once: remember the raw call (the tensors are kept alive by the plan)
             import ctypes
@@ -174,10 +180,11 @@ class VllmPackedInt4Linear(nn.Module):
                     y_out, y_copy = alias.value, None
             args = (x_host.data_ptr(), stage[0].data_ptr(), self.weight_packed.data_ptr(), self._scale_zero.data_ptr(),
                     None if self.bias is None else self.bias.data_ptr(), y_out, y_copy,
-                    m, self.out_features, self.in_features, self.group_size)
+                    m, self.out_features, self.in_features, self.group_size,
+                    None if stage[2] is None else stage[2].data_ptr(), 0 if stage[2] is None else stage[2].numel())
             if len(self._host_plans) >= 64:
                 self._host_plans.clear()
-            self._host_plans[key] = (_lib.load().mp_w4a16_linear_decode_host, args, y_host,
+            self._host_plans[key] = (_lib.load().mp_w4a16_linear_decode_host_ws, args, y_host,
                                      dict(M=m, N=self.out_features, K=self.in_features, group=self.group_size),
                                      (x_host, stage, self._scale_zero))
         return y
@@ -185,6 +192,58 @@ class VllmPackedInt4Linear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"w_bit=4, group_size={self.group_size}, asymmetric={self.weight_zero_point is not None}")
+
+
+_HOST_MANY_PLANS: dict = {}
+
+
+def forward_host_many(linears, x_hosts, y_hosts, stream=None):
+    """``forward_host`` of several independent ``VllmPackedInt4Linear`` modules on ONE stream in one library
+    call: all H2D copies first, then the kernels back to back (so that under ``mp_set_programmatic_launch(1)`` each
+    fetches its weights while the one before drains), then the D2H copies.  For linears that do not depend on one
+    another -- the q/k/v or gate/up projections of a decoder layer.  ``x_hosts`` / ``y_hosts`` are pinned CPU fp16
+    tensors, one pair per module (<= 16 rows); returns ``y_hosts``, valid once the stream is synchronised.  The
+    first call with a given set of modules, buffers and stream goes through each module's own ``forward_host``
+    (argument checks, staging and scratch buffers); repeats reuse the recorded call."""
+    from . import _lib
+    st = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
+    key = (st,) + tuple((id(m), x.data_ptr(), y.data_ptr(), x.shape[0]) for m, x, y in zip(linears, x_hosts, y_hosts))
+    plan = _HOST_MANY_PLANS.get(key)
+    if plan is not None:
+        for m in linears:
+            m._ensure_prepared()
+        calls, derived, _keep = plan
+        if all(m._scale_zero is z and m.weight_packed.data_ptr() == p and (None if m.bias is None else m.bias.data_ptr()) == b
+               for m, (z, p, b) in zip(linears, derived)):
+            status = _lib.load().mp_w4a16_linear_decode_host_many(calls, len(derived), st)
+            if status != 0:
+                _lib.check(status, "w4a16_linear_decode_host_many", count=len(derived))
+            return y_hosts
+    if not (len(linears) == len(x_hosts) == len(y_hosts)) or not linears:
+        raise ValueError("forward_host_many takes one (x_host, y_host) pair per module")
+    if len({id(m) for m in linears}) != len(linears):
+        raise ValueError("a module may appear once per call (its staging buffers are per stream)")
+    for m, x, y in zip(linears, x_hosts, y_hosts):
+        if not isinstance(m, VllmPackedInt4Linear):
+            raise TypeError("forward_host_many expects VllmPackedInt4Linear modules")
+        if y is None or not x.is_pinned() or not y.is_pinned():
+            raise ValueError("forward_host_many needs pinned x_host and y_host tensors")
+        m.forward_host(x, y, stream=stream, zero_copy_output=False)      # validates; creates staging and scratch
+    calls = (_lib.HostLinear * len(linears))()
+    for c, m, x, y in zip(calls, linears, x_hosts, y_hosts):
+        xs, ys, ws = m._host_stage[(x.shape[0], st)]
+        c.x_host_f16, c.x_stage_f16 = x.data_ptr(), xs.data_ptr()
+        c.packed_i32, c.sz_f16x2 = m.weight_packed.data_ptr(), m._scale_zero.data_ptr()
+        c.bias_f16 = None if m.bias is None else m.bias.data_ptr()
+        c.y_stage_f16, c.y_host_f16 = ys.data_ptr(), y.data_ptr()
+        c.M, c.N, c.K, c.group = x.shape[0], m.out_features, m.in_features, m.group_size
+        c.workspace = None if ws is None else ws.data_ptr()
+        c.workspace_bytes = 0 if ws is None else ws.numel()
+    if len(_HOST_MANY_PLANS) >= 256:
+        _HOST_MANY_PLANS.clear()
+    _HOST_MANY_PLANS[key] = (calls, [(m._scale_zero, m.weight_packed.data_ptr(), None if m.bias is None else m.bias.data_ptr())
+                                     for m in linears], (list(linears), list(x_hosts), list(y_hosts)))
+    return y_hosts
 
 
 class SmoothQuantLinear(nn.Module):

@@ -188,11 +188,14 @@ def w4a16_linear_decode(x, weight_packed, scale_zero, bias=None, *, k_split: int
     return y
 
 
-def w4a16_linear_decode_host(x_host, weight_packed, scale_zero, bias=None, *, y_host=None, x_stage=None, y_stage=None):
+def w4a16_linear_decode_host(x_host, weight_packed, scale_zero, bias=None, *, y_host=None, x_stage=None, y_stage=None,
+                             workspace=None):
     """Decode linear (M <= 16) on HOST activations: H2D copy, kernel and D2H copy are enqueued on the
     current stream and the call returns without waiting; ``y_host`` is valid after the stream (or
     device) has been synchronised.  ``x_host`` / ``y_host`` are CPU fp16 tensors (pinned memory makes
-    the copies asynchronous); ``x_stage`` / ``y_stage`` are optional device staging buffers to reuse.
+    the copies asynchronous); ``x_stage`` / ``y_stage`` are optional device staging buffers to reuse;
+    ``workspace`` (``new_workspace(w4a16_decode_workspace_bytes(m, n, k))``, not shared with calls that may
+    overlap this one) lets the library pick among all decode kernels instead of the scratch-free ones.
     """
     if x_host.device.type != "cpu" or x_host.dtype != torch.float16 or x_host.dim() != 2 or not x_host.is_contiguous():
         raise ValueError("x_host must be a contiguous 2-D fp16 CPU tensor")
@@ -213,8 +216,12 @@ def w4a16_linear_decode_host(x_host, weight_packed, scale_zero, bias=None, *, y_
     ys = torch.empty((m, n), dtype=torch.float16, device=p.device) if y_stage is None else _req(y_stage, "y_stage", torch.float16, 2)
     if tuple(xs.shape) != (m, k) or tuple(ys.shape) != (m, n):
         raise ValueError("staging buffers must be [M, K] and [M, N]")
-    st = _lib.load().mp_w4a16_linear_decode_host(x_host.data_ptr(), xs.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b),
-                                                 ys.data_ptr(), y_host.data_ptr(), m, n, k, k // groups, _stream())
+    if workspace is not None and (not workspace.is_cuda or workspace.dtype != torch.uint8 or
+                                  workspace.numel() < w4a16_decode_workspace_bytes(m, n, k)):
+        raise ValueError("workspace must be a CUDA uint8 tensor of at least w4a16_decode_workspace_bytes(m, n, k) bytes")
+    st = _lib.load().mp_w4a16_linear_decode_host_ws(
+        x_host.data_ptr(), xs.data_ptr(), p.data_ptr(), sz.data_ptr(), _ptr(b), ys.data_ptr(), y_host.data_ptr(), m, n, k,
+        k // groups, _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream())
     _lib.check(st, "w4a16_linear_decode_host", M=m, N=n, K=k, group=k // groups)
     return y_host
 

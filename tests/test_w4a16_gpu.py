@@ -222,6 +222,74 @@ def test_zero_copy_output_of_the_host_buffer_entry():
             assert torch.equal(y_pageable, want)
 
 
+def test_host_buffer_entry_on_a_shape_that_takes_the_workspace_kernel():
+    """A gate/up-sized linear at 16 rows: the host-buffer call owns a workspace per stream, so the library picks the
+    same kernel as for device-resident activations -- same bits, staged or stored straight into pinned memory, on
+    two streams in turn."""
+    from mindpipe_b200 import ops
+    from mindpipe_b200.modules import VllmPackedInt4Linear
+    n, k, m = 22016, 4096, 16
+    assert ops.w4a16_decode_kernel_choice(m, n, k) == "umma"
+    w = synth.normal_weight(n, k, seed=6, index=1).cuda()
+    packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+    mod = VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k, out_features=n,
+                               zero_point=zero)
+    x_host = synth.normal_activation(m, k, seed=6, index=2).pin_memory()
+    want = mod(x_host.cuda()).cpu()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for zero_copy in (True, False):
+        y_hosts = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _ in streams]
+        for _ in range(3):
+            for s_, y_host in zip(streams, y_hosts):
+                y_host.zero_()
+                mod.forward_host(x_host, y_host, stream=s_, zero_copy_output=zero_copy)
+            torch.cuda.synchronize()
+            for y_host in y_hosts:
+                assert torch.equal(y_host, want)
+    ops.check_device_errors()
+
+
+def test_forward_host_many_matches_the_single_calls():
+    """Several independent linears in one library call (copies in, kernels back to back, copies out): the bits of
+    the one-by-one calls, with and without programmatic dependent launch, and again after one module's scales
+    changed under the recorded call."""
+    from mindpipe_b200 import _lib, ops
+    from mindpipe_b200.modules import VllmPackedInt4Linear, forward_host_many
+    shapes = [(768, 1024), (22016, 4096), (512, 2048), (4096, 4096)]
+    mods, xs, ys, want = [], [], [], []
+    for i, (n, k) in enumerate(shapes):
+        w = synth.normal_weight(n, k, seed=14, index=i).cuda()
+        packed, scale, zero, _ = ops.w4a16_quantize(w, 128)
+        mods.append(VllmPackedInt4Linear(packed_weight=packed, scale=scale, bias=None, in_features=k, out_features=n,
+                                         zero_point=zero))
+        xs.append(synth.normal_activation(16, k, seed=14, index=10 + i).pin_memory())
+        ys.append(torch.empty((16, n), dtype=torch.float16).pin_memory())
+        want.append(mods[-1](xs[-1].cuda()).cpu())
+    side = torch.cuda.Stream()
+    lib = _lib.load()
+    for chained in (0, 1):
+        before = lib.mp_set_programmatic_launch(chained)
+        try:
+            for _ in range(3):
+                for y in ys:
+                    y.zero_()
+                out = forward_host_many(mods, xs, ys, stream=side)
+                side.synchronize()
+                assert out is ys
+                for y, w_ in zip(ys, want):
+                    assert torch.equal(y, w_)
+        finally:
+            lib.mp_set_programmatic_launch(before)
+    mods[0].weight_scale.mul_(2)                      # the recorded call's derived buffer is stale now
+    want0 = mods[0](xs[0].cuda()).cpu()
+    forward_host_many(mods, xs, ys, stream=side)
+    side.synchronize()
+    assert torch.equal(ys[0], want0) and torch.equal(ys[1], want[1])
+    with pytest.raises(ValueError):
+        forward_host_many([mods[0], mods[0]], xs[:2], ys[:2])
+    ops.check_device_errors()
+
+
 def test_derived_buffers_follow_load_state_dict_and_in_place_updates():
     """The kernel-side (scale, zero) layout and the remembered host calls are rebuilt when the scales change
     under the module: through ``load_state_dict`` (copies in place) and through a plain in-place write."""
