@@ -196,29 +196,39 @@ moe_requant_kernel(const __half* __restrict__ h, const float* __restrict__ absma
                    const int* __restrict__ num_tiles, int8_t* __restrict__ q, float* __restrict__ scale) {
   chain_wait();
   chain_release();
-  __shared__ float s_red[8];
+  constexpr int kBatch = 32;                                     // rows whose scales are found before they stream
+  __shared__ float s_scale[kBatch];
   const int rows = *num_tiles * kTileRows;                       // rows in use; the grid strides over them
   const float eps = h2f(f2h(1e-5f));
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    float m = 0.0f;
-    for (int i = threadIdx.x; i < slots; i += 256) m = fmaxf(m, absmax[(size_t)row * slots + i]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row0 = blockIdx.x; row0 < rows; row0 += gridDim.x * kBatch) {
+    // a warp per row: the maximum of the row's slots, then the scale
+    for (int i = warp; i < kBatch; i += 8) {
+      const int row = row0 + i * gridDim.x;
+      if (row >= rows) break;
+      float m = 0.0f;
+      for (int j = lane; j < slots; j += 32) m = fmaxf(m, absmax[(size_t)row * slots + j]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    __syncthreads();                                              // the previous row's readers are done with s_red
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
-    __syncthreads();
-    m = s_red[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
-    const float sf = h2f(f2h(__fdiv_rn(fmaxf(m, eps), 127.0f)));
-    const RowQuant rq = make_row_quant(sf);
-    if (threadIdx.x == 0) scale[row] = sf;
-    const __half* hr = h + (size_t)row * I;
-    int8_t* qr = q + (size_t)row * I;
-    for (int c = threadIdx.x; c < (I >> 3); c += 256) {
-      uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
-      *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (lane == 0) {
+        const float sf = h2f(f2h(__fdiv_rn(fmaxf(m, eps), 127.0f)));
+        s_scale[i] = sf;
+        scale[row] = sf;
+      }
     }
+    __syncthreads();
+    for (int i = 0; i < kBatch; ++i) {
+      const int row = row0 + i * gridDim.x;
+      if (row >= rows) break;
+      const RowQuant rq = make_row_quant(s_scale[i]);
+      const __half* hr = h + (size_t)row * I;
+      int8_t* qr = q + (size_t)row * I;
+      for (int c = threadIdx.x; c < (I >> 3); c += 256) {
+        uint4 raw = *reinterpret_cast<const uint4*>(hr + c * 8);
+        *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+      }
+    }
+    __syncthreads();                                              // s_scale is rewritten by the next batch
   }
 }
 
