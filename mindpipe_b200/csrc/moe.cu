@@ -135,6 +135,9 @@ moe_count_plan_kernel(const int* __restrict__ ids, int n_entries, int lo, int hi
 // write the token's int8 codes and scale there -- the gather and the per-token quant of
 // npu_moe_init_routing_quant (acceleration/runtime_patches/vllm_ascend.patch:2369-2379)
 // in one pass.  Arithmetic as in act_quant.cu.
+// KEEP: rows of up to 4096 values (two 16-byte pieces per thread) stay in registers between the abs-max pass
+// and the quantising pass instead of being read a second time.
+template <bool KEEP>
 __global__ void __launch_bounds__(256)
 moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict__ ids, int H, int k, int lo, int hi,
                         int* __restrict__ plan, int E, int* __restrict__ dest_row,
@@ -154,13 +157,28 @@ moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict
   const __half* xr = hidden + (size_t)t * H;
   const int chunks = H >> 3;
   float amax = 0.0f;
-  for (int c = threadIdx.x; c < chunks; c += 256) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
-    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+  [[maybe_unused]] uint4 kept[2];
+  if constexpr (KEEP) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 f = __half22float2(__habs2(h2[j]));
-      amax = fmaxf(amax, fmaxf(f.x, f.y));
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + 256 * i;
+      kept[i] = c < chunks ? *reinterpret_cast<const uint4*>(xr + c * 8) : make_uint4(0, 0, 0, 0);
+      const __half2* h2 = reinterpret_cast<const __half2*>(&kept[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(__habs2(h2[j]));
+        amax = fmaxf(amax, fmaxf(f.x, f.y));
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < chunks; c += 256) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(__habs2(h2[j]));
+        amax = fmaxf(amax, fmaxf(f.x, f.y));
+      }
     }
   }
 #pragma unroll
@@ -182,9 +200,17 @@ moe_gather_quant_kernel(const __half* __restrict__ hidden, const int* __restrict
   const float sf = s_scale;
   const RowQuant rq = make_row_quant(sf);
   int8_t* qr = routed_q + (size_t)s_dest * H;
-  for (int c = threadIdx.x; c < chunks; c += 256) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
-    *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+  if constexpr (KEEP) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + 256 * i;
+      if (c < chunks) *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(kept[i], rq);
+    }
+  } else {
+    for (int c = threadIdx.x; c < chunks; c += 256) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + c * 8);
+      *reinterpret_cast<uint2*>(qr + c * 8) = quant8_pack(raw, rq);
+    }
   }
 }
 
@@ -373,7 +399,8 @@ extern "C" int mp_moe_route_gather_quant(const void* hidden_f16, const void* top
     moe_plan_kernel<<<1, 32, 0, st>>>(plan, E, padded / kTileRows);
     MP_LAUNCH_CHECK();
   }
-  return launch_chained(moe_gather_quant_kernel, dim3(n_entries), dim3(256), 0, st,
+  return launch_chained(H <= 4096 ? moe_gather_quant_kernel<true> : moe_gather_quant_kernel<false>, dim3(n_entries),
+                        dim3(256), 0, st,
                         static_cast<const __half*>(hidden_f16), static_cast<const int*>(topk_ids_i32), H, k, expert_lo,
                         expert_hi, plan, E, static_cast<int*>(dest_row_i32), static_cast<int8_t*>(routed_q_i8),
                         static_cast<float*>(routed_scale_f32));

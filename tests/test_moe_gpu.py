@@ -32,10 +32,11 @@ def test_router_matches_reference(golden):
     assert np.allclose(w.float().cpu().numpy(), ow.astype(np.float32), atol=1e-3)
 
 
+@pytest.mark.parametrize("h", [256, 4096, 4608])          # rows kept in registers (<= 4096 values) or read twice
 @pytest.mark.parametrize("lo,hi", [(0, 8), (2, 5), (7, 8)])
-def test_route_gather_quant_bit_exact(lo, hi):
+def test_route_gather_quant_bit_exact(lo, hi, h):
     from mindpipe_b200 import ops
-    t, h, e, k = 777, 256, 8, 2
+    t, e, k = 777, 8, 2
     hs = synth.outlier_activation(t, h, seed=3).numpy()
     ids, _ = O.router_top2(synth.router_logits(t, e, seed=3).numpy(), k)
     ids = ids.astype(np.int32)
