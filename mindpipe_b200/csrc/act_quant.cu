@@ -37,6 +37,8 @@ template <int NV, bool CODES, bool FAKE>
 __global__ void __launch_bounds__(128)
 act_quant_warp_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
                       float* __restrict__ scale, __half* __restrict__ fake) {
+  chain_wait();              // programmatic dependent launch: the producer of x has finished
+  chain_release();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= M) return;
   const int lane = threadIdx.x & 31;
@@ -77,14 +79,14 @@ act_quant_warp_kernel(const __half* __restrict__ x, int M, int K, int8_t* __rest
 }
 
 template <int NV>
-static void launch_act_quant_warp(const __half* x, int M, int K, int8_t* q, float* sc, __half* fk, cudaStream_t st) {
+static int launch_act_quant_warp(const __half* x, int M, int K, int8_t* q, float* sc, __half* fk, cudaStream_t st) {
   const unsigned blocks = static_cast<unsigned>((M + 3) / 4);
   if (q && fk) {
-    act_quant_warp_kernel<NV, true, true><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_warp_kernel<NV, true, true>, dim3(blocks), dim3(128), 0, st, x, M, K, q, sc, fk);
   } else if (q) {
-    act_quant_warp_kernel<NV, true, false><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_warp_kernel<NV, true, false>, dim3(blocks), dim3(128), 0, st, x, M, K, q, sc, fk);
   } else {
-    act_quant_warp_kernel<NV, false, true><<<blocks, 128, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_warp_kernel<NV, false, true>, dim3(blocks), dim3(128), 0, st, x, M, K, q, sc, fk);
   }
 }
 
@@ -95,6 +97,8 @@ template <int THREADS, int NV>
 __global__ void __launch_bounds__(THREADS)
 act_quant_kernel(const __half* __restrict__ x, int M, int K, int8_t* __restrict__ q,
                  float* __restrict__ scale, __half* __restrict__ fake) {
+  chain_wait();
+  chain_release();
   __shared__ float s_red[THREADS / 32];
   __shared__ float s_scale;
   const int row = blockIdx.x;
@@ -357,20 +361,18 @@ extern "C" int mp_act_quant_per_token(const void* x_f16, int M, int K, void* q_i
   float* sc = static_cast<float*>(scale_f32);
   __half* fk = static_cast<__half*>(fake_f16);
   if (K <= 1024) {
-    launch_act_quant_warp<4>(x, M, K, q, sc, fk, st);
+    return launch_act_quant_warp<4>(x, M, K, q, sc, fk, st);
   } else if (K <= 2048) {
-    launch_act_quant_warp<8>(x, M, K, q, sc, fk, st);
+    return launch_act_quant_warp<8>(x, M, K, q, sc, fk, st);
   } else if (K <= 4096) {
-    launch_act_quant_warp<16>(x, M, K, q, sc, fk, st);
+    return launch_act_quant_warp<16>(x, M, K, q, sc, fk, st);
   } else if (K <= 8192) {
-    act_quant_kernel<512, 2><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_kernel<512, 2>, dim3(M), dim3(512), 0, st, x, M, K, q, sc, fk);
   } else if (K <= 16384) {
-    act_quant_kernel<512, 4><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_kernel<512, 4>, dim3(M), dim3(512), 0, st, x, M, K, q, sc, fk);
   } else {
-    act_quant_kernel<512, 0><<<M, 512, 0, st>>>(x, M, K, q, sc, fk);
+    return launch_chained(act_quant_kernel<512, 0>, dim3(M), dim3(512), 0, st, x, M, K, q, sc, fk);
   }
-  MP_LAUNCH_CHECK();
-  return MP_OK;
 }
 
 extern "C" int mp_affine_quant_per_row(const void* x_f16, int M, int K, void* q_u8, void* scale_f32, void* zero_f32,

@@ -553,6 +553,8 @@ template <bool F16OUT>
 __global__ void __launch_bounds__(256)
 w8a8_splitk_reduce_kernel(const int* __restrict__ partial, int k_split, int M, int N, const float* __restrict__ a_scale,
                           const float* __restrict__ b_scale, const __half* __restrict__ bias, void* __restrict__ out) {
+  chain_wait();
+  chain_release();
   const int quads = N >> 2;
   const size_t slice = (size_t)M * N;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += gridDim.x * blockDim.x) {
@@ -674,10 +676,8 @@ template <bool F16OUT>
 static int launch_splitk_reduce(const GemmCall& c, cudaStream_t st) {
   int blocks = (c.M * (c.N / 4) + 255) / 256;
   if (blocks > 2 * kSmCount) blocks = 2 * kSmCount;
-  w8a8_splitk_reduce_kernel<F16OUT><<<blocks, 256, 0, st>>>(c.partial, c.k_split, c.M, c.N, c.a_scale, c.b_scale, c.bias,
-                                                           c.out);
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(w8a8_splitk_reduce_kernel<F16OUT>, dim3(blocks), dim3(256), 0, st, c.partial, c.k_split, c.M, c.N,
+                        c.a_scale, c.b_scale, c.bias, c.out);
 }
 
 // The CTA-pair form pays once there are enough 256-row tiles to occupy the 74 pairs.

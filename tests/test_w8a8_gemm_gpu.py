@@ -145,6 +145,39 @@ def test_w8a8_cfg3_other_shapes_row_sample(n, k):
     assert O.rel_frobenius(y[rows], ref) <= TOL
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (16, 1024, 14336), (300, 512, 1024), (4096, 1024, 4096)])
+def test_w8a8_linear_under_programmatic_dependent_launch_same_bits(m, n, k):
+    """Per-token quant -> GEMM (-> split-K reduce for small batches), each launch allowed to be scheduled before
+    its predecessor has finished (every kernel waits on the device): same bits as the serialised launches, eagerly
+    and as a replayed CUDA graph of three forwards."""
+    from mindpipe_b200 import _lib, ops
+    from mindpipe_b200.modules import SmoothQuantLinear
+    lin = torch.nn.Linear(k, n, bias=True).half().cuda()
+    mod = SmoothQuantLinear.from_float(lin, quantize_output=(m == 300))
+    x = synth.outlier_activation(m, k, seed=17).cuda()
+    base = mod(x)
+    lib = _lib.load()
+    before = lib.mp_set_programmatic_launch(1)
+    try:
+        for _ in range(3):
+            assert torch.equal(mod(x), base)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            mod(x)
+            with torch.cuda.graph(graph, stream=side):
+                outs = [mod(x) for _ in range(3)]
+            graph.replay()
+            graph.replay()
+        side.synchronize()
+        for o in outs:
+            assert torch.equal(o, base)
+    finally:
+        lib.mp_set_programmatic_launch(before)
+    ops.check_device_errors()
+
+
 def test_smoothquant_linear_module_matches_reference_golden(golden):
     """SmoothQuantLinear twin (int8 weights) vs the reference module's outputs on the golden case."""
     from mindpipe_b200 import ops
