@@ -50,6 +50,14 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert lib.mp_w4a16_decode_workspace_bytes_ex(16, 4096, 4096, 4) > 0
     assert lib.mp_w4a16_decode_workspace_bytes(128, 4096, 4096) == 0     # decode kernel is M <= 64
     assert lib.mp_w4a16_decode_workspace_bytes(1, 4096, 100) == 0        # K must be a multiple of 128
+    assert lib.mp_w4a16_linear_decode_host_many(None, 0, None) == -1
+    too_many_rows = (_lib.HostLinear * 1)()
+    too_many_rows[0].x_host_f16 = too_many_rows[0].x_stage_f16 = too_many_rows[0].y_stage_f16 = 4096   # never touched
+    too_many_rows[0].M, too_many_rows[0].N, too_many_rows[0].K, too_many_rows[0].group = 17, 128, 128, 128
+    assert lib.mp_w4a16_linear_decode_host_many(too_many_rows, 1, None) == -2      # host-buffer form: M <= 16
+    assert lib.mp_host_buffer_device_alias(None, 0, None) == -1
+    assert lib.mp_moe_ep_push_signal(None, None, 2, 1, 256, 128, None, None, 0, None, None, None) == -1
+    assert lib.mp_moe_combine_after_peers(None, 2, None, None, None, None, None, 4, 128, 2, None, None, None) == -1
     with pytest.raises(_lib.MindPipeKernelError, match="invalid argument"):
         _lib.check(-1, "probe", M=1)
 
