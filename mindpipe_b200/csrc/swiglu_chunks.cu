@@ -20,6 +20,8 @@ namespace mp {
 __global__ void __launch_bounds__(256)
 chunk_stage_kernel(const uint4* __restrict__ x, const float* __restrict__ x_scale, int T, int t_pad, int vec_per_row,
                    int chunks, uint4* __restrict__ x_rep, float* __restrict__ scale_rep, int* __restrict__ plan) {
+  chain_wait();                                     // programmatic dependent launch: the producer of x has finished
+  chain_release();
   const int row = blockIdx.x;                       // row of the replicated buffer
   const int t = row % t_pad;
   if (row == 0) {
@@ -42,6 +44,8 @@ chunk_stage_kernel(const uint4* __restrict__ x, const float* __restrict__ x_scal
 __global__ void __launch_bounds__(256)
 chunk_requant_kernel(const __half* __restrict__ h, const float* __restrict__ absmax, int slots, int T, int t_pad,
                      int C, int8_t* __restrict__ q, float* __restrict__ scale) {
+  chain_wait();
+  chain_release();
   __shared__ float s_red[8];
   const int c = blockIdx.x / T, t = blockIdx.x % T;
   const size_t src_row = (size_t)c * t_pad + t;
@@ -108,16 +112,14 @@ extern "C" int mp_w8a8_gate_up_swiglu_requant(const void* x_i8, const void* x_sc
   __half* h = reinterpret_cast<__half*>(ws);
   ws += up256(P * C * 2);
   float* absmax = reinterpret_cast<float*>(ws);
-  chunk_stage_kernel<<<(unsigned)P, 256, 0, st>>>(static_cast<const uint4*>(x_i8),
-                                                  static_cast<const float*>(x_scale_f32), T, t_pad, H / 16, chunks,
-                                                  reinterpret_cast<uint4*>(x_rep), scale_rep, plan);
-  MP_LAUNCH_CHECK();
-  int rc = launch_moe_gemm1_swiglu(x_rep, scale_rep, w_i8, static_cast<const float*>(w_scale_f32), (int)P, H, C,
+  int rc = launch_chained(chunk_stage_kernel, dim3((unsigned)P), dim3(256), 0, st, static_cast<const uint4*>(x_i8),
+                          static_cast<const float*>(x_scale_f32), T, t_pad, H / 16, chunks,
+                          reinterpret_cast<uint4*>(x_rep), scale_rep, plan);
+  if (rc != MP_OK) return rc;
+  rc = launch_moe_gemm1_swiglu(x_rep, scale_rep, w_i8, static_cast<const float*>(w_scale_f32), (int)P, H, C,
                                    chunks, plan, plan + 1, h, absmax, error_word, st);
   if (rc != MP_OK) return rc;
-  chunk_requant_kernel<<<(unsigned)(chunks * T), 256, 0, st>>>(h, absmax, moe_absmax_slots(C), T, t_pad, C,
-                                                               static_cast<int8_t*>(q_out_i8),
-                                                               static_cast<float*>(scale_out_f32));
-  MP_LAUNCH_CHECK();
-  return MP_OK;
+  return launch_chained(chunk_requant_kernel, dim3((unsigned)(chunks * T)), dim3(256), 0, st, h, absmax,
+                        moe_absmax_slots(C), T, t_pad, C, static_cast<int8_t*>(q_out_i8),
+                        static_cast<float*>(scale_out_f32));
 }

@@ -84,6 +84,21 @@ def test_loop_out_matches_oracle_composition(ops, t, h, c, chunks):
     _check(q, s, ref_q, ref_s)
 
 
+def test_loop_out_under_programmatic_dependent_launch_same_bits(ops):
+    """The op's three launches chained (each kernel waits for its predecessor on the device): the bits of the
+    serialised launches."""
+    from mindpipe_b200 import _lib
+    base = _run(ops, 300, 512, 256, 3, seed=77)
+    lib = _lib.load()
+    before = lib.mp_set_programmatic_launch(1)
+    try:
+        for _ in range(3):
+            got = _run(ops, 300, 512, 256, 3, seed=77)
+            assert np.array_equal(got[4], base[4]) and np.array_equal(got[5], base[5])
+    finally:
+        lib.mp_set_programmatic_launch(before)
+
+
 def test_loop_out_qwen25_vl_7b_shape_token_sample(ops):
     """Hidden 3584, four chunks of 4736 (scripts/repro/verify_qwen25_vl_w8a8_loop_out_hybrid.py:17-19), a ragged
     token count; the oracle runs on a seeded sample of tokens (each output row depends on its own token only)."""
