@@ -289,3 +289,80 @@ def test_all_gather_wire_layout(world, rows, slice_bytes):
                     assert (w[1::2] == epoch).all()
                     out[mm, r, 4 * j:4 * j + 4] = w[0::2]
         assert np.array_equal(out, np.transpose(src, (1, 0, 2)))
+
+
+# ---- the expert-parallel layer's epoch protocol, replayed on the CPU under random interleavings ----
+def _ep_rank_program(r, world, layers, flags, epoch, q_version, back_version, log):
+    """One rank of SymmetricExpertParallelMoE.forward as a generator: every ``yield`` is a point where another
+    rank may run; ``yield cond`` (a callable) blocks until the condition holds.  Buffers are modelled by version
+    numbers: q_version[r] = layer whose routed rows rank r's buffer holds, back_version[r][p] = layer whose result
+    rows rank p has stored into rank r's result buffer."""
+    for layer in range(1, layers + 1):
+        # route: overwrite this rank's routed buffer (peers must be done pulling the previous layer's rows)
+        q_version[r] = ("writing", layer)
+        yield None
+        q_version[r] = layer
+        yield None
+        # barrier + plan (mp_moe_ep_barrier_plan): advance the epoch, raise the word on every peer, wait for theirs
+        epoch[r] += 1
+        e = epoch[r]
+        for p in range(world):
+            flags[p][r] = e
+            yield None
+        yield (lambda e=e: all((flags[r][p] - e) % (1 << 32) < (1 << 31) for p in range(world)))
+        # pull: every peer's routed rows must be this layer's, completely written
+        for p in range(world):
+            assert q_version[p] == layer, (r, p, layer, q_version[p])
+            yield None
+        log.append(("pulled", r, layer))
+        # expert stage, then push: store result rows into every peer's buffer
+        for p in range(world):
+            assert back_version[p][r] in (layer - 1, ("read", layer - 1)), (r, p, layer, back_version[p][r])
+            back_version[p][r] = layer
+            yield None
+        # the push's last block: advance the epoch and raise the word on every peer (mp_moe_ep_push_signal)
+        epoch[r] += 1
+        e = epoch[r]
+        for p in range(world):
+            flags[p][r] = e
+            yield None
+        # combine (mp_moe_combine_after_peers): wait for every peer's word, then read this rank's result buffer
+        yield (lambda e=e: all((flags[r][p] - e) % (1 << 32) < (1 << 31) for p in range(world)))
+        for p in range(world):
+            assert back_version[r][p] == layer, (r, p, layer, back_version[r][p])
+            back_version[r][p] = ("read", layer)
+            yield None
+        log.append(("combined", r, layer))
+
+
+@pytest.mark.parametrize("world,seed", [(2, 0), (2, 1), (4, 2), (8, 3), (8, 4)])
+def test_expert_parallel_epoch_protocol_under_random_interleavings(world, seed):
+    """Barrier-and-plan, push-then-signal and wait-then-combine with one epoch counter per rank: under any
+    interleaving no rank pulls rows that are not this layer's, overwrites result rows a peer has not combined
+    yet, or combines before every peer has stored.  The epochs start near the 32-bit wrap."""
+    rng = np.random.default_rng(seed)
+    layers = 6
+    start = (1 << 32) - 5                                   # the counters wrap during the run
+    flags = [[start] * world for _ in range(world)]
+    epoch = [start] * world
+    q_version = [0] * world
+    back_version = [[0] * world for _ in range(world)]
+    log = []
+    progs = [_ep_rank_program(r, world, layers, flags, epoch, q_version, back_version, log) for r in range(world)]
+    # wrap the model's epochs to 32 bits where they are stored
+    waiting = [None] * world
+    alive = set(range(world))
+    steps = 0
+    while alive:
+        steps += 1
+        assert steps < 10 ** 6, "deadlock"
+        runnable = [r for r in alive if waiting[r] is None or waiting[r]()]
+        assert runnable, "every rank is blocked"
+        r = int(rng.choice(runnable))
+        epoch[r] %= 1 << 32
+        try:
+            waiting[r] = next(progs[r])
+        except StopIteration:
+            alive.discard(r)
+            waiting[r] = None
+    assert sum(1 for ev in log if ev[0] == "combined") == world * layers
